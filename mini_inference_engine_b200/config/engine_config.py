@@ -1,0 +1,39 @@
+"""Engine options.  Names and meanings follow ``EngineConfig`` of
+inference_engine/config.py:45-56; the two Triton switches have no counterpart here
+(every GPU op is this package's own CUDA), and ``num_blocks`` and ``seed`` are added:
+tests need tiny page pools (the reference can only shrink its pool through the memory
+fraction, tests/test_correctness.py:46), and seeded sampling needs a seed."""
+from __future__ import annotations
+
+from dataclasses import dataclass, fields
+
+
+@dataclass
+class EngineConfig:
+    block_size: int = 16                    # tokens per cache page
+    max_num_seqs: int = 256                 # most requests running at once
+    max_num_batched_tokens: int = 2048      # token budget of one step (caps a prompt portion)
+    kv_cache_memory_fraction: float = 0.85  # of the memory free after the weights are loaded
+    max_model_len: int = 2048
+    enable_chunked_prefill: bool = True
+    use_cuda_graphs: bool = True
+    cuda_graph_batch_sizes: tuple = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256)
+    num_blocks: int | None = None           # explicit pool size in pages (page 0 included); None = from memory
+    seed: int = 0                           # sampling seed
+
+    def __post_init__(self):
+        if self.block_size < 16 or self.block_size & (self.block_size - 1) or self.block_size > 128:
+            raise ValueError(f"block_size must be a power of two in 16..128, got {self.block_size}")
+        if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1 or self.max_model_len < 1:
+            raise ValueError("max_num_seqs, max_num_batched_tokens and max_model_len must be positive")
+        self.cuda_graph_batch_sizes = tuple(sorted(set(int(b) for b in self.cuda_graph_batch_sizes)))
+
+    @classmethod
+    def from_overrides(cls, overrides: dict | None) -> "EngineConfig":
+        """``--overrides '<json>'`` of benchmarks/bench_throughput.py:100,147."""
+        overrides = dict(overrides or {})
+        known = {f.name for f in fields(cls)}
+        unknown = sorted(set(overrides) - known)
+        if unknown:
+            raise ValueError(f"unknown EngineConfig option(s): {', '.join(unknown)}")
+        return cls(**overrides)

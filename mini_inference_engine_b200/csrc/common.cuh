@@ -1,0 +1,62 @@
+// Shared device helpers for the kernels of this package (sm_100a only).
+// Every launcher is an extern "C" function that takes raw device pointers, sizes and a
+// stream, launches on that stream and returns the cudaError_t of the launch (0 = ok), or a
+// negative code of its own for arguments it refuses.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MIE_ERR_BAD_ARG (-1)      // a size or option this kernel does not take
+#define MIE_ERR_TOO_LARGE (-2)    // beyond a stated maximum
+
+// element type tags shared with the Python side
+#define MIE_F32 0
+#define MIE_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// load by runtime tag (norm weights and tables may be stored in either type)
+__device__ __forceinline__ float load_tagged(const void* p, int64_t i, int tag) {
+    return tag == MIE_F32 ? reinterpret_cast<const float*>(p)[i]
+                          : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` is 33 floats of
+// shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();                       // protect `red` against a previous use
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }

@@ -1,0 +1,31 @@
+// Embedding gather: res[t, :] = table[ids[t], :], written as float32 because the gathered row
+// opens the residual stream, which this engine keeps in 32-bit
+// (what F.embedding does at inference_engine/model.py:168).
+#include "common.cuh"
+
+template <typename TT>
+__global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    // ids are checked on the host when a request is added; the clamp only keeps a bad id from
+    // reading outside the table
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const TT* src = table + (int64_t)id * hidden;
+    float* dst = out + (int64_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<TT>(src[i]);
+}
+
+extern "C" int mie_embedding(const void* table, int table_tag, const int* ids, float* out,
+                             int num_tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0) return MIE_ERR_BAD_ARG;
+    const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
+    if (table_tag == MIE_F32)
+        embedding_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    else if (table_tag == MIE_BF16)
+        embedding_kernel<bf16><<<num_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
+    else
+        return MIE_ERR_BAD_ARG;
+    return launch_status();
+}

@@ -1,0 +1,63 @@
+// Fused residual-add + RMSNorm.
+//   res[r, :] += delta[r, :]            (float32 residual stream, updated in place)
+//   out[r, :]  = res[r, :] * rsqrt(mean(res[r, :]^2) + eps) * w[:]
+// One block per row; the summed row stays in shared memory between the two passes, so each
+// input is read once.  Statistics, the sum and the scaling are float32; only `out` is rounded
+// to the activation type.  The reference's Triton kernel does the same in one program per row
+// but keeps the residual in the model dtype (inference_engine/kernels/rmsnorm.py:13-32).
+//
+// `rows` (optional) gathers: output row b is computed from input row rows[b] and the residual
+// is left untouched -- the row selection before the final norm (inference_engine/model.py:182-184).
+#include "common.cuh"
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ res,
+                                   const void* __restrict__ w, int w_tag, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int n, float eps, int use_smem) {
+    extern __shared__ float row_cache[];
+    __shared__ float red[33];
+    const int b = blockIdx.x;
+    const int64_t r = rows ? rows[b] : b;
+    float* res_row = res + r * n;
+    const TD* d_row = delta ? delta + r * n : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = res_row[i];
+        if (d_row) v += to_f32<TD>(d_row[i]);
+        if (use_smem) row_cache[i] = v;
+        if (!rows && d_row) res_row[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(total / (float)n + eps);
+    TO* o_row = out + (int64_t)b * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v;
+        if (use_smem) v = row_cache[i];
+        else { v = res_row[i]; if (rows && d_row) v += to_f32<TD>(d_row[i]); }
+        o_row[i] = from_f32<TO>(v * rstd * load_tagged(w, i, w_tag));
+    }
+}
+
+// act_tag: type of delta and out (MIE_F32 or MIE_BF16).  delta may be null (first layer: the
+// residual already holds the embedding).
+extern "C" int mie_add_rmsnorm(const void* delta, float* res, const void* w, int w_tag, void* out,
+                               int act_tag, const int* rows, int num_rows, int n, float eps,
+                               cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (n <= 0) return MIE_ERR_BAD_ARG;
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < n) threads <<= 1;
+    const size_t smem_bytes = (size_t)n * sizeof(float);
+    const int use_smem = smem_bytes <= 40 * 1024;
+    const size_t smem = use_smem ? smem_bytes : 0;
+    if (act_tag == MIE_F32)
+        add_rmsnorm_kernel<float, float><<<num_rows, threads, smem, stream>>>(
+            (const float*)delta, res, w, w_tag, (float*)out, rows, n, eps, use_smem);
+    else if (act_tag == MIE_BF16)
+        add_rmsnorm_kernel<bf16, bf16><<<num_rows, threads, smem, stream>>>(
+            (const bf16*)delta, res, w, w_tag, (bf16*)out, rows, n, eps, use_smem);
+    else
+        return MIE_ERR_BAD_ARG;
+    return launch_status();
+}

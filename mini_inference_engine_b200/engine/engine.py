@@ -1,0 +1,289 @@
+"""``LLMEngine``: the Python entry point, with the surface of inference_engine/engine.py:35-244 --
+``LLMEngine(model, engine_config, dtype, load_tokenizer, verbose)``, ``add_request``, ``step``,
+``generate`` returning ``RequestOutput(seq_id, prompt_len, output_ids, text, ttft, latency)``.
+
+One step: schedule -> pack the batch (one host->device transfer) -> the model's step function
+(a captured CUDA graph for pure-decode steps, eager otherwise) -> sample on the device -> one small
+device->host read of the new tokens -> bookkeeping.  Sampling is inside the captured graph, so a
+decode step is one transfer in, one graph launch, one transfer out.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig, load_config
+from ..models.decoder import DecoderModel
+from ..parts.base import Runtime
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights import read_model_folder
+from .runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import Sequence
+
+ACTIVATION_RESERVE = 768 * 2 ** 20      # kept free for activations when sizing the cache (inference_engine/engine.py:51)
+
+
+@dataclass
+class RequestOutput:
+    seq_id: int
+    prompt_len: int
+    output_ids: list
+    text: str | None
+    ttft: float | None          # seconds from arrival to the first generated token
+    latency: float | None       # seconds from arrival to the end
+
+
+class _DecodeGraph:
+    def __init__(self, graph, layout, buffer, tokens):
+        self.graph, self.layout, self.buffer, self.tokens = graph, layout, buffer, tokens
+
+
+def _nvtx_range(name):
+    return torch.cuda.nvtx.range(name)
+
+
+class LLMEngine:
+    def __init__(self, model: str, engine_config: EngineConfig | None = None, dtype=torch.bfloat16,
+                 load_tokenizer: bool = True, verbose: bool = True, device: str = "cuda:0"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("LLMEngine needs a CUDA device: every operator is a CUDA kernel of this package")
+        self.cfg = engine_config or EngineConfig()
+        self.verbose = verbose
+        if not os.path.isdir(model):
+            raise FileNotFoundError(f"{model!r} is not a model folder (config.json + *.safetensors); "
+                                    "downloading by name is not supported")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.model_cfg = load_config(model)
+        spec = self.model_cfg.model_spec()
+        self.cfg.max_model_len = min(self.cfg.max_model_len, spec.max_position)      # inference_engine/engine.py:42
+        self.eos_token_id = spec.eos_token_id
+        self.vocab_size = spec.vocab_size
+        rt = Runtime(self.device, dtype)
+        self.model = DecoderModel(spec, read_model_folder(model), rt, where=model)
+        torch.cuda.empty_cache()
+
+        layout = self.model.cache_layout
+        per_page = sum(layout.bytes_per_page(g, self.cfg.block_size, dtype) for g in range(len(layout.groups)))
+        if self.cfg.num_blocks is not None:
+            num_blocks = int(self.cfg.num_blocks)
+        else:                                      # size the pool from the memory left after the weights
+            free, _ = torch.cuda.mem_get_info(self.device)
+            state = layout.bytes_per_state_slot() * (self.cfg.max_num_seqs + 1)
+            kv_bytes = int((free - ACTIVATION_RESERVE - state) * self.cfg.kv_cache_memory_fraction)
+            num_blocks = kv_bytes // max(per_page, 1)
+            # no request can use more than max_model_len positions: cap what max_num_seqs can ever hold
+            ceiling = self.cfg.max_num_seqs * (-(-self.cfg.max_model_len // self.cfg.block_size)) + 1
+            num_blocks = min(num_blocks, ceiling + max(1, ceiling // 100) + 1)
+        if num_blocks < 2:
+            raise RuntimeError(f"not enough memory for the cache: {num_blocks} pages of {per_page} bytes")
+        self.runner = ModelRunner(self.model, num_blocks, self.cfg.block_size, self.cfg.max_num_seqs)
+        self.cache = self.runner.cache
+        self.scheduler = Scheduler(self.cfg, self.cache)
+        self.max_blocks_per_seq = -(-self.cfg.max_model_len // self.cfg.block_size)
+        self.sampler = Sampler(self.device, self.cfg.seed)
+        if verbose:
+            print(f"[mini_inference_engine_b200] cache: {num_blocks} pages x {self.cfg.block_size} tokens = "
+                  f"{num_blocks * self.cfg.block_size} tokens ({num_blocks * per_page / 2 ** 30:.2f} GiB)")
+
+        self.tokenizer = None
+        if load_tokenizer and any(os.path.isfile(os.path.join(model, f))
+                                  for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")):
+            from transformers import AutoTokenizer          # text in/out only; never on the token path
+            self.tokenizer = AutoTokenizer.from_pretrained(model)
+
+        self._pinned_tokens = torch.empty(max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs, 256),
+                                          dtype=torch.int32, pin_memory=True)
+        self.graphs: dict = {}
+        self.graph_sizes: list = []
+        self.num_steps = 0
+        self.num_graph_steps = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        if self.cfg.use_cuda_graphs:
+            self._capture_cuda_graphs()
+
+    # ------------------------------------------------------------------ CUDA graphs of decode steps
+    def _sampling_extras(self, n, temps=None, reqs=None, outpos=None):
+        t = np.zeros(n, dtype=np.float32)
+        r = np.zeros(n, dtype=np.int64)
+        p = np.zeros(n, dtype=np.int32)
+        if temps is not None:
+            k = len(temps)
+            t[:k], r[:k], p[:k] = temps, reqs, outpos
+        return {"temperature": t, "request": r, "out_position": p}
+
+    def _forward_and_sample(self, ctx, tokens_out=None):
+        logits = self.model.step(ctx)
+        if logits.shape[0] == 0:
+            return None
+        return self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
+                                   ctx.extras["out_position"], out=tokens_out)
+
+    @torch.inference_mode()
+    def _capture_cuda_graphs(self):
+        """One graph per batch-size bucket, largest first so the smaller ones share its memory
+        pool (inference_engine/engine.py:76-104).  A graph covers the whole step including the
+        sampling kernel; its inputs live in one static device buffer that a step overwrites with one
+        copy.  Rows that pad a batch up to its bucket are scratch rows: one token at position 0 of
+        page 0, context length 1."""
+        t0 = time.perf_counter()
+        sizes = sorted(b for b in self.cfg.cuda_graph_batch_sizes if b <= self.cfg.max_num_seqs)
+        if not sizes:
+            return
+        b = self.runner.builder
+        pool = None
+        for bs in reversed(sizes):
+            buf, layout = b.pack([], pad_rows=bs, table_width=self.max_blocks_per_seq,
+                                 extras=self._sampling_extras(bs))
+            layout["max_ctx_len"] = self.cfg.max_model_len          # static bound for kernels that plan by it
+            static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
+            ctx = b.to_device(buf, layout, into=static)
+            tokens = torch.zeros(bs, dtype=torch.int32, device=self.device)
+            self._forward_and_sample(ctx, tokens)                   # warm-up: builds kernels, sizes buffers
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                self._forward_and_sample(ctx, tokens)
+            pool = g.pool()
+            self.graphs[bs] = _DecodeGraph(g, layout, static, tokens)
+        torch.cuda.synchronize()
+        self.graph_sizes = sizes
+        if self.verbose:
+            print(f"[mini_inference_engine_b200] captured {len(sizes)} decode graphs (batch <= {sizes[-1]}) "
+                  f"in {time.perf_counter() - t0:.1f} s")
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt, params: SamplingParams | None = None) -> Sequence:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a text prompt needs a tokenizer in the model folder; pass token ids instead")
+            ids = self.tokenizer.encode(prompt)
+        else:
+            ids = [int(t) for t in prompt]
+        params = params or SamplingParams()
+        if not ids:
+            raise ValueError("empty prompt")
+        bad = [t for t in ids if not 0 <= t < self.vocab_size]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {self.vocab_size})")
+        if len(ids) > self.cfg.max_model_len:
+            raise ValueError(f"prompt of {len(ids)} tokens exceeds max_model_len {self.cfg.max_model_len}")
+        if len(ids) + params.max_tokens > self.cfg.max_model_len:     # inference_engine/engine.py:126-127
+            params = SamplingParams(**{**params.__dict__, "max_tokens": max(1, self.cfg.max_model_len - len(ids))})
+        most = min(len(ids) + params.max_tokens, self.cfg.max_model_len)
+        if not self.scheduler.can_ever_fit(most):
+            raise ValueError(f"a request of {most} positions can never fit the cache "
+                             f"({self.cache.pools[0].num_usable} usable pages of {self.cfg.block_size})")
+        seq = Sequence(ids, params)
+        self.scheduler.add(seq)
+        return seq
+
+    # ------------------------------------------------------------------ one engine step
+    @torch.inference_mode()
+    def step(self) -> list:
+        """One scheduling + model step; returns the requests that finished in it."""
+        with _nvtx_range("schedule"):
+            batch = self.scheduler.schedule()
+        if not batch:
+            return []
+        with _nvtx_range("prepare"):
+            rows, sample_seqs = [], []
+            for seq, n in batch:
+                nc = seq.num_computed
+                last = nc + n == seq.num_tokens
+                rows.append(self.runner.make_row(seq.cache, seq.token_ids[nc:nc + n], [n - 1] if last else []))
+                if last:
+                    sample_seqs.append(seq)
+            extras = self._sampling_extras(
+                len(sample_seqs), [s.params.temperature for s in sample_seqs], [s.seq_id for s in sample_seqs],
+                [s.num_output_tokens for s in sample_seqs]) if sample_seqs else None
+            # the seed of a sampled row: its own if it has one, else the engine's
+            row_seeds = [self.cfg.seed if s.params.seed is None else s.params.seed for s in sample_seqs]
+            seeds = {sd for sd, s in zip(row_seeds, sample_seqs) if s.params.temperature > 0}
+            pure_decode = len(sample_seqs) == len(batch) and all(n == 1 for _, n in batch)
+            use_graph = (pure_decode and self.graph_sizes and len(batch) <= self.graph_sizes[-1]
+                         and seeds <= {self.cfg.seed})
+
+        with _nvtx_range("forward"):
+            b = self.runner.builder
+            if use_graph:
+                bs = next(s for s in self.graph_sizes if s >= len(batch))
+                g = self.graphs[bs]
+                ex = self._sampling_extras(bs, extras["temperature"], extras["request"], extras["out_position"])
+                buf, layout = b.pack(rows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=ex)
+                assert layout["size"] == g.layout["size"]
+                b.to_device(buf, g.layout, into=g.buffer)
+                g.graph.replay()
+                tokens = g.tokens
+                self.num_graph_steps += 1
+                self.h2d_bytes += buf.nbytes
+            else:
+                buf, layout = b.pack(rows, extras=extras)
+                ctx = b.to_device(buf, layout)
+                self.h2d_bytes += buf.nbytes
+                logits = self.model.step(ctx)
+                tokens = None
+                if sample_seqs and len(seeds) <= 1:
+                    tokens = self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
+                                                 ctx.extras["out_position"],
+                                                 seed=next(iter(seeds)) if seeds else None)
+                elif sample_seqs:           # requests with different seeds of their own: one launch per row
+                    tokens = torch.empty(len(sample_seqs), dtype=torch.int32, device=self.device)
+                    for i, sd in enumerate(row_seeds):
+                        self.sampler.sample(logits[i:i + 1], ctx.extras["temperature"][i:i + 1],
+                                            ctx.extras["request"][i:i + 1], ctx.extras["out_position"][i:i + 1],
+                                            out=tokens[i:i + 1], seed=sd)
+
+        with _nvtx_range("sample"):
+            new_tokens = []
+            if sample_seqs:
+                k = len(sample_seqs)
+                self._pinned_tokens[:k].copy_(tokens[:k], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                new_tokens = self._pinned_tokens[:k].tolist()
+                self.d2h_bytes += 4 * k
+            else:
+                torch.cuda.current_stream().synchronize()
+
+        self.num_steps += 1
+        for seq, n in batch:
+            self.cache.advance(seq.cache, n)
+        now = time.perf_counter()
+        finished = []
+        for seq, tok in zip(sample_seqs, new_tokens):
+            seq.token_ids.append(tok)
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+            done = (seq.num_output_tokens >= seq.params.max_tokens
+                    or seq.num_tokens >= self.cfg.max_model_len
+                    or (tok == self.eos_token_id and not seq.params.ignore_eos))    # inference_engine/engine.py:222-224
+            if done:
+                seq.finish_time = now
+                self.scheduler.finish(seq)
+                finished.append(seq)
+        return finished
+
+    # ------------------------------------------------------------------ offline API
+    def generate(self, prompts, params=None, decode_text: bool = True) -> list:
+        if not isinstance(params, list):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt")
+        seqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.scheduler.has_work():
+            self.step()
+        outs = []
+        for s in seqs:
+            text = None
+            if decode_text and self.tokenizer is not None:
+                text = self.tokenizer.decode(s.output_ids, skip_special_tokens=True)
+            outs.append(RequestOutput(s.seq_id, s.prompt_len, s.output_ids, text,
+                                      s.first_token_time - s.arrival_time, s.finish_time - s.arrival_time))
+        return outs

@@ -1,0 +1,201 @@
+"""Python faces of the CUDA kernels: each function checks shapes and types, then calls the
+``extern "C"`` launcher of its library on torch's current stream.  Tensors are passed as raw
+device pointers; nothing here computes on the host or through a library kernel, and there is no
+other path: a tensor that is not on a CUDA device is refused.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_TAGS = {torch.float32: F32, torch.bfloat16: BF16}
+
+_CUDA_ERRORS = {-1: "a size or option the kernel does not take", -2: "beyond the kernel's stated maximum"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def tag(t: torch.Tensor) -> int:
+    try:
+        return _TAGS[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {t.dtype}; kernels take float32 and bfloat16") from None
+
+
+def _ptr(t):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernels of this package run on CUDA tensors only; got a tensor on " + str(t.device))
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused, {_CUDA_ERRORS.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _i32(t, name):
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+# --------------------------------------------------------------------------- embedding
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]] as float32 (the residual stream)."""
+    _i32(ids, "ids")
+    V, h = table.shape
+    _need(out.dtype == torch.float32 and out.shape == (ids.numel(), h) and out.is_contiguous(),
+          "embedding output must be contiguous float32 [tokens, hidden]")
+    _need(table.is_contiguous(), "embedding table must be contiguous")
+    lib = build.load("embedding")
+    _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(out), ids.numel(), h, V, _stream()),
+           "embedding")
+    return out
+
+
+# --------------------------------------------------------------------------- norm
+
+def add_rmsnorm(delta, res: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """res += delta (in place, float32); out = rmsnorm(res) * weight.  With ``rows`` the inputs are
+    gathered (output row b from input row rows[b]) and ``res`` is not written."""
+    n = res.shape[-1]
+    _need(res.dtype == torch.float32 and res.is_contiguous(), "the residual stream must be contiguous float32")
+    _need(out.is_contiguous() and out.shape[-1] == n, "norm output must be contiguous [rows, n]")
+    _need(weight.numel() == n and weight.is_contiguous(), f"norm weight must have {n} entries")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.shape == res.shape and delta.is_contiguous(),
+              "delta must match the residual's shape and the output's type")
+    num_rows = out.shape[0]
+    if rows is not None:
+        _i32(rows, "rows")
+        _need(rows.numel() == num_rows, "one gathered row per output row")
+    else:
+        _need(res.shape[0] == num_rows, "output rows must match residual rows")
+    lib = build.load("norm")
+    _check(lib.mie_add_rmsnorm(_ptr(delta), _ptr(res), _ptr(weight), tag(weight), _ptr(out), tag(out),
+                               _ptr(rows), num_rows, n, ctypes.c_float(eps), _stream()), "add_rmsnorm")
+    return out
+
+
+# --------------------------------------------------------------------------- rope + cache write
+
+def rope_tables(inv_freq: torch.Tensor, max_pos: int):
+    """cos, sin [max_pos, rotary_dim/2] float32 of p * inv_freq[j]."""
+    _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous(), "inv_freq must be float32")
+    half = inv_freq.numel()
+    cos = torch.empty(max_pos, half, dtype=torch.float32, device=inv_freq.device)
+    sin = torch.empty_like(cos)
+    lib = build.load("rope_cache")
+    _check(lib.mie_rope_table(_ptr(inv_freq), _ptr(cos), _ptr(sin), max_pos, half, _stream()), "rope_table")
+    return cos, sin
+
+
+def rope_cache_write(qkv: torch.Tensor, positions, slots, cos, sin, k_cache, v_cache, num_heads: int,
+                     num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                     write_cache: bool = True) -> None:
+    """Rotates q in place inside ``qkv`` [T, (H + 2 H_kv) D] and writes rotated k and v into their
+    cache slots (pages laid out [page, kv_head, slot, D])."""
+    T = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim,
+          "qkv must be contiguous [tokens, (H + 2 H_kv) * D]")
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache type must match qkv")
+    _need(cos.shape[1] * 2 == rotary_dim, "rotation table does not match rotary_dim")
+    lib = build.load("rope_cache")
+    _check(lib.mie_rope_cache_write(_ptr(qkv), tag(qkv), _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin),
+                                    _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim,
+                                    rotary_dim, page_size, cos.shape[0], int(write_cache), _stream()),
+           "rope_cache_write")
+
+
+# --------------------------------------------------------------------------- attention
+
+def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
+                    row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                    head_dim: int, page_size: int, scale: float, window: int | None = None) -> torch.Tensor:
+    """Causal attention of every new token over its request's pages (CUDA-core kernel, float32 or
+    bfloat16).  ``q`` holds [H, D] at the start of each token row of ``q_stride`` elements."""
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
+          f"head_dim {head_dim}: this kernel takes multiples of 16 from 16 to 256")
+    _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
+    for t, n in ((block_tables, "block_tables"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"),
+                 (row_ctx_len, "row_ctx_len")):
+        _i32(t, n)
+    _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "q, caches and out must share a type")
+    _need(out.is_contiguous(), "attention output must be contiguous")
+    rows = row_q_len.numel()
+    lib = build.load("attention_simt")
+    _check(lib.mie_paged_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
+                                   _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
+                                   _ptr(row_ctx_len), rows, num_tokens, _ptr(out), tag(q), num_heads,
+                                   num_kv_heads, head_dim, page_size, ctypes.c_float(scale),
+                                   int(window or 0), _stream()), "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- activation
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    T, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype
+          and out.is_contiguous() and gate_up.is_contiguous(), "swiglu shapes/types do not match")
+    lib = build.load("activation")
+    _check(lib.mie_swiglu(_ptr(gate_up), _ptr(out), tag(out), T, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+# --------------------------------------------------------------------------- matrix product (CUDA cores)
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None):
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias), float32 accumulation on CUDA cores."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemm shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm operands must be contiguous")
+    lib = build.load("gemm_simt")
+    _check(lib.mie_gemm_simt(_ptr(x), tag(x), _ptr(w), tag(w), _ptr(bias), tag(bias) if bias is not None else 0,
+                             _ptr(out), tag(out), M, N, K, _stream()),
+           f"gemm_simt ({x.dtype}, {w.dtype} -> {out.dtype})")
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, temperature, request, position, seed: int, out: torch.Tensor):
+    """Token ids [rows] from float32 logits [rows, vocab]; per-row temperature (0 = greedy), request
+    id (int64) and output position (int32) key the noise."""
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be contiguous float32")
+    _need(temperature.dtype == torch.float32 and request.dtype == torch.int64 and position.dtype == torch.int32
+          and out.dtype == torch.int32, "sampling argument types")
+    lib = build.load("sampling")
+    _check(lib.mie_sample(_ptr(logits), _ptr(temperature), _ptr(request), _ptr(position),
+                          ctypes.c_uint64(seed & ((1 << 64) - 1)), _ptr(out), rows, vocab, _stream()), "sample")
+    return out
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

@@ -1,0 +1,117 @@
+"""The generic decoder: a model is what its ``ModelSpec`` says -- an embedding, layers put together
+from registered parts, a run order, a final norm and a head.  Nothing here names an architecture.
+
+``step(ctx)`` is the one step function: it runs exactly the tokens of the batch (prompt portions
+beside single decoded tokens), reading earlier positions from the cache and writing the new
+ones, and returns float32 logits at the wanted positions only
+(the reference's ``LlamaModel.forward``, inference_engine/model.py:161-185, returns every row in a
+pure-decode step; here the wanted positions are always explicit).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.storage import CacheLayout, CacheStorage
+from ..config.model_config import ModelSpec
+from ..parts.base import Runtime, StepContext, build_part, part_class
+from ..weights.loader import TensorSpec, check_and_bind
+
+
+def _layer_parts(layer_spec):
+    mixer = build_part("mixer", layer_spec.mixer)
+    ff = build_part("feed_forward", layer_spec.feed_forward)
+    n1 = build_part("norm", layer_spec.mixer_norm)
+    n2 = build_part("norm", layer_spec.feed_forward_norm)
+    block = part_class("block", layer_spec.block)(mixer, ff, n1, n2)
+    named = [(layer_spec.mixer.prefix, mixer), (layer_spec.feed_forward.prefix, ff),
+             (layer_spec.mixer_norm.prefix, n1), (layer_spec.feed_forward_norm.prefix, n2)]
+    return block, named
+
+
+class _Skeleton:
+    """The parts of a model, built but not yet given weights."""
+
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = build_part("embedding", spec.embedding)
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.head = build_part("head", spec.head)
+        self.blocks = []
+        self.named = [(spec.embedding.prefix, self.embedding), (spec.final_norm.prefix, self.final_norm)]
+        if spec.head.prefix != spec.embedding.prefix:
+            self.named.append((spec.head.prefix, self.head))
+        for ls in spec.layers:
+            block, named = _layer_parts(ls)
+            self.blocks.append(block)
+            self.named.extend(named)
+        for e in spec.run_order:
+            if not (0 <= e.layer < len(self.blocks) and 0 <= e.cache_of < len(self.blocks)):
+                raise ValueError(f"run order names layer {e.layer} / cache of {e.cache_of}; the model has {len(self.blocks)}")
+
+    def expected(self) -> dict[str, TensorSpec]:
+        out: dict[str, TensorSpec] = {}
+        for prefix, part in self.named:
+            for local, ts in part.tensor_specs().items():
+                name = prefix + local
+                if name in out and tuple(out[name].shape) != tuple(ts.shape):
+                    raise ValueError(f"two parts want {name} with different shapes")
+                out[name] = ts
+        return out
+
+
+def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
+    """Every checkpoint tensor the model of ``spec`` reads, by full name."""
+    return _Skeleton(spec).expected()
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, state: dict, rt: Runtime, where: str = "checkpoint",
+                 ignore: tuple = ("*rotary_emb.inv_freq",)):
+        sk = _Skeleton(spec)
+        self.spec = spec
+        self.rt = rt
+        tied = spec.head.prefix == spec.embedding.prefix
+        if tied:
+            ignore = tuple(ignore) + ("lm_head.weight",)
+        tensors = check_and_bind(state, sk.expected(), ignore=ignore, where=where)
+        for prefix, part in sk.named:
+            local = {n: tensors[prefix + n] for n in part.tensor_specs()}
+            part.bind(local, rt)
+        if tied:
+            sk.head.bind({}, rt, shared=sk.embedding.weight)
+        self.embedding, self.final_norm, self.head, self.blocks = sk.embedding, sk.final_norm, sk.head, sk.blocks
+        self.run_order = spec.run_order
+        needs = {i: b.mixer.cache_need() for i, b in enumerate(self.blocks)}
+        self.cache_layout = CacheLayout.from_needs(needs)
+        self.storage: CacheStorage | None = None
+        self._caches: list = []
+
+    # ------------------------------------------------------------------ cache
+    def allocate_cache(self, num_pages, page_size: int, num_state_slots: int) -> CacheStorage:
+        self.storage = CacheStorage(self.cache_layout, num_pages, page_size, num_state_slots, self.rt.dtype,
+                                    self.rt.device)
+        self._caches = [self.storage.layer_cache(e.cache_of, e.writes_cache) for e in self.run_order]
+        return self.storage
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for obj in [self.embedding, self.final_norm, self.head] + [p for b in self.blocks for p in
+                                                                  (b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm)]:
+            for v in vars(obj).values():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    total += v.numel() * v.element_size()
+        return total
+
+    # ------------------------------------------------------------------ the step function
+    def step(self, ctx: StepContext) -> torch.Tensor:
+        if self.storage is None:
+            raise RuntimeError("allocate_cache() must be called before step()")
+        res = self.embedding.forward(ctx)
+        delta = None
+        for entry, cache in zip(self.run_order, self._caches):
+            delta = self.blocks[entry.layer].forward(delta, res, ctx, cache)
+        if ctx.want.numel() == 0:
+            return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.rt.device)
+        x = self.final_norm(delta, res, rows=ctx.want)
+        return self.head.forward(x)
