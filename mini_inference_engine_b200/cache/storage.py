@@ -20,15 +20,16 @@ from .manager import GroupSpec
 
 @dataclass
 class CacheLayout:
-    """Which layers own which kind of storage.  ``kv[layer] = (group index, KVNeed)``,
-    ``state[layer] = StateNeed``; ``groups`` are the page groups in index order."""
+    """Which cache ids (see ``RunEntry.cache``) own which kind of storage.
+    ``kv[cache id] = (group index, KVNeed)``, ``state[cache id] = StateNeed``; ``groups`` are the
+    page groups in index order."""
     groups: list = field(default_factory=list)
     kv: dict = field(default_factory=dict)
     state: dict = field(default_factory=dict)
 
     @classmethod
     def from_needs(cls, needs: dict) -> "CacheLayout":
-        """``needs[layer]`` is what that layer's mixer declared (None, KVNeed or StateNeed)."""
+        """``needs[cache id]`` is what the mixer that uses it declared (None, KVNeed or StateNeed)."""
         lay = cls()
         windows = sorted({n.window for n in needs.values() if isinstance(n, KVNeed)},
                          key=lambda w: (w is not None, w or 0))

@@ -41,10 +41,12 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class RunEntry:
-    """One entry of the run order: run ``layer`` with the cache that belongs to ``cache_of``
-    (its own by default).  ``writes_cache`` is False when the layer only reads that cache."""
+    """One entry of the run order: run ``layer`` (an index into ``layers``; the same layer may be
+    named by several entries, which then share its weights) on cache ``cache`` (an id of the
+    entry's choosing: entries with the same id work on the same keys and values or state).
+    ``writes_cache`` is False when this run only reads what an earlier entry wrote there."""
     layer: int
-    cache_of: int
+    cache: int
     writes_cache: bool = True
 
 

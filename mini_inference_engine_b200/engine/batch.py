@@ -133,7 +133,8 @@ class BatchBuilder:
         layout = dict(off=off, T=T, R=R, W=W, width=width, size=n, real_rows=R_real,
                       extras={k: v[:3] for k, v in extra_off.items()},
                       max_q_len=int(q_len.max()) if R else 0, max_ctx_len=int(ctx_len.max()) if R else 0,
-                      q_len=q_len.tolist(), ctx_len=ctx_len.tolist(), q_start=q_start[:R].tolist())
+                      q_len=q_len.tolist(), ctx_len=ctx_len.tolist(), q_start=q_start[:R].tolist(),
+                      state_slots=[r.state_slot for r in rows] + [0] * (R - R_real))
         return buf, layout
 
     # ------------------------------------------------------------------ to the device
@@ -179,7 +180,7 @@ class BatchBuilder:
             max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"],
             extras={k: dev[o:o + w].view(_TORCH_DTYPES[d]) for k, (o, w, d) in layout.get("extras", {}).items()},
             host=dict(q_len=layout["q_len"], ctx_len=layout["ctx_len"], q_start=layout["q_start"],
-                      real_rows=layout["real_rows"]))
+                      state_slots=layout["state_slots"], real_rows=layout["real_rows"]))
 
     def build(self, rows: list[BatchRow]) -> StepContext:
         buf, layout = self.pack(rows)

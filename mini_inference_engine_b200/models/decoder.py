@@ -45,8 +45,8 @@ class _Skeleton:
             self.blocks.append(block)
             self.named.extend(named)
         for e in spec.run_order:
-            if not (0 <= e.layer < len(self.blocks) and 0 <= e.cache_of < len(self.blocks)):
-                raise ValueError(f"run order names layer {e.layer} / cache of {e.cache_of}; the model has {len(self.blocks)}")
+            if not 0 <= e.layer < len(self.blocks):
+                raise ValueError(f"run order names layer {e.layer}; the model has {len(self.blocks)}")
 
     def expected(self) -> dict[str, TensorSpec]:
         out: dict[str, TensorSpec] = {}
@@ -81,7 +81,18 @@ class DecoderModel:
             sk.head.bind({}, rt, shared=sk.embedding.weight)
         self.embedding, self.final_norm, self.head, self.blocks = sk.embedding, sk.final_norm, sk.head, sk.blocks
         self.run_order = spec.run_order
-        needs = {i: b.mixer.cache_need() for i, b in enumerate(self.blocks)}
+        needs: dict = {}
+        for e in self.run_order:                   # a cache's shape is what the layers that use it declare
+            need = self.blocks[e.layer].mixer.cache_need()
+            if e.cache in needs and needs[e.cache] != need:
+                raise ValueError(f"cache {e.cache} is used by layers with different needs: {needs[e.cache]} and {need}")
+            needs[e.cache] = need
+        first_writer = {}
+        for e in self.run_order:
+            if e.writes_cache:
+                first_writer.setdefault(e.cache, e.layer)
+            elif e.cache not in first_writer:
+                raise ValueError(f"layer {e.layer} reads cache {e.cache} before any entry has written it")
         self.cache_layout = CacheLayout.from_needs(needs)
         self.storage: CacheStorage | None = None
         self._caches: list = []
@@ -90,7 +101,7 @@ class DecoderModel:
     def allocate_cache(self, num_pages, page_size: int, num_state_slots: int) -> CacheStorage:
         self.storage = CacheStorage(self.cache_layout, num_pages, page_size, num_state_slots, self.rt.dtype,
                                     self.rt.device)
-        self._caches = [self.storage.layer_cache(e.cache_of, e.writes_cache) for e in self.run_order]
+        self._caches = [self.storage.layer_cache(e.cache, e.writes_cache) for e in self.run_order]
         return self.storage
 
     def weight_bytes(self) -> int:

@@ -141,3 +141,51 @@ if __name__ == "__main__":
         with open(os.path.join(HERE, name + ".json"), "w") as f:
             json.dump(g, f)
         print(name, "written; reference cut-vs-whole max abs", g["reference_cut_vs_whole_max_abs"])
+
+
+# --------------------------------------------------------------------------- scheduler decisions
+
+SCHED_CASES = {
+    "roomy": dict(prompts=[5, 17, 33, 40, 3], max_tokens=[8, 8, 8, 4, 12], budget=48, num_blocks=64, max_num_seqs=4),
+    "tight_pages": dict(prompts=[30, 30, 30, 30], max_tokens=[40, 40, 40, 40], budget=64, num_blocks=9, max_num_seqs=4),
+    "tiny_budget": dict(prompts=[20, 9, 1, 50], max_tokens=[5, 5, 5, 5], budget=7, num_blocks=32, max_num_seqs=3),
+}
+
+
+def run_reference_scheduler(ref_root: str, case: dict) -> dict:
+    """Drives the reference's Scheduler + BlockAllocator with the bookkeeping of its engine step
+    (inference_engine/engine.py:212-229), a token being appended whenever a portion reaches the end."""
+    sys.path.insert(0, ref_root)
+    from inference_engine.block_manager import BlockAllocator
+    from inference_engine.config import EngineConfig
+    from inference_engine.sampling import SamplingParams
+    from inference_engine.scheduler import Scheduler
+    from inference_engine.sequence import Sequence
+
+    cfg = EngineConfig(max_num_seqs=case["max_num_seqs"], max_num_batched_tokens=case["budget"])
+    alloc = BlockAllocator(case["num_blocks"], 16)
+    sched = Scheduler(cfg, alloc)
+    seqs = [Sequence([1] * p, SamplingParams(max_tokens=m, ignore_eos=True))
+            for p, m in zip(case["prompts"], case["max_tokens"])]
+    for s in seqs:
+        sched.add(s)
+    steps = []
+    while sched.has_work() and len(steps) < 2000:
+        batch = sched.schedule()
+        steps.append([[seqs.index(s), n] for s, n in batch])
+        for s, n in batch:
+            last = s.num_computed + n == s.num_tokens
+            s.num_computed += n
+            if last:
+                s.token_ids.append(7)
+                if s.num_output_tokens >= s.params.max_tokens:
+                    sched.finish(s)
+    return dict(case=case, steps=steps, preemptions=sched.num_preemptions, free_at_end=alloc.num_free)
+
+
+if __name__ == "__main__":
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    out = {name: run_reference_scheduler(ref, case) for name, case in SCHED_CASES.items()}
+    with open(os.path.join(HERE, "scheduler.json"), "w") as f:
+        json.dump(out, f)
+    print("scheduler:", {k: (len(v["steps"]), v["preemptions"]) for k, v in out.items()})

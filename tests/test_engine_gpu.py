@@ -1,0 +1,170 @@
+"""Generation through the Python entry point against the plain implementation: greedy and seeded
+temperature sampling, the four ways of exercising the engine that the reference's own test uses
+(default; a tiny token budget, so prompts go in several portions; no captured graphs; a tiny cache,
+with preemptions asserted -- tests/test_correctness.py:41-47 of the reference), long decoding, stop
+rules and refusals."""
+import random
+
+import pytest
+import torch
+
+import plain_llama as pl
+from conftest import TINY, plain_weights
+from helpers import TOL
+
+pytestmark = pytest.mark.gpu
+DTYPES = {"float32": (torch.float32, pl.identity), "bfloat16": (torch.bfloat16, pl.round_bf16)}
+
+
+def engine_for(folder, dtype, **overrides):
+    from mini_inference_engine_b200 import EngineConfig, LLMEngine
+    return LLMEngine(folder, EngineConfig(**overrides), dtype=dtype, load_tokenizer=False, verbose=False)
+
+
+def assert_tokens_follow_plain(cfg, W, rnd, prompt, out_ids, dtype, temperature=0.0, seed=0, request=0):
+    """Every generated token must be the plain implementation's choice given the same prefix, or
+    tie with it within the logits tolerance (the reference accepts ties of 2 bfloat16 ULPs,
+    tests/test_correctness.py:95 of the reference).  After a tie the engine's own prefix is followed."""
+    ids = list(prompt)
+    for n, tok in enumerate(out_ids):
+        logits = pl.forward(cfg, W, ids, rnd)[-1]
+        if temperature > 0:
+            scores = pl.sample_scores(logits, temperature, seed, request, n)
+            slack = TOL[dtype] * logits.abs().max().item() / temperature
+        else:
+            scores = logits
+            slack = TOL[dtype] * logits.abs().max().item()
+        assert scores[tok] >= scores.max() - slack, (
+            f"output {n}: engine chose {tok} (score {scores[tok]:.5f}), plain top {int(scores.argmax())} "
+            f"({scores.max():.5f}), slack {slack:.2e}")
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(dtype_name, model_folders):
+    dtype, rnd = DTYPES[dtype_name]
+    folder = model_folders["tiny_a"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(0)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (5, 17, 33)]
+    from mini_inference_engine_b200 import SamplingParams
+    eng = engine_for(folder, dtype)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    assert [o.prompt_len for o in outs] == [5, 17, 33] and all(len(o.output_ids) == 8 for o in outs)
+    assert all(o.ttft is not None and o.latency >= o.ttft for o in outs)
+    for p, o in zip(prompts, outs):
+        assert_tokens_follow_plain(cfg, W, rnd, p, o.output_ids, dtype)
+    if dtype_name == "float32":                       # float32 has no near ties on random weights
+        assert [o.output_ids for o in outs] == [pl.generate(cfg, W, p, 8) for p in prompts]
+    assert eng.num_graph_steps > 0 and eng.cache.num_free() == eng.cache.pools[0].num_usable
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_seeded_temperature_sampling_tiny_b_in_portions_of_7(dtype_name, model_folders):
+    dtype, rnd = DTYPES[dtype_name]
+    folder = model_folders["tiny_b"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(1)
+    prompts = [[rng.randrange(384) for _ in range(rng.randint(1, 60))] for _ in range(5)]
+    from mini_inference_engine_b200 import SamplingParams
+    sp = SamplingParams(max_tokens=12, temperature=0.8, ignore_eos=True)
+    eng = engine_for(folder, dtype, max_num_batched_tokens=7, seed=99)
+    outs = eng.generate(prompts, sp)
+    for p, o in zip(prompts, outs):
+        assert_tokens_follow_plain(cfg, W, rnd, p, o.output_ids, dtype, 0.8, 99, o.seq_id)
+    # a request's tokens do not depend on batching: the same seed and request ids, one by one, no graphs
+    if dtype_name == "float32":
+        from mini_inference_engine_b200.engine import sequence
+        eng2 = engine_for(folder, dtype, use_cuda_graphs=False, seed=99)
+        again = []
+        for p, o in zip(prompts, outs):
+            sequence._ids = iter([o.seq_id])          # the same request id keys the same noise
+            again.append(eng2.generate([p], sp)[0].output_ids)
+        import itertools
+        sequence._ids = itertools.count(10 ** 6)
+        assert again == [o.output_ids for o in outs]
+
+
+def test_four_ways_of_running_give_the_same_tokens(model_folders):
+    folder = model_folders["tiny_b"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(2)
+    prompts = [[rng.randrange(384) for _ in range(n)] for n in (40, 3, 75, 18, 64, 31)]
+    want = [pl.generate(cfg, W, p, 20) for p in prompts]
+    from mini_inference_engine_b200 import SamplingParams
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    ways = {"default": {}, "budget 9": dict(max_num_batched_tokens=9), "no graphs": dict(use_cuda_graphs=False),
+            "tiny cache": dict(num_blocks=12), "no chunking": dict(enable_chunked_prefill=False, max_num_batched_tokens=80)}
+    for name, ov in ways.items():
+        eng = engine_for(folder, torch.float32, **ov)
+        got = [o.output_ids for o in eng.generate(prompts, sp)]
+        assert got == want, f"{name}: tokens differ from the plain implementation"
+        if name == "tiny cache":
+            assert eng.scheduler.num_preemptions > 0, "the tiny cache was meant to force preemptions"
+        if name == "budget 9":
+            assert eng.num_steps > 30
+        eng.cache.check()
+        assert eng.cache.num_free() == eng.cache.pools[0].num_usable
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_long_decoding_to_the_position_limit(dtype_name, model_folders):
+    dtype, rnd = DTYPES[dtype_name]
+    folder = model_folders["tiny_b"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    from mini_inference_engine_b200 import SamplingParams
+    eng = engine_for(folder, dtype, max_model_len=256)
+    out = eng.generate([[7, 8, 9]], SamplingParams(max_tokens=1000, ignore_eos=True))[0]
+    assert len(out.output_ids) == 253                 # stops at max_model_len = max_position_embeddings
+    assert_tokens_follow_plain(cfg, W, rnd, [7, 8, 9], out.output_ids, dtype)
+
+
+def test_eos_stops_and_is_kept(model_folders, tmp_path):
+    import json
+    import os
+    import shutil
+    folder = model_folders["tiny_a"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    prompt = [3, 1, 4, 1, 5]
+    plain = pl.generate(cfg, W, prompt, 10)
+    eos = plain[4]
+    d = str(tmp_path / "m")
+    shutil.copytree(folder, d)
+    with open(os.path.join(d, "config.json")) as f:
+        c = json.load(f)
+    c["eos_token_id"] = eos
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(c, f)
+    from mini_inference_engine_b200 import SamplingParams
+    eng = engine_for(d, torch.float32)
+    stop = plain.index(eos) + 1
+    assert eng.generate([prompt], SamplingParams(max_tokens=10))[0].output_ids == plain[:stop]
+    assert eng.generate([prompt], SamplingParams(max_tokens=10, ignore_eos=True))[0].output_ids == plain
+
+
+def test_refusals(model_folders):
+    from mini_inference_engine_b200 import SamplingParams
+    eng = engine_for(model_folders["tiny_a"], torch.float32, num_blocks=4, use_cuda_graphs=False)
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request([1, 256])
+    with pytest.raises(ValueError, match="max_model_len"):
+        eng.add_request([1] * 129)
+    with pytest.raises(ValueError, match="never fit"):
+        eng.add_request([1] * 40, SamplingParams(max_tokens=30))     # 3 usable pages, watermark 1: 32 positions
+    with pytest.raises(ValueError, match="empty"):
+        eng.add_request([])
+    with pytest.raises(ValueError, match="tokenizer"):
+        eng.add_request("text")
+    assert eng.generate([[1] * 20], SamplingParams(max_tokens=12))[0].prompt_len == 20
+
+
+def test_step_api_and_counters(model_folders):
+    from mini_inference_engine_b200 import SamplingParams
+    eng = engine_for(model_folders["tiny_a"], torch.bfloat16)
+    a = eng.add_request([1, 2, 3], SamplingParams(max_tokens=2, ignore_eos=True))
+    b = eng.add_request([4] * 20, SamplingParams(max_tokens=3, ignore_eos=True))
+    finished = []
+    while eng.scheduler.has_work():
+        finished += eng.step()
+    assert finished == [a, b] and a.num_output_tokens == 2 and b.num_output_tokens == 3
+    assert eng.num_steps == 3 and eng.h2d_bytes > 0 and eng.d2h_bytes == 4 * 5

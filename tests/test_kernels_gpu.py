@@ -1,0 +1,273 @@
+"""Each CUDA kernel alone against the plain float32 formulas, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import close, scattered_tables
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_inference_engine_b200.kernels import ops
+    return ops
+
+
+@pytest.mark.parametrize("tdt", DTYPES)
+def test_embedding(ops, tdt):
+    torch.manual_seed(0)
+    table = torch.randn(301, 100).to(tdt).to(DEV)
+    ids = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 100, device=DEV)
+    ops.embedding(table, ids, out)
+    assert torch.equal(out.cpu(), pl.embedding(table.cpu(), ids.cpu()))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows,n", [(1, 96), (7, 2048), (256, 896), (3, 11000), (5, 1)])
+def test_add_rmsnorm(ops, dt, rows, n):
+    torch.manual_seed(rows + n)
+    delta = torch.randn(rows, n).to(dt).to(DEV)
+    res = torch.randn(rows, n, device=DEV) * 3
+    w = (1 + 0.1 * torch.randn(n)).to(dt).to(DEV)
+    want_res = res.cpu() + delta.float().cpu()
+    want = pl.rmsnorm(want_res, w.cpu(), 1e-5)
+    out = torch.empty(rows, n, dtype=dt, device=DEV)
+    res2 = res.clone()
+    ops.add_rmsnorm(delta, res2, w, 1e-5, out)
+    assert torch.equal(res2.cpu(), want_res)              # the residual sum is exact float32
+    close(out, want, dt, "norm")
+    # no delta (first layer): residual untouched
+    res3 = res.clone()
+    ops.add_rmsnorm(None, res3, w, 1e-5, out)
+    assert torch.equal(res3, res)
+    close(out, pl.rmsnorm(res.cpu(), w.cpu(), 1e-5), dt, "norm without delta")
+    # float32 weight beside bfloat16 activations stays float32
+    ops.add_rmsnorm(delta, res.clone(), w.float(), 1e-5, out)
+    close(out, want, dt, "norm with float32 weight")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_add_rmsnorm_gathers_rows_and_leaves_the_residual(ops, dt):
+    torch.manual_seed(3)
+    delta = torch.randn(9, 200).to(dt).to(DEV)
+    res = torch.randn(9, 200, device=DEV)
+    w = torch.randn(200).to(dt).to(DEV)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, 200, dtype=dt, device=DEV)
+    before = res.clone()
+    ops.add_rmsnorm(delta, res, w, 1e-6, out, rows)
+    assert torch.equal(res, before)
+    want = pl.rmsnorm((before.cpu() + delta.float().cpu())[rows.cpu().long()], w.cpu(), 1e-6)
+    close(out, want, dt, "gathered norm")
+
+
+@pytest.mark.parametrize("theta,rot,max_pos", [(10000.0, 16, 128), (500000.0, 48, 5000), (1e6, 128, 3000)])
+def test_rope_tables(ops, theta, rot, max_pos):
+    j = torch.arange(0, rot, 2, dtype=torch.int64).float()
+    inv = 1.0 / (theta ** (j / rot))
+    cos, sin = ops.rope_tables(inv.to(DEV), max_pos)
+    ang = pl.rope_angles(torch.arange(max_pos), rot, theta)
+    # angles reach thousands of radians: float32 sin/cos of the same float32 angle
+    assert (cos.cpu() - ang.cos()).abs().max() < 2e-6 and (sin.cpu() - ang.sin()).abs().max() < 2e-6
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,Hkv,D,rot,page", [(4, 2, 16, 16, 16), (3, 1, 48, 48, 32), (8, 8, 128, 64, 16), (5, 5, 32, 0, 64)])
+def test_rope_and_cache_write(ops, dt, H, Hkv, D, rot, page):
+    torch.manual_seed(H * D)
+    T, theta, max_pos, num_pages = 11, 10000.0, 512, 12
+    qkv = torch.randn(T, (H + 2 * Hkv) * D).to(dt)
+    positions = torch.tensor([0, 1, 2, 15, 16, 17, 100, 333, 31, 32, 511], dtype=torch.int32)
+    slots = torch.randperm((num_pages - 1) * page)[:T].to(torch.int32) + page       # never the scratch page
+    if rot:
+        j = torch.arange(0, rot, 2, dtype=torch.int64).float()
+        cos, sin = ops.rope_tables((1.0 / (theta ** (j / rot))).to(DEV), max_pos)
+    else:
+        cos = sin = torch.zeros(max_pos, 0, device=DEV)
+    k_cache = torch.full((num_pages, Hkv, page, D), 7.0, dtype=dt, device=DEV)
+    v_cache = torch.full_like(k_cache, 7.0)
+    dev_qkv = qkv.to(DEV)
+    ops.rope_cache_write(dev_qkv, positions.to(DEV), slots.to(DEV), cos, sin, k_cache, v_cache, H, Hkv, D, rot, page)
+    q, k, v = qkv.float().split([H * D, Hkv * D, Hkv * D], -1)
+    q, k, v = q.view(T, H, D), k.view(T, Hkv, D), v.view(T, Hkv, D)
+
+    def rotate(x):
+        if not rot:
+            return x
+        ang = pl.rope_angles(positions, rot, theta)
+        return torch.cat((pl.apply_rope(x[..., :rot], ang), x[..., rot:]), -1)
+
+    close(dev_qkv[:, :H * D].reshape(T, H, D), rotate(q), dt, "rotated q")
+    assert torch.equal(dev_qkv[:, H * D:].cpu(), qkv[:, H * D:])          # k, v in the activation are untouched
+    kc, vc = k_cache.cpu().float(), v_cache.cpu().float()
+    want_k = rotate(k)
+    for t in range(T):
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        close(kc[pg, :, off], want_k[t], dt, f"cached k of token {t}")
+        assert torch.equal(vc[pg, :, off], v[t].to(dt).float())
+    untouched = torch.ones(num_pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert (kc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()   # nothing else was written
+
+
+def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None):
+    """rows: list of (q_len, ctx_len).  Builds random q/k/v per request, scatters k/v into pages, runs
+    the kernel and the plain attention on each request's whole sequence."""
+    torch.manual_seed(seed)
+    num_pages = sum(math.ceil(c / page) for _, c in rows) + 3
+    tables = scattered_tables([c for _, c in rows], page, num_pages, seed)
+    width = max(len(t) for t in tables) + 1
+    k_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)        # stale junk everywhere, finite
+    v_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)
+    q_all, want = [], []
+    scale = 1.0 / math.sqrt(D)
+    for r, (ql, cl) in enumerate(rows):
+        q = torch.randn(cl, H, D).to(dt)
+        k = torch.randn(cl, Hkv, D).to(dt)
+        v = torch.randn(cl, Hkv, D).to(dt)
+        if boost is not None:                                         # one far key must dominate the last query
+            key = boost if boost < cl else 0
+            k[key] *= 0
+            k[key, :, 0] = 30.0
+            q[-1] *= 0
+            q[-1, :, 0] = 30.0
+            v[key] = 5.0
+        for p in range(cl):
+            k_cache[tables[r][p // page], :, p % page] = k[p]
+            v_cache[tables[r][p // page], :, p % page] = v[p]
+        q_all.append(q[cl - ql:])
+        want.append(pl.causal_attention(q.float(), k.float(), v.float(), scale, window)[cl - ql:])
+    q_all = torch.cat(q_all, 0)
+    T = q_all.shape[0]
+    bt = torch.zeros(len(rows), width, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t)
+        bt[r, len(t):] = 0
+    q_len = torch.tensor([a for a, _ in rows], dtype=torch.int32)
+    ctx_len = torch.tensor([c for _, c in rows], dtype=torch.int32)
+    q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+    out = torch.empty(T, H, D, dtype=dt, device=DEV)
+    ops.paged_attention(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV), q_start.to(DEV),
+                        q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window)
+    return out, torch.cat(want, 0)
+
+
+RAGGED = [[(1, 1)], [(1, 17)], [(1, 1000)], [(1, 2048)],
+          [(1, 5), (1, 300), (1, 1), (1, 2047), (1, 64), (1, 65)],            # decode rows, the reference's ragged case
+          [(5, 5), (17, 17), (33, 33)],                                       # whole prompts
+          [(7, 40), (2, 18), (1, 129), (16, 16), (31, 300)],                  # continued portions beside decodes
+          [(300, 300)]]
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("rows", RAGGED)
+def test_paged_attention_ragged(ops, dt, rows):
+    out, want = _paged_case(ops, dt, 32, 4, 64, 16, rows)
+    close(out, want, dt, f"attention rows {rows}")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 6, 48, 32), (16, 1, 128, 64),
+                                          (2, 1, 256, 16), (12, 4, 80, 128), (40, 2, 16, 16)])
+def test_paged_attention_head_shapes(ops, dt, H, Hkv, D, page):
+    out, want = _paged_case(ops, dt, H, Hkv, D, page, [(1, 70), (9, 41), (35, 35), (2, 2)], seed=H + D)
+    close(out, want, dt, f"attention H{H} Hkv{Hkv} D{D} page{page}")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 100])
+def test_paged_attention_window_edges(ops, dt, window):
+    out, want = _paged_case(ops, dt, 4, 2, 32, 16, [(1, 90), (20, 60), (50, 50), (1, 3)], window=window, seed=window)
+    close(out, want, dt, f"attention window {window}")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("far", [0, 15, 16, 511, 777])
+def test_paged_attention_one_far_key_among_hundreds(ops, dt, far):
+    """The last query's score for key `far` stands out: the output must be that key's value, so a
+    kernel that skips or misplaces one key (a page edge, a tile edge) cannot hide behind the average."""
+    out, want = _paged_case(ops, dt, 8, 2, 64, 16, [(1, 800), (3, 800)], boost=far, seed=far)
+    assert (want[0] - 5.0).abs().max() < 1e-3
+    close(out, want, dt, f"far key {far}")
+
+
+def test_paged_attention_refuses_head_sizes_it_does_not_take(ops):
+    from mini_inference_engine_b200.kernels.ops import KernelError
+    z = torch.zeros(1, 1, 24, device=DEV)
+    i = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="head_dim"):
+        ops.paged_attention(z, 24, z, z, i, i[0], i[0], i[0], 1, z.clone(), 1, 1, 24, 16, 1.0)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_swiglu(ops, dt):
+    torch.manual_seed(1)
+    gu = (torch.randn(13, 2 * 176) * 3).to(dt).to(DEV)
+    out = torch.empty(13, 176, dtype=dt, device=DEV)
+    ops.swiglu(gu, out)
+    close(out, pl.swiglu(gu.cpu()[:, :176], gu.cpu()[:, 176:]), dt, "swiglu")
+
+
+@pytest.mark.parametrize("types", [(torch.float32, torch.float32, torch.float32),
+                                   (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                   (torch.bfloat16, torch.bfloat16, torch.float32),
+                                   (torch.bfloat16, torch.float32, torch.bfloat16),
+                                   (torch.bfloat16, torch.float32, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 384, 176), (8, 2048, 96), (17, 100, 2048), (70, 130, 50),
+                                   (200, 256, 64), (300, 384, 176), (260, 129, 33)])
+def test_gemm_simt(ops, types, M, N, K):
+    xt, wt, yt = types
+    torch.manual_seed(M * N + K)
+    x = torch.randn(M, K).to(xt).to(DEV)
+    w = torch.randn(N, K).to(wt).to(DEV)
+    b = torch.randn(N).to(wt).to(DEV)
+    y = torch.empty(M, N, dtype=yt, device=DEV)
+    want = (x.double().cpu() @ w.double().cpu().t())
+    ops.gemm_simt(x, w, y)
+    close(y, want.float(), yt, "gemm")
+    if yt == torch.float32:                                 # float32 result: float32 accuracy whatever the inputs
+        assert (y.cpu().double() - want).abs().max() <= 1e-5 * max(1.0, want.abs().max())
+    ops.gemm_simt(x, w, y, b)
+    close(y, (want + b.double().cpu()).float(), yt, "gemm + bias")
+
+
+def test_sampling_greedy_and_ties(ops):
+    lg = torch.zeros(3, 1000, device=DEV)
+    lg[0, 999] = 1.0
+    lg[1, [17, 500]] = 2.0                                  # a tie: the lowest index wins
+    lg[2] = -torch.arange(1000.0)
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    z = torch.zeros(3, device=DEV)
+    ops.sample(lg, z, torch.zeros(3, dtype=torch.int64, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV), 0, out)
+    assert out.tolist() == [999, 17, 0]
+
+
+@pytest.mark.parametrize("vocab", [384, 5000, 32000])
+def test_sampling_temperature_matches_plain(ops, vocab):
+    torch.manual_seed(vocab)
+    rows = 6
+    lg = torch.randn(rows, vocab) * 2
+    temps = torch.tensor([0.8, 0.0, 1.5, 0.8, 0.1, 1.0])
+    req = torch.tensor([3, 3, 2 ** 40 + 5, 4, 0, 77], dtype=torch.int64)
+    pos = torch.tensor([0, 1, 2, 0, 9, 5], dtype=torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(lg.to(DEV), temps.to(DEV), req.to(DEV), pos.to(DEV), 1234, out)
+    for r in range(rows):
+        tok = int(out[r])
+        if temps[r] == 0:
+            assert tok == int(lg[r].argmax())
+            continue
+        scores = pl.sample_scores(lg[r], float(temps[r]), 1234, int(req[r]), int(pos[r]))
+        # the kernel's token is the plain argmax, or ties with it within float32 rounding of log()
+        assert scores[tok] >= scores.max() - 1e-4 * max(1.0, scores.abs().max())
+    # the same request and position give the same token in another batch order
+    out2 = torch.empty(rows, dtype=torch.int32, device=DEV)
+    perm = torch.tensor([5, 4, 3, 2, 1, 0])
+    ops.sample(lg[perm].to(DEV), temps[perm].to(DEV), req[perm].to(DEV), pos[perm].to(DEV), 1234, out2)
+    assert out2.cpu()[perm.argsort()].tolist() == out.tolist()
