@@ -1,0 +1,242 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, random weights, synthetic tokens.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 512] [--layers L]
+    python bench.py --impl reference
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch and context, timed
+on the device with CUDA events around K back-to-back launches of the captured decode step (model +
+sampling) on the live batch; ``e2e`` is the same batch driven through ``LLMEngine.step()``: every
+step packs the batch on the host, copies it from pinned memory, launches, and reads the sampled
+tokens back.  ``prefill`` is one 2,048-token prompt through the entry point's step, ``points`` are
+decode at batch 1 and 64, ``roofline`` relates the decode step to the bytes it must read.
+Between timed iterations nothing is flushed: one step reads all weights (over 2 GB), far more than
+the 126 MB L2 holds.
+"""
+import argparse
+import json
+import os
+import shutil
+import statistics
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_DECODE_TOK_S = {1: 104.0, 8: 798.0, 32: 2680.0, 64: 3646.0}   # the reference's README, RTX 5070 Laptop
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            m = json.load(f)
+        return dict(hbm_gbs=float(m["hbm_gbs"]), tflops=float(m.get("bf16_tflops_sustained") or m["bf16_tflops"]),
+                    tflops_burst=float(m["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_burst=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs (reads only)."""
+
+    def __init__(self):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self._thread = None
+
+    def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {getattr(pynvml, n): n[len("nvmlClocksThrottleReason"):] for n in dir(pynvml)
+                     if n.startswith("nvmlClocksThrottleReason") and n not in
+                     ("nvmlClocksThrottleReasonNone", "nvmlClocksThrottleReasonAll", "nvmlClocksThrottleReasonGpuIdle")}
+
+            def run():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                        r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                        self.reasons.update(n for bit, n in names.items() if bit and r & bit)
+                    except Exception:      # noqa: BLE001 - sampling must never end the run
+                        pass
+                    time.sleep(0.05)
+
+            self._thread = threading.Thread(target=run, daemon=True)
+            self._thread.start()
+        except Exception:                  # noqa: BLE001
+            pass
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def prompts_for(batch, length, vocab):
+    return [[1] + [(1000 + i * 7 + j) % vocab for j in range(length - 1)] for i in range(batch)]
+
+
+def decode_point(eng, batch, context, steps, warmup, e2e=False):
+    """Device time per decode step at (batch, context) and, if asked, the end-to-end step time."""
+    import torch
+
+    from mini_inference_engine_b200 import SamplingParams
+    from mini_inference_engine_b200.kernels import ops
+    for p in prompts_for(batch, context, eng.vocab_size):
+        eng.add_request(p, SamplingParams(max_tokens=2 * (steps + warmup) + 8, ignore_eos=True))
+    while any(s.num_new_tokens > 1 for s in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(warmup):
+        eng.step()
+    bucket = next(s for s in eng.graph_sizes if s >= batch)
+    g = eng.graphs[bucket]
+    out = {}
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        g.graph.replay()                     # the captured step on the live batch: model + sampling
+    end.record()
+    torch.cuda.synchronize()
+    out["device_ms"] = start.elapsed_time(end) / steps
+    out["launches_per_step"] = g.kernels
+    if e2e:
+        h0, d0 = eng.h2d_bytes, eng.d2h_bytes
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            eng.step()
+        torch.cuda.synchronize()
+        out["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / steps
+        out["h2d"] = (eng.h2d_bytes - h0) // steps
+        out["d2h"] = (eng.d2h_bytes - d0) // steps
+    for s in list(eng.scheduler.running):
+        eng.scheduler.finish(s)
+    return out
+
+
+def prefill_point(eng, tokens, steps, warmup):
+    import torch
+
+    from mini_inference_engine_b200 import SamplingParams
+    times = []
+    for i in range(warmup + steps):
+        eng.add_request(prompts_for(1, tokens, eng.vocab_size)[0], SamplingParams(max_tokens=1, ignore_eos=True))
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        eng.step()
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+        assert not eng.scheduler.has_work()
+    return statistics.median(times)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=512)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--preset", default="tinyllama-1.1b")
+    ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference has no setup.py or pyproject.toml, so pip cannot install it offline into "
+                          "baseline/_ref (pip: 'Directory is not installable')"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    import dataclasses
+
+    import torch
+
+    from mini_inference_engine_b200 import EngineConfig, LLMEngine
+    from mini_inference_engine_b200.config import load_preset
+    from mini_inference_engine_b200.kernels import ops
+    from mini_inference_engine_b200.weights import write_model_folder
+
+    cfg = load_preset(args.preset)
+    full_layers = cfg.num_hidden_layers
+    if args.layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    folder = tempfile.mkdtemp(prefix="mie_b200_bench_")
+    try:
+        write_model_folder(folder, cfg, seed=0)
+        point_batches = [int(b) for b in args.points.split(",") if b]
+        max_seqs = max([args.batch] + point_batches)
+        eng = LLMEngine(folder, EngineConfig(max_num_seqs=max_seqs, max_num_batched_tokens=max(2048, args.prefill_tokens),
+                                             max_model_len=cfg.max_position_embeddings,
+                                             cuda_graph_batch_sizes=tuple(sorted({args.batch, *point_batches}))),
+                        dtype=torch.bfloat16, load_tokenizer=False, verbose=False)
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+    pk = peaks()
+    launches0 = ops.launches
+    with ClockSampler() as clocks:
+        main_pt = decode_point(eng, args.batch, args.context, steps, warmup, e2e=True)
+    points = {}
+    for b in point_batches:
+        pt = decode_point(eng, b, args.context, max(10, steps // 2), warmup)
+        points[f"decode_b{b}"] = round(b / pt["device_ms"] * 1e3, 1)
+    pre_ms = prefill_point(eng, args.prefill_tokens, max(3, min(10, steps // 10)), 3)
+
+    L, h, I, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    layer_params = (H + 2 * Hkv) * D * h + h * H * D + 3 * I * h
+    weight_bytes = 2 * (L * (layer_params + 2 * h) + h + V * h)                 # every matrix once, norms, head
+    kv_bytes = args.batch * (args.context + warmup) * 2 * L * Hkv * D * 2       # the live requests' cache
+    step_bytes = weight_bytes + kv_bytes + args.batch * h * 2
+    achieved = step_bytes / (main_pt["device_ms"] * 1e-3) / 1e9
+    T = args.prefill_tokens
+    flops = 2 * T * L * layer_params + 2 * V * h + L * 4 * H * D * T * (T + 1) // 2
+    value = args.batch / main_pt["device_ms"] * 1e3
+    base = BASELINE_DECODE_TOK_S.get(args.batch)
+    line = {
+        "metric": "decode tok/s", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(main_pt["device_ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / base, 2) if base else None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": args.preset, "layers": L, "layers_full": full_layers, "hidden": h, "heads": H, "kv_heads": Hkv,
+                   "head_dim": D, "intermediate": I, "vocab": V, "global_batch": args.batch, "seq_len": args.context,
+                   "prefill_tokens": T, "page_size": eng.cfg.block_size, "weights": "random N(0,0.02) seed 0",
+                   "parallelism": "single_gpu", "l2": "inputs larger than L2 (weights 2 GB per step), no flush",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(args.batch / main_pt["e2e_ms"] * 1e3, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": main_pt["h2d"], "d2h_bytes_per_step": main_pt["d2h"]},
+        "gpu_launches": main_pt["launches_per_step"] * steps,
+        "prefill": {"value": round(T / pre_ms * 1e3, 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms * 1e-3) / (pk["tflops_burst"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(),
+        "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -36,3 +36,21 @@ def load_config(path_or_dict):
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
+
+
+def preset_names() -> list[str]:
+    import os
+    d = os.path.join(os.path.dirname(__file__), "presets")
+    return sorted(f[:-5] for f in os.listdir(d) if f.endswith(".json"))
+
+
+def load_preset(name: str):
+    """A named config.json shipped with the package (the shapes the benchmarks quote), for the
+    random-weights mode.  These are data files, read like any config.json."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(__file__), "presets", name + ".json")
+    if not os.path.isfile(path):
+        raise ConfigError(f"no preset {name!r}; available: {', '.join(preset_names())}")
+    with open(path) as f:
+        return load_config(json.load(f))

@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from ..config import EngineConfig, load_config
+from ..kernels import ops
 from ..models.decoder import DecoderModel
 from ..parts.base import Runtime
 from ..sampling.params import SamplingParams
@@ -40,8 +41,9 @@ class RequestOutput:
 
 
 class _DecodeGraph:
-    def __init__(self, graph, layout, buffer, tokens):
+    def __init__(self, graph, layout, buffer, tokens, kernels):
         self.graph, self.layout, self.buffer, self.tokens = graph, layout, buffer, tokens
+        self.kernels = kernels        # kernels of this package inside the captured step
 
 
 def _nvtx_range(name):
@@ -149,10 +151,11 @@ class LLMEngine:
             self._forward_and_sample(ctx, tokens)                   # warm-up: builds kernels, sizes buffers
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            before = ops.launches
             with torch.cuda.graph(g, pool=pool):
                 self._forward_and_sample(ctx, tokens)
             pool = g.pool()
-            self.graphs[bs] = _DecodeGraph(g, layout, static, tokens)
+            self.graphs[bs] = _DecodeGraph(g, layout, static, tokens, ops.launches - before)
         torch.cuda.synchronize()
         self.graph_sizes = sizes
         if self.verbose:

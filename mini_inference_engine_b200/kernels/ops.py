@@ -41,8 +41,13 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launches = 0        # kernels of this package launched so far (captured launches count once, at capture)
+
+
 def _check(code: int, what: str) -> None:
+    global launches
     if code == 0:
+        launches += 1
         return
     if code < 0:
         raise KernelError(f"{what}: refused, {_CUDA_ERRORS.get(code, code)}")
