@@ -51,7 +51,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
                        const int* __restrict__ row_q_len, const int* __restrict__ row_ctx_len,
                        int num_rows, T* __restrict__ out, int num_heads, int num_kv_heads,
                        int head_dim, int page_size, int page_shift, float scale, int window,
-                       int QT, int HG) {
+                       int QT, int HG, int min_q_len) {
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_row, s_q0;
     const int D = head_dim, DP = head_dim + 4;
@@ -63,7 +63,8 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     if (threadIdx.x == 0) {
         int tile = blockIdx.x, r = 0;
         for (; r < num_rows; ++r) {
-            const int tiles = (row_q_len[r] + QT - 1) / QT;
+            const int ql = row_q_len[r];
+            const int tiles = ql >= min_q_len ? (ql + QT - 1) / QT : 0;   // shorter rows belong to another kernel
             if (tile < tiles) break;
             tile -= tiles;
         }
@@ -169,13 +170,14 @@ static size_t att_smem_bytes(int head_dim) {
     return sizeof(float) * ((size_t)ATT_WARPS * head_dim + 2 * (size_t)ATT_KEYS * (head_dim + 4));
 }
 
+// Rows with fewer than `min_q_len` new tokens are skipped (another kernel serves them).
 // q: [num_tokens, ...] with `q_stride` elements between tokens and heads packed [H, D] at the row
 // start; out: [num_tokens, H, D] contiguous; caches: [pages, H_kv, page_size, D].
 extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                    const int* block_tables, int table_stride, const int* row_q_start,
                                    const int* row_q_len, const int* row_ctx_len, int num_rows,
                                    int num_tokens, void* out, int act_tag, int num_heads, int num_kv_heads,
-                                   int head_dim, int page_size, float scale, int window,
+                                   int head_dim, int page_size, float scale, int window, int min_q_len,
                                    cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (head_dim < 16 || head_dim > ATT_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
@@ -196,14 +198,14 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
         paged_attention_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG);
+            page_size, page_shift, scale, window, QT, HG, min_q_len);
     } else if (act_tag == MIE_BF16) {
         e = cudaFuncSetAttribute(paged_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         paged_attention_kernel<bf16><<<grid, ATT_WARPS * 32, smem, stream>>>(
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (bf16*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG);
+            page_size, page_shift, scale, window, QT, HG, min_q_len);
     } else {
         return MIE_ERR_BAD_ARG;
     }

@@ -1,6 +1,13 @@
-"""Chooses the attention kernel for a step.  The CUDA-core kernel serves every case in both
-types; tensor-core kernels for bfloat16 take over the cases they are written for."""
+"""Chooses the attention kernels for a step.
+
+float32 (the true 32-bit path): the CUDA-core kernel serves every row.
+bfloat16: rows with one new token go to the tensor-core decode kernel (context split across
+blocks), rows with more go to the prefill kernel; head sizes beyond those kernels fall back to the
+CUDA-core kernel, which takes every size up to 256.  ``set_backend("simt")`` forces the CUDA-core
+kernel everywhere (used by tests to compare the two)."""
 from __future__ import annotations
+
+import torch
 
 from . import ops
 
@@ -16,6 +23,19 @@ def set_backend(name: str) -> None:
 
 def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window):
     q_stride = (num_heads + 2 * num_kv_heads) * head_dim
-    return ops.paged_attention(qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start,
-                               ctx.row_q_len, ctx.row_ctx_len, ctx.num_tokens, out, num_heads, num_kv_heads,
-                               head_dim, cache.page_size, scale, window)
+    args = (qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start, ctx.row_q_len,
+            ctx.row_ctx_len)
+    fast = _backend == "auto" and qkv.dtype == torch.bfloat16 and head_dim <= 128
+    if not fast:
+        return ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size,
+                                   scale, window)
+    q_lens = ctx.host.get("q_len")
+    has_decode = q_lens is None or any(n == 1 for n in q_lens)
+    has_prefill = q_lens is None or any(n > 1 for n in q_lens)
+    if has_decode:
+        ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
+                             max_ctx=ctx.max_ctx_len)
+    if has_prefill:
+        ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale,
+                            window, min_q_len=2)
+    return out

@@ -139,9 +139,11 @@ def rope_cache_write(qkv: torch.Tensor, positions, slots, cos, sin, k_cache, v_c
 
 def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                     row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
-                    head_dim: int, page_size: int, scale: float, window: int | None = None) -> torch.Tensor:
+                    head_dim: int, page_size: int, scale: float, window: int | None = None,
+                    min_q_len: int = 1) -> torch.Tensor:
     """Causal attention of every new token over its request's pages (CUDA-core kernel, float32 or
-    bfloat16).  ``q`` holds [H, D] at the start of each token row of ``q_stride`` elements."""
+    bfloat16).  ``q`` holds [H, D] at the start of each token row of ``q_stride`` elements.  Rows
+    with fewer than ``min_q_len`` new tokens are left alone."""
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
           f"head_dim {head_dim}: this kernel takes multiples of 16 from 16 to 256")
     _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
@@ -156,7 +158,63 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
                                    _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                    _ptr(row_ctx_len), rows, num_tokens, _ptr(out), tag(q), num_heads,
                                    num_kv_heads, head_dim, page_size, ctypes.c_float(scale),
-                                   int(window or 0), _stream()), "paged_attention")
+                                   int(window or 0), int(min_q_len), _stream()), "paged_attention")
+    return out
+
+
+NUM_SMS = 148
+_workspaces: dict = {}
+
+
+def _workspace(device, name: str, numel: int, dtype) -> torch.Tensor:
+    """A persistent, zero-initialised scratch tensor per (device, name), grown on demand.  Kernels
+    that use it leave it as they need to find it, so it is cleared only when it is (re)made."""
+    key = (str(device), name)
+    t = _workspaces.get(key)
+    if t is None or t.numel() < numel:
+        t = torch.zeros(max(numel, 1024), dtype=dtype, device=device)
+        _workspaces[key] = t
+    return t
+
+
+def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
+    """How many parts to cut the context into: enough blocks for two per SM when the batch alone
+    does not give them, never parts shorter than one 64-key tile (the reference's rule keeps 256 keys
+    a part, inference_engine/kernels/decode_attention.py:117-125)."""
+    blocks = max(1, rows * kv_units)
+    if blocks >= 2 * NUM_SMS:
+        return 1
+    return max(1, min(-(-2 * NUM_SMS // blocks), -(-max_ctx // 64), 64))
+
+
+def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
+                     row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                     page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
+                     splits: int | None = None) -> torch.Tensor:
+    """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
+    blocks and merged in the same launch).  Rows with more new tokens are skipped."""
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "decode attention is bfloat16")
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
+          f"head_dim {head_dim}: the decode kernel takes multiples of 16 from 16 to 128")
+    _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
+    for t, n in ((block_tables, "block_tables"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"),
+                 (row_ctx_len, "row_ctx_len")):
+        _i32(t, n)
+    rows = row_q_len.numel()
+    chunks = -(-(num_heads // num_kv_heads) // 16)
+    if splits is None:
+        splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
+    part_o = part_lse = counters = None
+    if splits > 1:
+        part_o = _workspace(q.device, "decode_part_o", rows * num_heads * splits * head_dim, torch.float32)
+        part_lse = _workspace(q.device, "decode_part_lse", rows * num_heads * splits, torch.float32)
+        counters = _workspace(q.device, "decode_counters", rows * num_kv_heads * chunks, torch.int32)
+    lib = build.load("attention_decode")
+    _check(lib.mie_decode_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
+                                    _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
+                                    _ptr(row_ctx_len), rows, _ptr(out), num_heads, num_kv_heads, head_dim,
+                                    page_size, ctypes.c_float(scale), int(window or 0), int(splits),
+                                    _ptr(part_o), _ptr(part_lse), _ptr(counters), _stream()), "decode_attention")
     return out
 
 

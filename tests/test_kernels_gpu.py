@@ -271,3 +271,93 @@ def test_sampling_temperature_matches_plain(ops, vocab):
     perm = torch.tensor([5, 4, 3, 2, 1, 0])
     ops.sample(lg[perm].to(DEV), temps[perm].to(DEV), req[perm].to(DEV), pos[perm].to(DEV), 1234, out2)
     assert out2.cpu()[perm.argsort()].tolist() == out.tolist()
+
+
+# --------------------------------------------------------------------------- tensor-core decode attention
+
+def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=None, q_lens=None, max_ctx=None):
+    """Rows with one new token each (or q_lens given: rows with more are to be skipped)."""
+    dt = torch.bfloat16
+    torch.manual_seed(seed)
+    q_lens = q_lens or [1] * len(ctxs)
+    num_pages = sum(math.ceil(c / page) for c in ctxs) + 3
+    tables = scattered_tables(ctxs, page, num_pages, seed)
+    width = max(len(t) for t in tables) + 2
+    k_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)
+    v_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)
+    q_all, want = [], []
+    scale = 1.0 / math.sqrt(D)
+    for r, (ql, cl) in enumerate(zip(q_lens, ctxs)):
+        q = torch.randn(cl, H, D).to(dt)
+        k = torch.randn(cl, Hkv, D).to(dt)
+        v = torch.randn(cl, Hkv, D).to(dt)
+        if boost is not None:
+            key = boost if boost < cl else 0
+            k[key] *= 0
+            k[key, :, 0] = 30.0
+            q[-1] *= 0
+            q[-1, :, 0] = 30.0
+            v[key] = 5.0
+        for p in range(cl):
+            k_cache[tables[r][p // page], :, p % page] = k[p]
+            v_cache[tables[r][p // page], :, p % page] = v[p]
+        q_all.append(q[cl - ql:])
+        want.append(pl.causal_attention(q.float(), k.float(), v.float(), scale, window)[cl - ql:])
+    q_all = torch.cat(q_all, 0)
+    T = q_all.shape[0]
+    bt = torch.zeros(len(ctxs), width, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t)
+    q_len = torch.tensor(q_lens, dtype=torch.int32)
+    ctx_len = torch.tensor(ctxs, dtype=torch.int32)
+    q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+    out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
+    ops.decode_attention(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV),
+                         q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV), out, H, Hkv, D, page, scale, window,
+                         max_ctx=max_ctx or max(ctxs), splits=splits)
+    return out, torch.cat(want, 0), q_start.tolist()
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3, 8])
+@pytest.mark.parametrize("ctxs", [[1], [17], [1000], [2048], [5, 300, 1, 2047, 64, 65], list(range(1, 200, 7))])
+def test_decode_attention_ragged_contexts_and_splits(ops, ctxs, splits):
+    """The reference's own cases (tests/test_kernels.py:45-59 of the reference): ragged contexts, 1 / 3 / 8
+    splits, and a looser static bound as under captured graphs."""
+    out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, splits)
+    close(out, want, torch.bfloat16, f"decode ctx {ctxs[:6]} splits {splits}")
+    if splits is None:
+        out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, None, max_ctx=2048)
+        close(out, want, torch.bfloat16, "decode with a static context bound")
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 6, 48, 32), (16, 1, 128, 64),
+                                          (12, 4, 80, 128), (40, 2, 16, 16), (34, 1, 64, 16), (8, 8, 112, 16)])
+def test_decode_attention_head_shapes(ops, H, Hkv, D, page):
+    for splits in (1, 4):
+        out, want, _ = _decode_case(ops, H, Hkv, D, page, [70, 41, 300, 2, 129], splits, seed=H + D)
+        close(out, want, torch.bfloat16, f"decode H{H} Hkv{Hkv} D{D} page{page} splits {splits}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
+def test_decode_attention_window(ops, window):
+    for splits in (1, 3):
+        out, want, _ = _decode_case(ops, 8, 2, 32, 16, [90, 200, 3, 64, 129], splits, window=window, seed=window)
+        close(out, want, torch.bfloat16, f"decode window {window} splits {splits}")
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 511, 777, 799])
+def test_decode_attention_one_far_key(ops, far):
+    for splits in (1, 5):
+        out, want, _ = _decode_case(ops, 8, 2, 64, 16, [800, 800], splits, boost=far, seed=far)
+        assert (want[0] - 5.0).abs().max() < 1e-3
+        close(out, want, torch.bfloat16, f"decode far key {far} splits {splits}")
+
+
+def test_decode_attention_skips_rows_with_more_tokens_and_runs_twice(ops):
+    """Rows with q_len > 1 are another kernel's: their outputs stay untouched.  A second launch on
+    the same scratch gives the same answer (the split counters are left at zero)."""
+    for _ in range(2):
+        out, want, starts = _decode_case(ops, 8, 2, 64, 16, [100, 50, 300, 7], 4, q_lens=[1, 5, 1, 2])
+        assert (out[starts[1]:starts[1] + 5] == 77.0).all() and (out[starts[3]:starts[3] + 2] == 77.0).all()
+        close(out[starts[0]], want[starts[0]], torch.bfloat16, "row 0")
+        close(out[starts[2]], want[starts[2]], torch.bfloat16, "row 2")
