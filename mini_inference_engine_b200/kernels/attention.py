@@ -36,6 +36,6 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
                              max_ctx=ctx.max_ctx_len)
     if has_prefill:
-        ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale,
-                            window, min_q_len=2)
+        ops.prefill_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale,
+                              window, min_q_len=2)
     return out

@@ -162,6 +162,29 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
     return out
 
 
+def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
+                      row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                      head_dim: int, page_size: int, scale: float, window: int | None = None,
+                      min_q_len: int = 2) -> torch.Tensor:
+    """Causal attention of prompt portions over their request's pages (bfloat16, tensor cores).
+    Rows with fewer than ``min_q_len`` new tokens are left alone."""
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
+          f"head_dim {head_dim}: the prefill kernel takes multiples of 16 from 16 to 128")
+    _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
+    for t, n in ((block_tables, "block_tables"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"),
+                 (row_ctx_len, "row_ctx_len")):
+        _i32(t, n)
+    _need(out.is_contiguous(), "attention output must be contiguous")
+    lib = build.load("attention_prefill")
+    _check(lib.mie_prefill_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
+                                     _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
+                                     _ptr(row_ctx_len), row_q_len.numel(), num_tokens, _ptr(out), num_heads,
+                                     num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window or 0),
+                                     int(min_q_len), _stream()), "prefill_attention")
+    return out
+
+
 NUM_SMS = 148
 _workspaces: dict = {}
 

@@ -116,7 +116,7 @@ def test_rope_and_cache_write(ops, dt, H, Hkv, D, rot, page):
     assert (kc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()   # nothing else was written
 
 
-def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None):
+def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None, kernel="simt", min_q_len=1):
     """rows: list of (q_len, ctx_len).  Builds random q/k/v per request, scatters k/v into pages, runs
     the kernel and the plain attention on each request's whole sequence."""
     torch.manual_seed(seed)
@@ -152,9 +152,10 @@ def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None)
     q_len = torch.tensor([a for a, _ in rows], dtype=torch.int32)
     ctx_len = torch.tensor([c for _, c in rows], dtype=torch.int32)
     q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
-    out = torch.empty(T, H, D, dtype=dt, device=DEV)
-    ops.paged_attention(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV), q_start.to(DEV),
-                        q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window)
+    out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
+    fn = ops.paged_attention if kernel == "simt" else ops.prefill_attention
+    fn(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV), q_start.to(DEV),
+       q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window, min_q_len=min_q_len)
     return out, torch.cat(want, 0)
 
 
@@ -361,3 +362,41 @@ def test_decode_attention_skips_rows_with_more_tokens_and_runs_twice(ops):
         assert (out[starts[1]:starts[1] + 5] == 77.0).all() and (out[starts[3]:starts[3] + 2] == 77.0).all()
         close(out[starts[0]], want[starts[0]], torch.bfloat16, "row 0")
         close(out[starts[2]], want[starts[2]], torch.bfloat16, "row 2")
+
+
+# --------------------------------------------------------------------------- tensor-core prefill attention
+
+@pytest.mark.parametrize("rows", RAGGED + [[(2, 2), (63, 63), (64, 64), (65, 65), (129, 129)], [(2048, 2048)],
+                                           [(2, 1000), (64, 1024), (100, 2047)]])
+def test_prefill_attention_ragged(ops, rows):
+    out, want = _paged_case(ops, torch.bfloat16, 32, 4, 64, 16, rows, kernel="prefill")
+    close(out, want, torch.bfloat16, f"prefill rows {rows}")
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 6, 48, 32), (16, 1, 128, 64),
+                                          (12, 4, 80, 128), (5, 5, 112, 16)])
+def test_prefill_attention_head_shapes(ops, H, Hkv, D, page):
+    out, want = _paged_case(ops, torch.bfloat16, H, Hkv, D, page, [(1, 70), (9, 41), (135, 135), (2, 2), (70, 200)],
+                            seed=H + D, kernel="prefill")
+    close(out, want, torch.bfloat16, f"prefill H{H} Hkv{Hkv} D{D} page{page}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 64, 65, 100, 200])
+def test_prefill_attention_window_edges(ops, window):
+    out, want = _paged_case(ops, torch.bfloat16, 4, 2, 32, 16, [(1, 90), (20, 60), (150, 150), (70, 300), (2, 3)],
+                            window=window, seed=window, kernel="prefill")
+    close(out, want, torch.bfloat16, f"prefill window {window}")
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 511, 777])
+def test_prefill_attention_one_far_key(ops, far):
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(100, 800), (3, 800)], boost=far, seed=far, kernel="prefill")
+    assert (want[99] - 5.0).abs().max() < 1e-3
+    close(out, want, torch.bfloat16, f"prefill far key {far}")
+
+
+def test_prefill_attention_skips_single_token_rows(ops):
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(1, 100), (5, 50), (1, 300), (2, 7)], kernel="prefill", min_q_len=2)
+    assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
+    close(out[1:6], want[1:6], torch.bfloat16, "row 1")
+    close(out[7:9], want[7:9], torch.bfloat16, "row 3")
