@@ -1,0 +1,294 @@
+// The decode attention kernel, its parameter block and its launch by head size, shared by the two
+// entry points that differ only in where the scratch memory comes from (attention_decode.cu: the
+// caller's; attention_decode_static.cu: a fixed array inside the library).
+#pragma once
+#include "mma_common.cuh"
+
+#define DEC_WARPS 4
+#define DEC_TILE 64
+#define DEC_MAX_D 128
+
+struct DecodeParams {
+    const bf16* q; int64_t q_stride;
+    const bf16* k_cache; const bf16* v_cache;
+    const int* block_tables; int table_stride;
+    const int* row_q_start; const int* row_q_len; const int* row_ctx_len;
+    bf16* out;
+    float* part_o; float* part_lse; int* counters;      // scratch (splits > 1)
+    int num_heads, num_kv_heads, page_size, page_shift, window, splits, chunks;
+    float scale_log2e;
+};
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(const DecodeParams p) {
+    constexpr int DP = D + 8;                    // padded row: ldmatrix rows fall into different banks
+    constexpr int KSTEPS = D / 16, NBLK = D / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [2][DEC_TILE][DP]
+    bf16* v_s = k_s + 2 * DEC_TILE * DP;                           // [2][DEC_TILE][DP]
+    __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
+    __shared__ int s_last;
+
+    const int row = blockIdx.z;
+    if (p.row_q_len[row] != 1) return;
+    const int G = p.num_heads / p.num_kv_heads;
+    const int kvh = blockIdx.y / p.chunks, chunk = blockIdx.y - kvh * p.chunks;
+    const int g0 = chunk * 16, gn = min(16, G - g0);               // query heads of this block within the group
+    const int split = blockIdx.x;
+    const int ctx = p.row_ctx_len[row];
+    const int token = p.row_q_start[row];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int quad = lane >> 2, tq = lane & 3;
+
+    // this block's part of the context: the range [lo, ctx) cut into `splits` parts of whole tiles
+    const int lo = p.window > 0 ? (max(0, ctx - p.window) & ~(DEC_TILE - 1)) : 0;
+    const int first_key = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int tiles_total = (ctx - lo + DEC_TILE - 1) / DEC_TILE;
+    const int tiles_per = (tiles_total + p.splits - 1) / p.splits;
+    const int kbeg = lo + split * tiles_per * DEC_TILE;
+    const int kend = min(ctx, kbeg + tiles_per * DEC_TILE);
+    const int ntiles = kend > kbeg ? (kend - kbeg + DEC_TILE - 1) / DEC_TILE : 0;
+
+    // Q fragments (A operand), rows = query heads of the group, zero beyond gn
+    unsigned qf[KSTEPS][4];
+    {
+        const bf16* qb = p.q + (int64_t)token * p.q_stride + (int64_t)(kvh * G + g0) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = quad + (i & 1) * 8, c = ks * 16 + tq * 2 + (i >> 1) * 8;
+                qf[ks][i] = r < gn ? *reinterpret_cast<const unsigned*>(qb + (int64_t)r * D + c) : 0u;
+            }
+        }
+    }
+
+    float o[NBLK][4];
+#pragma unroll
+    for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    const int* table = p.block_tables + (int64_t)row * p.table_stride;
+    constexpr int CHUNKS_PER_ROW = D / 8;                          // 16-byte pieces per key
+    auto load_tile = [&](int t, int stage) {
+        const int k0 = kbeg + t * DEC_TILE;
+        bf16* kd = k_s + stage * DEC_TILE * DP;
+        bf16* vd = v_s + stage * DEC_TILE * DP;
+        for (int idx = threadIdx.x; idx < DEC_TILE * CHUNKS_PER_ROW; idx += DEC_WARPS * 32) {
+            const int r = idx / CHUNKS_PER_ROW, c = (idx - r * CHUNKS_PER_ROW) * 8;
+            const int key = k0 + r;
+            if (key < kend) {
+                const int page = table[key >> p.page_shift];
+                const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1))) * D + c;
+                cp_async16(kd + r * DP + c, p.k_cache + src);
+                cp_async16(vd + r * DP + c, p.v_cache + src);
+            } else {                                               // beyond the part: zeros, so that 0 * v stays 0
+                *reinterpret_cast<uint4*>(kd + r * DP + c) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + r * DP + c) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    if (ntiles > 0) load_tile(0, 0);
+    cp_async_commit();
+    for (int t = 0; t < ntiles; ++t) {
+        const int stage = t & 1;
+        if (t + 1 < ntiles) load_tile(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kt = k_s + stage * DEC_TILE * DP + warp * 16 * DP;
+        const bf16* vt = v_s + stage * DEC_TILE * DP + warp * 16 * DP;
+        const int key0 = kbeg + t * DEC_TILE + warp * 16;
+        if (key0 < kend) {                                          // warp-uniform
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, kt + ((lane & 7) + (lane >> 4) * 8) * DP + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[0], qf[ks], b0, b1);
+                mma_bf16(s[1], qf[ks], b2, b3);
+            }
+            // mask, scale to base 2, running max
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + n * 8 + tq * 2 + (i & 1);
+                    const bool ok = key < kend && key >= first_key;
+                    s[n][i] = ok ? s[n][i] * p.scale_log2e : -INFINITY;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
+                }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            }
+            float alpha[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float mn = fmaxf(m[h], mx[h]);
+                alpha[h] = mn == -INFINITY ? 1.f : exp2f(m[h] - mn);
+                m[h] = mn;
+            }
+            unsigned pf[4];
+            {
+                float pv[2][4];
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float mm = m[i >> 1];
+                        pv[n][i] = mm == -INFINITY ? 0.f : exp2f(s[n][i] - mm);
+                        sum[i >> 1] += pv[n][i];
+                    }
+                pf[0] = pack_bf16(pv[0][0], pv[0][1]);
+                pf[1] = pack_bf16(pv[0][2], pv[0][3]);
+                pf[2] = pack_bf16(pv[1][0], pv[1][1]);
+                pf[3] = pack_bf16(pv[1][2], pv[1][3]);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+                sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+                l[h] = l[h] * alpha[h] + sum[h];
+            }
+#pragma unroll
+            for (int n = 0; n < NBLK; ++n) {
+                o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int n2 = 0; n2 < NBLK / 2; ++n2) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + n2 * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * n2], pf, b0, b1);
+                mma_bf16(o[2 * n2 + 1], pf, b2, b3);
+            }
+        }
+        __syncthreads();                                           // the stage may be overwritten next round
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps: each leaves (m, l, O) in shared memory (the tile buffers are free now)
+    float* o_s = reinterpret_cast<float*>(smem_raw);               // [DEC_WARPS][16][D]
+    if (tq == 0) { m_s[warp][quad] = m[0]; m_s[warp][quad + 8] = m[1]; l_s[warp][quad] = l[0]; l_s[warp][quad + 8] = l[1]; }
+#pragma unroll
+    for (int n = 0; n < NBLK; ++n) {
+        const int c = n * 8 + tq * 2;
+        o_s[(warp * 16 + quad) * D + c] = o[n][0];
+        o_s[(warp * 16 + quad) * D + c + 1] = o[n][1];
+        o_s[(warp * 16 + quad + 8) * D + c] = o[n][2];
+        o_s[(warp * 16 + quad + 8) * D + c + 1] = o[n][3];
+    }
+    __syncthreads();
+    const int unit = (row * p.num_kv_heads + kvh) * p.chunks + chunk;
+    for (int idx = threadIdx.x; idx < gn * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, d = idx - g * D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, m_s[w][g]);
+        float acc = 0.f, ll = 0.f;
+        if (mm > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                const float f = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - mm);
+                acc += f * o_s[(w * 16 + g) * D + d];
+                ll += f * l_s[w][g];
+            }
+        }
+        const float val = ll > 0.f ? acc / ll : 0.f;
+        const int head = kvh * G + g0 + g;
+        if (p.splits == 1) {
+            p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(val);
+        } else {
+            const int64_t slot = ((int64_t)row * p.num_heads + head) * p.splits + split;
+            p.part_o[slot * D + d] = val;
+            if (d == 0) p.part_lse[slot] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+        }
+    }
+    if (p.splits == 1) return;
+
+    // the last block of this (row, kv head, chunk) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(p.counters + unit, 1);
+        s_last = done == p.splits - 1;
+        if (s_last) p.counters[unit] = 0;                          // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < gn * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, d = idx - g * D;
+        const int head = kvh * G + g0 + g;
+        const int64_t base = ((int64_t)row * p.num_heads + head) * p.splits;
+        float mm = -INFINITY;
+        for (int s2 = 0; s2 < p.splits; ++s2) mm = fmaxf(mm, __ldcg(p.part_lse + base + s2));
+        float acc = 0.f, wsum = 0.f;
+        for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float lse = __ldcg(p.part_lse + base + s2);
+            if (lse == -INFINITY) continue;
+            const float w = exp2f(lse - mm);
+            acc += w * __ldcg(p.part_o + (base + s2) * D + d);
+            wsum += w;
+        }
+        p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+    }
+}
+
+template <int D>
+static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t stream) {
+    const size_t smem = (size_t)2 * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
+    decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, stream>>>(p);
+    return launch_status();
+}
+
+
+// Checks the sizes, fills the parameter block and launches.  `part_o`, `part_lse` and `counters`
+// may be null when splits == 1.
+static int decode_attention_launch(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                   const int* block_tables, int table_stride, const int* row_q_start,
+                                   const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
+                                   int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
+                                   int window, int splits, float* part_o, float* part_lse, int* counters,
+                                   cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
+    if (page_size < 1 || (page_size & (page_size - 1))) return MIE_ERR_BAD_ARG;
+    if (splits < 1 || (splits > 1 && (!part_o || !part_lse || !counters))) return MIE_ERR_BAD_ARG;
+    if (num_rows > 65535) return MIE_ERR_TOO_LARGE;
+    DecodeParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride;
+    p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+    p.block_tables = block_tables; p.table_stride = table_stride;
+    p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len;
+    p.out = (bf16*)out; p.part_o = part_o; p.part_lse = part_lse; p.counters = counters;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window; p.splits = splits;
+    const int G = num_heads / num_kv_heads;
+    p.chunks = (G + 15) / 16;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    switch (head_dim) {
+        case 16: return launch_decode<16>(p, num_rows, stream);
+        case 32: return launch_decode<32>(p, num_rows, stream);
+        case 48: return launch_decode<48>(p, num_rows, stream);
+        case 64: return launch_decode<64>(p, num_rows, stream);
+        case 80: return launch_decode<80>(p, num_rows, stream);
+        case 96: return launch_decode<96>(p, num_rows, stream);
+        case 112: return launch_decode<112>(p, num_rows, stream);
+        case 128: return launch_decode<128>(p, num_rows, stream);
+    }
+    return MIE_ERR_BAD_ARG;
+}

@@ -122,6 +122,12 @@ def _compile(name: str, out: str, verbose: bool) -> None:
             pass
         raise BuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
+    for old in os.listdir(os.path.dirname(out)):          # libraries of earlier versions of this source
+        if old.startswith(f"lib{name}-") and old.endswith(".so") and old != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), old))
+            except OSError:
+                pass
     if verbose:
         print(f"[mini_inference_engine_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)
