@@ -32,7 +32,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
                 "-Xcompiler", "-fvisibility=default"]
 
 # every source file of the package; `build_all` compiles all of them
-SOURCES = ("embedding", "norm", "rope_cache", "attention_simt", "attention_decode", "attention_prefill", "activation", "gemm_simt",
+SOURCES = ("embedding", "norm", "rope_cache", "attention_simt", "attention_decode", "attention_decode_static", "attention_prefill",
+           "activation", "gemm_simt",
            "sampling")
 
 _libs: dict[str, ctypes.CDLL] = {}
