@@ -1,0 +1,435 @@
+// y[M, N] = x[M, K] * W[N, K]^T (+ bias) in bfloat16 on the 5th-generation tensor cores:
+// tcgen05.mma issued by one thread, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), the float32 accumulator in tensor memory (TMEM), read
+// back with tcgen05.ld for the epilogue.  The reference calls the vendor library for these products
+// (F.linear, inference_engine/model.py:172,178,180,181,185).
+//
+// Both operands are K-major (x rows and W rows are contiguous in K), so one kernel serves both
+// orientations of the 128-row MMA:
+//   NORMAL  (many tokens):  MMA rows = 128 tokens, MMA columns = BN output features.
+//   SWAPPED (few tokens, decode): MMA rows = 128 output features (the weight streams through the
+//           128-row operand at full tile height), MMA columns = the tokens padded to BN in
+//           {16, 32, 64, 128, 256}.  The step is then pure weight streaming; the K dimension is
+//           split across blocks (split-K) so that all SMs pull on HBM, and the block that finishes
+//           last for a tile adds the partial sums (float32, in scratch memory that stays in L2) and
+//           writes the result -- one launch, no second kernel.
+//
+// Roles in a block of 6 warps: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and MMA issuer
+// (one lane), warps 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).  A ring of
+// `stages` shared-memory slots is handed back and forth through mbarriers: full[s] (TMA bytes have
+// landed) and empty[s] (tcgen05.commit: the MMAs that read the slot are done).
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the block raises an error word in
+// host-visible memory, stops issuing work, lets copies in flight land, frees its TMEM and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_MAX_STAGES 8
+#define TC_THREADS 192
+#define WAIT_LIMIT (1u << 24)
+
+#define GEMM_OK 0
+
+struct TcParams {
+    void* out;               // [M, N] bfloat16 or float32
+    const void* bias;        // [N] or null
+    int bias_tag;
+    float* partial;          // [splits, M, N] float32 scratch (splits > 1)
+    int* counters;           // one per output tile, zero before the first launch and left zero
+    int* error;              // host-visible error word
+    int M, N, K;             // tokens, output features, inner size
+    int k_tiles, tiles_per_split, splits, stages;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  False when the limit ran out here or another role of the block gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 64 bfloat16 = 128 bytes, 128-byte swizzle (what a
+// TMA box of {64, rows} with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are 1024 bytes apart
+// (stride byte offset), the leading byte offset is not used by swizzled K-major layouts (set to 1),
+// descriptor version 1, layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, N >> 3 at bit 17,
+// M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <bool OUT_F32>
+__device__ __forceinline__ void store_out(void* out, int64_t idx, float v) {
+    if (OUT_F32) reinterpret_cast<float*>(out)[idx] = v;
+    else reinterpret_cast<bf16*>(out)[idx] = __float2bfloat16_rn(v);
+}
+
+// 16 consecutive output columns of one row, starting at a multiple of 8 (N % 8 == 0, so groups of 8
+// are wholly inside or outside the row).
+template <bool OUT_F32>
+__device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, int N, const float* v) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        if (n + g * 8 >= N) return;
+        if (OUT_F32) {
+            float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + row_off + n + g * 8);
+            p[0] = make_float4(v[g * 8], v[g * 8 + 1], v[g * 8 + 2], v[g * 8 + 3]);
+            p[1] = make_float4(v[g * 8 + 4], v[g * 8 + 5], v[g * 8 + 6], v[g * 8 + 7]);
+        } else {
+            uint4 w;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(out) + row_off + n + g * 8) = w;
+        }
+    }
+}
+
+template <int BN, bool SWAPPED, bool OUT_F32>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row operand: x (NORMAL) or W (SWAPPED)
+               const __grid_constant__ CUtensorMap map_b,     // the BN-row operand:  W (NORMAL) or x (SWAPPED)
+               const TcParams p) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];
+    __shared__ __align__(8) uint64_t tmem_full_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag, s_last;
+
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;        // swizzled tiles sit on 1024-byte lines
+    unsigned char* tiles = smem_dyn + (tiles_base - smem_u32(smem_dyn));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * TC_BM;          // first row of the 128-row operand
+    const int b0 = blockIdx.y * BN;             // first row of the BN-row operand
+    const int split = blockIdx.z;
+    const int kt0 = split * p.tiles_per_split;
+    const int kt1 = min(p.k_tiles, kt0 + p.tiles_per_split);
+    const int n_kt = kt1 - kt0;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the barriers are used by the TMA unit
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < n_kt; ++it) {
+                const int s = it % p.stages, round = it / p.stages;
+                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p)) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* slot = tiles + (size_t)s * STAGE_BYTES;
+                const int k = (kt0 + it) * TC_BK;
+                tma_load_2d(slot, &map_a, &full_bar[s], k, a0);
+                tma_load_2d(slot + A_BYTES, &map_b, &full_bar[s], k, b0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+            bool ok = true;
+            for (int it = 0; it < n_kt && ok; ++it) {
+                const int s = it % p.stages, round = it / p.stages;
+                ok = mbar_wait(&full_bar[s], round & 1, abort_p);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = tiles_base + (uint32_t)s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int j = 0; j < TC_BK / 16; ++j) {       // 16 elements = 32 bytes of K per MMA, inside the swizzle row
+                    umma_bf16(tmem_base, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc,
+                              (it > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);                  // frees the slot once these MMAs have read it
+            }
+            if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
+        }
+    } else {
+        // epilogue: warp q reads TMEM lanes 32q .. 32q+31
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                         // row of the MMA tile this thread owns
+        const bool ready = mbar_wait(&tmem_full_bar, 0, abort_p);
+        tc_fence_after();
+        if (ready) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const bool direct = p.splits == 1;
+            float* part = direct ? nullptr : p.partial + (size_t)split * p.M * p.N;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                tmem_ld16(taddr + c, v);
+                if (!SWAPPED) {
+                    const int m = a0 + r, n = b0 + c;
+                    if (m < p.M && n < p.N) {
+                        if (direct) {
+                            if (p.bias) {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) if (n + i < p.N) v[i] += load_tagged(p.bias, n + i, p.bias_tag);
+                            }
+                            store_row16<OUT_F32>(p.out, (int64_t)m * p.N, n, p.N, v);
+                        } else {
+                            store_row16<true>(part, (int64_t)m * p.N, n, p.N, v);
+                        }
+                    }
+                } else {
+                    const int n = a0 + r;
+                    if (n < p.N) {
+                        const float b = (direct && p.bias) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int t = b0 + c + i;
+                            if (t < p.M) {
+                                if (direct) store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, v[i] + b);
+                                else part[(int64_t)t * p.N + n] = v[i];
+                            }
+                        }
+                    }
+                }
+            }
+            if (!direct) __threadfence();                    // partial sums are visible before the tile's counter moves
+        }
+    }
+
+    // split-K: the block that finishes last for this tile adds the partial sums
+    tc_fence_before();
+    __syncthreads();                                         // every role is done; nothing waits any more
+    const bool aborted = abort_flag != 0;
+    if (p.splits > 1 && !aborted) {
+        if (threadIdx.x == 0) {
+            const int unit = blockIdx.y * gridDim.x + blockIdx.x;
+            const int done = atomicAdd(p.counters + unit, 1);
+            s_last = done == p.splits - 1;
+            if (s_last) p.counters[unit] = 0;
+        }
+        __syncthreads();
+        if (s_last && warp >= 2) {
+            __threadfence();
+            const int q = warp & 3, r = q * 32 + lane;
+            if (!SWAPPED) {
+                const int m = a0 + r;
+                if (m < p.M) {
+                    for (int c = 0; c < BN; c += 8) {
+                        const int n = b0 + c;
+                        if (n >= p.N) break;
+                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        for (int s = 0; s < p.splits; ++s) {
+                            const float4* src = reinterpret_cast<const float4*>(p.partial + ((size_t)s * p.M + m) * p.N + n);
+                            const float4 x = __ldcg(src), y = __ldcg(src + 1);
+                            acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                            acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (p.bias) acc[i] += load_tagged(p.bias, n + i, p.bias_tag);
+                            store_out<OUT_F32>(p.out, (int64_t)m * p.N + n + i, acc[i]);
+                        }
+                    }
+                }
+            } else {
+                const int n = a0 + r;
+                if (n < p.N) {
+                    const float b = p.bias ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+                    for (int i = 0; i < BN; ++i) {
+                        const int t = b0 + i;
+                        if (t >= p.M) break;
+                        float acc = 0.f;
+                        for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + ((size_t)s * p.M + t) * p.N + n);
+                        store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, acc + b);
+                    }
+                }
+            }
+        }
+    }
+
+    if (aborted) {
+        if (threadIdx.x == 0) atomicExch(p.error, 1);
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);       // let copies that are still in flight land
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static int* g_error_host = nullptr;     // pinned, mapped: the kernel writes it, the host reads it without a copy
+static int* g_error_dev = nullptr;
+
+static int tc_setup() {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return (int)e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return MIE_ERR_BAD_ARG;
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    if (!g_error_host) {
+        cudaError_t e = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+        if (e != cudaSuccess) return (int)e;
+        *g_error_host = 0;
+        e = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of {64, box_rows} elements
+// and the 128-byte swizzle; rows and columns outside the matrix read as zero.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BN, bool SWAPPED, bool OUT_F32>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t stream) {
+    const size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAPPED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    gemm_tc_kernel<BN, SWAPPED, OUT_F32><<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
+    return launch_status();
+}
+
+template <bool SWAPPED, bool OUT_F32>
+static int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return launch_tc<16, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+        case 32: return launch_tc<32, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+        case 64: return launch_tc<64, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+        case 128: return launch_tc<128, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+        case 256: return launch_tc<256, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+    }
+    return MIE_ERR_BAD_ARG;
+}
+
+// x [M, K] and w [N, K] bfloat16, y [M, N] bfloat16 (y_tag MIE_BF16) or float32.  `swapped` puts the
+// weight on the 128-row side (few tokens), `bn` is the other side's tile (16..256), `splits` cuts K;
+// with splits > 1 `partial` holds splits*M*N floats and `counters` one zeroed int per output tile.
+// Needs K % 8 == 0 and N % 8 == 0 and 16-byte aligned pointers; refuses anything else.
+extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
+                           int K, int swapped, int bn, int splits, int stages, float* partial, int* counters,
+                           cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 8) return MIE_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
+    if (stages < 2 || stages > TC_MAX_STAGES || splits < 1) return MIE_ERR_BAD_ARG;
+    if (splits > 1 && (!partial || !counters)) return MIE_ERR_BAD_ARG;
+    int rc = tc_setup();
+    if (rc) return rc;
+    TcParams p;
+    p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.partial = partial; p.counters = counters; p.error = g_error_dev;
+    p.M = M; p.N = N; p.K = K;
+    p.k_tiles = (K + TC_BK - 1) / TC_BK;
+    if (splits > p.k_tiles) splits = p.k_tiles;
+    p.tiles_per_split = (p.k_tiles + splits - 1) / splits;
+    p.splits = (p.k_tiles + p.tiles_per_split - 1) / p.tiles_per_split;      // every split has at least one k-tile
+    p.stages = stages;
+    CUtensorMap ma, mb;
+    dim3 grid;
+    if (swapped) {
+        if ((rc = make_map(&ma, w, N, K, TC_BM))) return rc;
+        if ((rc = make_map(&mb, x, M, K, bn))) return rc;
+        grid = dim3((N + TC_BM - 1) / TC_BM, (M + bn - 1) / bn, p.splits);
+    } else {
+        if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
+        if ((rc = make_map(&mb, w, N, K, bn))) return rc;
+        grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, p.splits);
+    }
+    if (grid.y > 65535 || grid.z > 65535) return MIE_ERR_TOO_LARGE;
+    const bool f32 = y_tag == MIE_F32;
+    if (swapped) return f32 ? dispatch_bn<true, true>(bn, ma, mb, p, grid, stream) : dispatch_bn<true, false>(bn, ma, mb, p, grid, stream);
+    return f32 ? dispatch_bn<false, true>(bn, ma, mb, p, grid, stream) : dispatch_bn<false, false>(bn, ma, mb, p, grid, stream);
+}
+
+// Non-zero when a block of any launch so far gave up a bounded wait.  Reads host memory that the
+// kernel writes directly; meaningful after the launches have completed (a stream synchronise).
+extern "C" int mie_gemm_tc_error(void) { return g_error_host ? *g_error_host : 0; }
+extern "C" void mie_gemm_tc_clear_error(void) { if (g_error_host) *g_error_host = 0; }

@@ -1,0 +1,83 @@
+"""The tcgen05 matrix product (``csrc/gemm_tcgen05.cu``): plan and launch.
+
+The plan picks the orientation (weight on the 128-row side for few tokens, tokens on the 128-row
+side otherwise), the tile of the other side, how far to split K so that all SMs stream, and the
+depth of the shared-memory ring."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import build, ops
+
+NUM_SMS = 148
+SMEM_BUDGET = 226 * 1024
+TWO_PER_SM = 112 * 1024
+
+
+class GemmTcError(RuntimeError):
+    pass
+
+
+def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    M, K = x.shape
+    N = w.shape[0]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and N % 8 == 0 and x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def plan(M: int, N: int, K: int) -> dict:
+    k_tiles = -(-K // 64)
+    if M <= 128:
+        swapped = True
+        bn = next(b for b in (16, 32, 64, 128) if b >= M)
+        tiles = -(-N // 128)
+    else:
+        swapped = False
+        bn = 128
+        tiles = -(-M // 128) * -(-N // bn)
+    stage = 128 * 64 * 2 + bn * 64 * 2
+    splits = 1
+    if tiles < 2 * NUM_SMS:
+        # enough blocks for two per SM, but at least two k-tiles per block
+        splits = max(1, min(k_tiles // 2 or 1, -(-2 * NUM_SMS // tiles)))
+        if not swapped and M * N * 4 * splits > 64 * 2 ** 20:      # partial sums should stay in L2
+            splits = 1
+    per_split = -(-k_tiles // splits)
+    stages = max(2, min(8, per_split, (TWO_PER_SM - 1024) // stage))
+    if stages < 3 and per_split > 2:
+        stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024) // stage))
+    return dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, **force) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) with bfloat16 operands on tcgen05."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not supports(x, w, out):
+        raise GemmTcError(f"tcgen05 gemm needs contiguous 16-byte aligned bfloat16 operands with K % 8 == 0 and "
+                          f"N % 8 == 0; got x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+    pl = plan(M, N, K)
+    pl.update(force)
+    splits = max(1, min(pl["splits"], -(-K // 64)))
+    partial = counters = None
+    if splits > 1:
+        tiles = -(-N // 128) * -(-M // pl["bn"]) if pl["swapped"] else -(-M // 128) * -(-N // pl["bn"])
+        partial = ops._workspace(x.device, "gemm_tc_partial", splits * M * N, torch.float32)
+        counters = ops._workspace(x.device, "gemm_tc_counters", tiles, torch.int32)
+    lib = build.load("gemm_tcgen05")
+    rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
+                         ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], splits, pl["stages"],
+                         ops._ptr(partial), ops._ptr(counters), ops._stream())
+    ops._check(rc, f"gemm_tc M{M} N{N} K{K} {pl}")
+    return out
+
+
+def check_error() -> None:
+    """Raises if a block of an earlier launch gave up a bounded wait (call after a synchronise)."""
+    lib = build.load("gemm_tcgen05")
+    if lib.mie_gemm_tc_error():
+        lib.mie_gemm_tc_clear_error()
+        raise GemmTcError("a tcgen05 gemm block gave up waiting on a barrier; its output is not valid")

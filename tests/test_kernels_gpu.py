@@ -400,3 +400,64 @@ def test_prefill_attention_skips_single_token_rows(ops):
     assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
     close(out[1:6], want[1:6], torch.bfloat16, "row 1")
     close(out[7:9], want[7:9], torch.bfloat16, "row 3")
+
+
+# --------------------------------------------------------------------------- tcgen05 matrix product
+
+def _tc_case(M, N, K, out_dt=torch.bfloat16, bias=False, seed=0, **force):
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(seed + M + N + K)
+    x = torch.randn(M, K).bfloat16().to(DEV)
+    w = torch.randn(N, K).bfloat16().to(DEV)
+    b = torch.randn(N).bfloat16().to(DEV) if bias else None
+    y = torch.full((M, N), 7.0, dtype=out_dt, device=DEV)
+    gemm_tc.gemm(x, w, y, b, **force)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    want = x.double().cpu() @ w.double().cpu().t()
+    if bias:
+        want = want + b.double().cpu()
+    return y, want
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (1, 2560, 2048), (8, 2048, 2048), (8, 11264, 2048), (8, 2048, 5632),
+                                   (7, 264, 176), (16, 384, 96), (33, 2560, 2048), (64, 32000, 2048), (100, 1000, 200),
+                                   (128, 2048, 2048)])
+def test_gemm_tc_few_tokens(M, N, K):
+    y, want = _tc_case(M, N, K)
+    close(y, want.float(), torch.bfloat16, f"tcgen05 gemm {M}x{N}x{K}")
+    y, want = _tc_case(M, N, K, out_dt=torch.float32, bias=True)
+    assert (y.cpu().double() - want).abs().max() <= 2e-3 * want.abs().max()      # float32 out: only the order of sums
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 256, 64), (2048, 2560, 2048), (300, 384, 96), (1000, 352, 176), (512, 2048, 5632),
+                                   (2048, 11264, 2048), (257, 32000, 2048)])
+def test_gemm_tc_many_tokens(M, N, K):
+    y, want = _tc_case(M, N, K)
+    close(y, want.float(), torch.bfloat16, f"tcgen05 gemm {M}x{N}x{K}")
+    y, want = _tc_case(M, N, K, out_dt=torch.float32, bias=True)
+    assert (y.cpu().double() - want).abs().max() <= 2e-3 * want.abs().max()
+
+
+@pytest.mark.parametrize("force", [dict(swapped=True, bn=16, splits=1, stages=2), dict(swapped=True, bn=32, splits=5, stages=3),
+                                   dict(swapped=True, bn=64, splits=32, stages=8), dict(swapped=True, bn=128, splits=3, stages=4),
+                                   dict(swapped=True, bn=256, splits=2, stages=4), dict(swapped=False, bn=16, splits=1, stages=4),
+                                   dict(swapped=False, bn=64, splits=4, stages=6), dict(swapped=False, bn=128, splits=1, stages=3),
+                                   dict(swapped=False, bn=256, splits=2, stages=4), dict(swapped=False, bn=128, splits=7, stages=2)])
+def test_gemm_tc_every_tile_orientation_and_split(force):
+    for M, N, K in ((40, 392, 840), (200, 520, 2048)):
+        if force["swapped"] and M > force["bn"] * 8:
+            continue
+        y, want = _tc_case(M, N, K, bias=True, **force)
+        close(y, want.float(), torch.bfloat16, f"tcgen05 gemm {M}x{N}x{K} {force}")
+        y2, _ = _tc_case(M, N, K, bias=True, **force)          # the scratch and counters are left ready for the next launch
+        assert torch.equal(y, y2)
+
+
+def test_gemm_tc_refuses_what_it_cannot_align():
+    from mini_inference_engine_b200.kernels import gemm_tc
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(16, 100, dtype=torch.bfloat16, device=DEV)
+    assert not gemm_tc.supports(x, w, torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(gemm_tc.GemmTcError):
+        gemm_tc.gemm(x, w, torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
