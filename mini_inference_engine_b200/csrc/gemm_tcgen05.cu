@@ -9,10 +9,23 @@
 //   NORMAL  (many tokens):  MMA rows = 128 tokens, MMA columns = BN output features.
 //   SWAPPED (few tokens, decode): MMA rows = 128 output features (the weight streams through the
 //           128-row operand at full tile height), MMA columns = the tokens padded to BN in
-//           {16, 32, 64, 128, 256}.  The step is then pure weight streaming; the K dimension is
-//           split across blocks (split-K) so that all SMs pull on HBM, and the block that finishes
-//           last for a tile adds the partial sums (float32, in scratch memory that stays in L2) and
-//           writes the result -- one launch, no second kernel.
+//           {16, 32, 64, 128, 256}.  The step is then pure weight streaming.
+//
+// Split-K without scratch memory: the blocks that share an output tile form a thread-block cluster
+// along grid.z (2, 4 or 8 blocks).  Each leaves its float32 partial tile in its own shared memory,
+// the cluster synchronises, and every block adds up its share of the tile's rows straight out of the
+// others' shared memory (distributed shared memory, ld.shared::cluster) in rank order -- the same
+// order every time -- and writes the result.  No global partial sums, no atomics, no second kernel.
+//
+// Programmatic dependent launch: the kernel lets its successor start at once
+// (griddepcontrol.launch_dependents) and itself may start while its predecessor still runs.  Weights
+// do not depend on the predecessor, so the producer fills the whole shared-memory ring with weight
+// tiles first and only then waits for the predecessor (griddepcontrol.wait) to fetch the activations:
+// the weight stream of one product overlaps the tail of the kernel before it.
+//
+// Optional SwiGLU epilogue: with gate and up rows interleaved in W (row 2i = gate_i, row 2i+1 = up_i)
+// the epilogue writes silu(gate) * up, N/2 wide, from the float32 accumulators
+// (inference_engine/model.py:180-181 does this with two more kernels on rounded values).
 //
 // Roles in a block of 6 warps: warp 0 = TMA producer (one lane), warp 1 = TMEM owner and MMA issuer
 // (one lane), warps 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).  A ring of
@@ -20,7 +33,8 @@
 // landed) and empty[s] (tcgen05.commit: the MMAs that read the slot are done).
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the block raises an error word in
-// host-visible memory, stops issuing work, lets copies in flight land, frees its TMEM and returns.
+// host-visible memory, stops issuing work, lets copies in flight land, still takes part in the
+// cluster's barriers, frees its TMEM and returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -32,17 +46,15 @@
 #define TC_THREADS 192
 #define WAIT_LIMIT (1u << 24)
 
-#define GEMM_OK 0
 
 struct TcParams {
-    void* out;               // [M, N] bfloat16 or float32
+    void* out;               // [M, N] (or [M, N/2] with the SwiGLU epilogue) bfloat16 or float32
     const void* bias;        // [N] or null
     int bias_tag;
-    float* partial;          // [splits, M, N] float32 scratch (splits > 1)
-    int* counters;           // one per output tile, zero before the first launch and left zero
     int* error;              // host-visible error word
-    int M, N, K;             // tokens, output features, inner size
+    int M, N, K;             // tokens, output features (rows of W), inner size
     int k_tiles, tiles_per_split, splits, stages;
+    int swiglu;              // 1: rows 2i / 2i+1 of W are gate_i / up_i; the output is silu(gate) * up, N/2 wide
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -150,6 +162,21 @@ __device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, i
     }
 }
 
+
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 template <int BN, bool SWAPPED, bool OUT_F32>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row operand: x (NORMAL) or W (SWAPPED)
@@ -160,17 +187,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];
     __shared__ __align__(8) uint64_t tmem_full_bar;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag, s_last;
+    __shared__ int abort_flag;
 
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int RED_LD = BN + 1;                            // padded row of the float32 partial tile
     const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;        // swizzled tiles sit on 1024-byte lines
     unsigned char* tiles = smem_dyn + (tiles_base - smem_u32(smem_dyn));
+
+    grid_dep_launch_dependents();                             // the next kernel may start its own prologue now
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TC_BM;          // first row of the 128-row operand
     const int b0 = blockIdx.y * BN;             // first row of the BN-row operand
-    const int split = blockIdx.z;
+    const int split = blockIdx.z;               // = rank in the cluster
     const int kt0 = split * p.tiles_per_split;
     const int kt1 = min(p.k_tiles, kt0 + p.tiles_per_split);
     const int n_kt = kt1 - kt0;
@@ -194,14 +224,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int it = 0; it < n_kt; ++it) {
+            // weights first: they do not depend on the kernel before this one
+            const CUtensorMap* map_w = SWAPPED ? &map_a : &map_b;
+            const CUtensorMap* map_x = SWAPPED ? &map_b : &map_a;
+            const uint32_t w_off = SWAPPED ? 0 : A_BYTES, x_off = SWAPPED ? A_BYTES : 0;
+            const int w0 = SWAPPED ? a0 : b0, x0 = SWAPPED ? b0 : a0;
+            const int ahead = min(n_kt, p.stages);
+            for (int it = 0; it < ahead; ++it) {
+                mbar_expect_tx(&full_bar[it], STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)it * STAGE_BYTES + w_off, map_w, &full_bar[it], (kt0 + it) * TC_BK, w0);
+            }
+            grid_dep_wait();                                  // the activations are the previous kernel's output
+            for (int it = 0; it < ahead; ++it)
+                tma_load_2d(tiles + (size_t)it * STAGE_BYTES + x_off, map_x, &full_bar[it], (kt0 + it) * TC_BK, x0);
+            for (int it = ahead; it < n_kt; ++it) {
                 const int s = it % p.stages, round = it / p.stages;
                 if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p)) break;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 unsigned char* slot = tiles + (size_t)s * STAGE_BYTES;
                 const int k = (kt0 + it) * TC_BK;
-                tma_load_2d(slot, &map_a, &full_bar[s], k, a0);
-                tma_load_2d(slot + A_BYTES, &map_b, &full_bar[s], k, b0);
+                tma_load_2d(slot + w_off, map_w, &full_bar[s], k, w0);
+                tma_load_2d(slot + x_off, map_x, &full_bar[s], k, x0);
             }
         }
     } else if (warp == 1) {
@@ -224,107 +267,126 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
         }
     } else {
-        // epilogue: warp q reads TMEM lanes 32q .. 32q+31
+        // epilogue: warp q reads TMEM lanes 32q .. 32q+31; thread r owns row r of the MMA tile
         const int q = warp & 3;
-        const int r = q * 32 + lane;                         // row of the MMA tile this thread owns
-        const bool ready = mbar_wait(&tmem_full_bar, 0, abort_p);
+        const int r = q * 32 + lane;
+        const bool have_work = n_kt > 0;                     // a split beyond the last k-tile adds a zero tile
+        const bool ready = have_work ? mbar_wait(&tmem_full_bar, 0, abort_p) : true;
         tc_fence_after();
         if (ready) {
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-            const bool direct = p.splits == 1;
-            float* part = direct ? nullptr : p.partial + (size_t)split * p.M * p.N;
+            float* red = reinterpret_cast<float*>(tiles);     // the ring is free: every MMA has read its slot
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
-                tmem_ld16(taddr + c, v);
-                if (!SWAPPED) {
+                if (have_work) tmem_ld16(taddr + c, v);
+                else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+                if (p.splits > 1) {                            // leave the partial tile for the cluster
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) red[r * RED_LD + c + i] = v[i];
+                } else if (!SWAPPED) {
                     const int m = a0 + r, n = b0 + c;
                     if (m < p.M && n < p.N) {
-                        if (direct) {
-                            if (p.bias) {
+                        if (p.bias) {
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) if (n + i < p.N) v[i] += load_tagged(p.bias, n + i, p.bias_tag);
+                            for (int i = 0; i < 16; ++i) if (n + i < p.N) v[i] += load_tagged(p.bias, n + i, p.bias_tag);
+                        }
+                        if (p.swiglu) {
+                            float h[16];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) h[i] = silu_mul(v[2 * i], v[2 * i + 1]);
+#pragma unroll
+                            for (int i = 8; i < 16; ++i) h[i] = 0.f;
+                            // 8 outputs starting at column n / 2 of a row N / 2 wide
+                            if (OUT_F32) {
+                                float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (int64_t)m * (p.N / 2) + n / 2);
+                                o[0] = make_float4(h[0], h[1], h[2], h[3]);
+                                o[1] = make_float4(h[4], h[5], h[6], h[7]);
+                            } else {
+                                uint4 w;
+                                __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) hp[i] = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + (int64_t)m * (p.N / 2) + n / 2) = w;
                             }
-                            store_row16<OUT_F32>(p.out, (int64_t)m * p.N, n, p.N, v);
                         } else {
-                            store_row16<true>(part, (int64_t)m * p.N, n, p.N, v);
+                            store_row16<OUT_F32>(p.out, (int64_t)m * p.N, n, p.N, v);
                         }
                     }
                 } else {
                     const int n = a0 + r;
-                    if (n < p.N) {
-                        const float b = (direct && p.bias) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+                    const float b = (p.bias && n < p.N) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int t = b0 + c + i;
-                            if (t < p.M) {
-                                if (direct) store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, v[i] + b);
-                                else part[(int64_t)t * p.N + n] = v[i];
-                            }
+                    for (int i = 0; i < 16; ++i) {
+                        const int t = b0 + c + i;
+                        float val = v[i] + b;
+                        if (p.swiglu) {                        // gate on the even lane, up on the odd one
+                            const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                            if (!(lane & 1) && t < p.M && n < p.N)
+                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                        } else if (t < p.M && n < p.N) {
+                            store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                         }
                     }
                 }
             }
-            if (!direct) __threadfence();                    // partial sums are visible before the tile's counter moves
         }
     }
 
-    // split-K: the block that finishes last for this tile adds the partial sums
     tc_fence_before();
-    __syncthreads();                                         // every role is done; nothing waits any more
+    __syncthreads();                                         // every role is done; nothing waits on an mbarrier any more
     const bool aborted = abort_flag != 0;
-    if (p.splits > 1 && !aborted) {
-        if (threadIdx.x == 0) {
-            const int unit = blockIdx.y * gridDim.x + blockIdx.x;
-            const int done = atomicAdd(p.counters + unit, 1);
-            s_last = done == p.splits - 1;
-            if (s_last) p.counters[unit] = 0;
-        }
-        __syncthreads();
-        if (s_last && warp >= 2) {
-            __threadfence();
-            const int q = warp & 3, r = q * 32 + lane;
+
+    if (p.splits > 1) {
+        // split-K: add the partial tiles of the cluster's blocks, each block its share of the rows
+        cluster_sync_all();
+        const int S = p.splits;
+        const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
+        const int r_lo = split * rows_per;
+        const uint32_t red_addr = tiles_base;
+        if (warp >= 2 && !aborted) {
+            const int tid = threadIdx.x - 64;                // 0..127
             if (!SWAPPED) {
-                const int m = a0 + r;
-                if (m < p.M) {
-                    for (int c = 0; c < BN; c += 8) {
-                        const int n = b0 + c;
-                        if (n >= p.N) break;
-                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        for (int s = 0; s < p.splits; ++s) {
-                            const float4* src = reinterpret_cast<const float4*>(p.partial + ((size_t)s * p.M + m) * p.N + n);
-                            const float4 x = __ldcg(src), y = __ldcg(src + 1);
-                            acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-                            acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            if (p.bias) acc[i] += load_tagged(p.bias, n + i, p.bias_tag);
-                            store_out<OUT_F32>(p.out, (int64_t)m * p.N + n + i, acc[i]);
-                        }
-                    }
+                // rows are tokens, columns output features: consecutive threads take consecutive columns
+                const int pairs = p.swiglu ? 2 : 1;
+                for (int idx = tid; idx < rows_per * (BN / pairs); idx += 128) {
+                    const int rr = r_lo + idx / (BN / pairs), c = (idx % (BN / pairs)) * pairs;
+                    const int m = a0 + rr, n = b0 + c;
+                    if (m >= p.M || n >= p.N) continue;
+                    float acc[2] = {0.f, 0.f};
+                    for (int s = 0; s < S; ++s)
+                        for (int j = 0; j < pairs; ++j) acc[j] += ld_cluster_f32(red_addr + (rr * RED_LD + c + j) * 4, s);
+                    if (p.bias) for (int j = 0; j < pairs; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
+                    if (p.swiglu) store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
+                    else store_out<OUT_F32>(p.out, (int64_t)m * p.N + n, acc[0]);
                 }
             } else {
-                const int n = a0 + r;
-                if (n < p.N) {
-                    const float b = p.bias ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
-                    for (int i = 0; i < BN; ++i) {
-                        const int t = b0 + i;
-                        if (t >= p.M) break;
-                        float acc = 0.f;
-                        for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + ((size_t)s * p.M + t) * p.N + n);
-                        store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, acc + b);
-                    }
+                // rows are output features, columns tokens: consecutive threads take consecutive features
+                const int pairs = p.swiglu ? 2 : 1;
+                const int feats = rows_per / pairs;
+                for (int idx = tid; idx < feats * BN; idx += 128) {
+                    const int t = b0 + idx / feats, rr = r_lo + (idx % feats) * pairs;
+                    const int n = a0 + rr, c = idx / feats;
+                    if (t >= p.M || n >= p.N) continue;
+                    float acc[2] = {0.f, 0.f};
+                    for (int s = 0; s < S; ++s)
+                        for (int j = 0; j < pairs; ++j) acc[j] += ld_cluster_f32(red_addr + ((rr + j) * RED_LD + c) * 4, s);
+                    if (p.bias) for (int j = 0; j < pairs; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
+                    if (p.swiglu) store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
+                    else store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, acc[0]);
                 }
             }
         }
+        cluster_sync_all();                                  // nobody leaves while its shared memory is being read
     }
 
     if (aborted) {
         if (threadIdx.x == 0) atomicExch(p.error, 1);
         for (int i = 0; i < 64; ++i) __nanosleep(2000);       // let copies that are still in flight land
     }
-    tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -370,47 +432,69 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 }
 
 template <int BN, bool SWAPPED, bool OUT_F32>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t stream) {
-    const size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int pdl, cudaStream_t stream) {
+    size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2);
+    const size_t red = (size_t)TC_BM * (BN + 1) * sizeof(float);           // the partial tile reuses the ring
+    if (p.splits > 1 && red > smem) smem = red;
+    smem += 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAPPED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    gemm_tc_kernel<BN, SWAPPED, OUT_F32><<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
-    return launch_status();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (p.splits > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = p.splits;
+        ++na;
+    }
+    if (pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAPPED, OUT_F32>, ma, mb, p);
+    return e != cudaSuccess ? (int)e : launch_status();
 }
 
 template <bool SWAPPED, bool OUT_F32>
-static int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t stream) {
+static int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int pdl, cudaStream_t stream) {
     switch (bn) {
-        case 16: return launch_tc<16, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
-        case 32: return launch_tc<32, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
-        case 64: return launch_tc<64, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
-        case 128: return launch_tc<128, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
-        case 256: return launch_tc<256, SWAPPED, OUT_F32>(ma, mb, p, grid, stream);
+        case 16: return launch_tc<16, SWAPPED, OUT_F32>(ma, mb, p, grid, pdl, stream);
+        case 32: return launch_tc<32, SWAPPED, OUT_F32>(ma, mb, p, grid, pdl, stream);
+        case 64: return launch_tc<64, SWAPPED, OUT_F32>(ma, mb, p, grid, pdl, stream);
+        case 128: return launch_tc<128, SWAPPED, OUT_F32>(ma, mb, p, grid, pdl, stream);
+        case 256: return launch_tc<256, SWAPPED, OUT_F32>(ma, mb, p, grid, pdl, stream);
     }
     return MIE_ERR_BAD_ARG;
 }
 
-// x [M, K] and w [N, K] bfloat16, y [M, N] bfloat16 (y_tag MIE_BF16) or float32.  `swapped` puts the
-// weight on the 128-row side (few tokens), `bn` is the other side's tile (16..256), `splits` cuts K;
-// with splits > 1 `partial` holds splits*M*N floats and `counters` one zeroed int per output tile.
-// Needs K % 8 == 0 and N % 8 == 0 and 16-byte aligned pointers; refuses anything else.
+// x [M, K] and w [N, K] bfloat16, y [M, N] (with `swiglu`: [M, N/2]) bfloat16 (y_tag MIE_BF16) or
+// float32.  `swapped` puts the weight on the 128-row side (few tokens), `bn` is the other side's
+// tile (16..256), `splits` in {1, 2, 4, 8} cuts K across a cluster, `pdl` launches with programmatic
+// stream serialization.  Needs K % 8 == 0, N % 8 == 0 (N % 16 == 0 with swiglu) and 16-byte aligned
+// pointers; refuses anything else.
 extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
-                           int K, int swapped, int bn, int splits, int stages, float* partial, int* counters,
-                           cudaStream_t stream) {
+                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || N % 8) return MIE_ERR_BAD_ARG;
+    if (K <= 0 || K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
-    if (stages < 2 || stages > TC_MAX_STAGES || splits < 1) return MIE_ERR_BAD_ARG;
-    if (splits > 1 && (!partial || !counters)) return MIE_ERR_BAD_ARG;
+    if (stages < 2 || stages > TC_MAX_STAGES) return MIE_ERR_BAD_ARG;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return MIE_ERR_BAD_ARG;
     int rc = tc_setup();
     if (rc) return rc;
     TcParams p;
-    p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.partial = partial; p.counters = counters; p.error = g_error_dev;
-    p.M = M; p.N = N; p.K = K;
+    p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.error = g_error_dev;
+    p.M = M; p.N = N; p.K = K; p.swiglu = swiglu;
     p.k_tiles = (K + TC_BK - 1) / TC_BK;
-    if (splits > p.k_tiles) splits = p.k_tiles;
+    while (splits > 1 && splits > p.k_tiles) splits >>= 1;
     p.tiles_per_split = (p.k_tiles + splits - 1) / splits;
-    p.splits = (p.k_tiles + p.tiles_per_split - 1) / p.tiles_per_split;      // every split has at least one k-tile
+    p.splits = splits;             // a block whose range is empty still joins the cluster with a zero tile
     p.stages = stages;
     CUtensorMap ma, mb;
     dim3 grid;
@@ -423,10 +507,10 @@ extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int b
         if ((rc = make_map(&mb, w, N, K, bn))) return rc;
         grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, p.splits);
     }
-    if (grid.y > 65535 || grid.z > 65535) return MIE_ERR_TOO_LARGE;
+    if (grid.y > 65535) return MIE_ERR_TOO_LARGE;
     const bool f32 = y_tag == MIE_F32;
-    if (swapped) return f32 ? dispatch_bn<true, true>(bn, ma, mb, p, grid, stream) : dispatch_bn<true, false>(bn, ma, mb, p, grid, stream);
-    return f32 ? dispatch_bn<false, true>(bn, ma, mb, p, grid, stream) : dispatch_bn<false, false>(bn, ma, mb, p, grid, stream);
+    if (swapped) return f32 ? dispatch_bn<true, true>(bn, ma, mb, p, grid, pdl, stream) : dispatch_bn<true, false>(bn, ma, mb, p, grid, pdl, stream);
+    return f32 ? dispatch_bn<false, true>(bn, ma, mb, p, grid, pdl, stream) : dispatch_bn<false, false>(bn, ma, mb, p, grid, pdl, stream);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait.  Reads host memory that the

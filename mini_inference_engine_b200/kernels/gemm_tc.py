@@ -28,6 +28,9 @@ def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
+pdl_enabled = True      # launch with programmatic stream serialization (see csrc/gemm_tcgen05.cu)
+
+
 def plan(M: int, N: int, K: int) -> dict:
     k_tiles = -(-K // 64)
     if M <= 128:
@@ -40,11 +43,8 @@ def plan(M: int, N: int, K: int) -> dict:
         tiles = -(-M // 128) * -(-N // bn)
     stage = 128 * 64 * 2 + bn * 64 * 2
     splits = 1
-    if tiles < 2 * NUM_SMS:
-        # enough blocks for two per SM, but at least two k-tiles per block
-        splits = max(1, min(k_tiles // 2 or 1, -(-2 * NUM_SMS // tiles)))
-        if not swapped and M * N * 4 * splits > 64 * 2 ** 20:      # partial sums should stay in L2
-            splits = 1
+    while splits < 8 and tiles * splits * 2 <= 2 * NUM_SMS and k_tiles // (splits * 2) >= 2:
+        splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
     per_split = -(-k_tiles // splits)
     stages = max(2, min(8, per_split, (TWO_PER_SM - 1024) // stage))
     if stages < 3 and per_split > 2:
@@ -52,25 +52,22 @@ def plan(M: int, N: int, K: int) -> dict:
     return dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
 
 
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, **force) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) with bfloat16 operands on tcgen05."""
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, **force) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) with bfloat16 operands on tcgen05.  With ``swiglu`` the
+    rows of ``w`` are gate/up interleaved and out is [M, N/2] = silu(gate) * up."""
     M, K = x.shape
     N = w.shape[0]
-    if not supports(x, w, out):
+    if not supports(x, w, out) or (swiglu and N % 16):
         raise GemmTcError(f"tcgen05 gemm needs contiguous 16-byte aligned bfloat16 operands with K % 8 == 0 and "
                           f"N % 8 == 0; got x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}")
+    if tuple(out.shape) != (M, N // 2 if swiglu else N):
+        raise GemmTcError(f"output shape {tuple(out.shape)} does not match")
     pl = plan(M, N, K)
     pl.update(force)
-    splits = max(1, min(pl["splits"], -(-K // 64)))
-    partial = counters = None
-    if splits > 1:
-        tiles = -(-N // 128) * -(-M // pl["bn"]) if pl["swapped"] else -(-M // 128) * -(-N // pl["bn"])
-        partial = ops._workspace(x.device, "gemm_tc_partial", splits * M * N, torch.float32)
-        counters = ops._workspace(x.device, "gemm_tc_counters", tiles, torch.int32)
     lib = build.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
-                         ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], splits, pl["stages"],
-                         ops._ptr(partial), ops._ptr(counters), ops._stream())
+                         ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], pl["splits"], pl["stages"],
+                         int(swiglu), int(pl.get("pdl", pdl_enabled)), ops._stream())
     ops._check(rc, f"gemm_tc M{M} N{N} K{K} {pl}")
     return out
 

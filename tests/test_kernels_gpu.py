@@ -439,19 +439,38 @@ def test_gemm_tc_many_tokens(M, N, K):
     assert (y.cpu().double() - want).abs().max() <= 2e-3 * want.abs().max()
 
 
-@pytest.mark.parametrize("force", [dict(swapped=True, bn=16, splits=1, stages=2), dict(swapped=True, bn=32, splits=5, stages=3),
-                                   dict(swapped=True, bn=64, splits=32, stages=8), dict(swapped=True, bn=128, splits=3, stages=4),
+@pytest.mark.parametrize("force", [dict(swapped=True, bn=16, splits=1, stages=2), dict(swapped=True, bn=32, splits=4, stages=3),
+                                   dict(swapped=True, bn=64, splits=8, stages=8), dict(swapped=True, bn=128, splits=2, stages=4),
                                    dict(swapped=True, bn=256, splits=2, stages=4), dict(swapped=False, bn=16, splits=1, stages=4),
                                    dict(swapped=False, bn=64, splits=4, stages=6), dict(swapped=False, bn=128, splits=1, stages=3),
-                                   dict(swapped=False, bn=256, splits=2, stages=4), dict(swapped=False, bn=128, splits=7, stages=2)])
-def test_gemm_tc_every_tile_orientation_and_split(force):
-    for M, N, K in ((40, 392, 840), (200, 520, 2048)):
+                                   dict(swapped=False, bn=256, splits=2, stages=4), dict(swapped=False, bn=128, splits=8, stages=2)])
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_gemm_tc_every_tile_orientation_and_split(force, pdl):
+    for M, N, K in ((40, 392, 840), (200, 520, 2048), (9, 128, 320)):       # 320 = 5 k-tiles: a split of 8 leaves blocks empty
         if force["swapped"] and M > force["bn"] * 8:
             continue
-        y, want = _tc_case(M, N, K, bias=True, **force)
+        y, want = _tc_case(M, N, K, bias=True, pdl=pdl, **force)
         close(y, want.float(), torch.bfloat16, f"tcgen05 gemm {M}x{N}x{K} {force}")
-        y2, _ = _tc_case(M, N, K, bias=True, **force)          # the scratch and counters are left ready for the next launch
+        y2, _ = _tc_case(M, N, K, bias=True, pdl=pdl, **force)          # split-K is deterministic: the same sum order every time
         assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("M,I,K,force", [(8, 5632, 2048, {}), (3, 176, 64, {}), (64, 256, 96, dict(splits=1)),
+                                         (300, 176, 64, {}), (2048, 5632, 2048, {}), (40, 200, 840, dict(swapped=True, bn=64, splits=4, stages=4)),
+                                         (200, 264, 2048, dict(swapped=False, bn=64, splits=4, stages=4))])
+def test_gemm_tc_swiglu_epilogue(M, I, K, force):
+    """gate/up rows interleaved in W; the epilogue writes silu(gate) * up from the float32 sums."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + I)
+    x = torch.randn(M, K).bfloat16()
+    gate, up = (torch.randn(I, K) * 0.1).bfloat16(), (torch.randn(I, K) * 0.1).bfloat16()
+    w = torch.stack((gate, up), 1).reshape(2 * I, K).contiguous()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm(x.to(DEV), w.to(DEV), out, swiglu=True, **force)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    want = pl.swiglu(x.float() @ gate.float().t(), x.float() @ up.float().t())
+    close(out, want, torch.bfloat16, f"swiglu epilogue {M}x{I}x{K}")
 
 
 def test_gemm_tc_refuses_what_it_cannot_align():
