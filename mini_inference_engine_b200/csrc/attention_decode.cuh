@@ -30,6 +30,7 @@ decode_attention_kernel(const DecodeParams p) {
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ int s_last;
 
+    pdl_enter();
     const int row = blockIdx.z;
     if (p.row_q_len[row] != 1) return;
     const int G = p.num_heads / p.num_kv_heads;
@@ -248,8 +249,7 @@ static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t strea
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
-    decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, stream>>>(p);
-    return launch_status();
+    return launch_kernel(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, p);
 }
 
 

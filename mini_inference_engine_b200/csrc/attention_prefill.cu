@@ -39,6 +39,7 @@ prefill_attention_kernel(const PrefillParams p) {
     bf16* v_s = k_s + 2 * PRE_BN * DP;                             // [2][PRE_BN][DP]
     __shared__ int s_row, s_q0;
 
+    pdl_enter();
     if (threadIdx.x == 0) {
         // tiles are numbered from the end of each row backwards so that the tiles with the longest
         // key range start first
@@ -222,8 +223,7 @@ static int launch_prefill(const PrefillParams& p, int num_tokens, cudaStream_t s
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid((num_tokens + PRE_BM - 1) / PRE_BM + p.num_rows, p.num_heads);
-    prefill_attention_kernel<D><<<grid, PRE_WARPS * 32, smem, stream>>>(p);
-    return launch_status();
+    return launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), smem, stream, p);
 }
 
 // Rows with fewer than `min_q_len` new tokens are skipped (the decode kernel serves single tokens).

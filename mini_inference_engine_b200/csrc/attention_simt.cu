@@ -59,6 +59,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     float* k_s = q_s + ATT_WARPS * D;           // [ATT_KEYS][DP]
     float* v_s = k_s + ATT_KEYS * DP;           // [ATT_KEYS][DP]
 
+    pdl_enter();
     // which row and query tile is this block's?
     if (threadIdx.x == 0) {
         int tile = blockIdx.x, r = 0;
@@ -195,19 +196,17 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
     if (act_tag == MIE_F32) {
         e = cudaFuncSetAttribute(paged_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        paged_attention_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
+        return launch_kernel(paged_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
             page_size, page_shift, scale, window, QT, HG, min_q_len);
     } else if (act_tag == MIE_BF16) {
         e = cudaFuncSetAttribute(paged_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        paged_attention_kernel<bf16><<<grid, ATT_WARPS * 32, smem, stream>>>(
+        return launch_kernel(paged_attention_kernel<bf16>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (bf16*)out, num_heads, num_kv_heads, head_dim,
             page_size, page_shift, scale, window, QT, HG, min_q_len);
-    } else {
-        return MIE_ERR_BAD_ARG;
     }
-    return launch_status();
+    return MIE_ERR_BAD_ARG;
 }

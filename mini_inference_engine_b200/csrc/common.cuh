@@ -60,3 +60,39 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  Every kernel of this package starts with pdl_enter(): it lets the
+// next kernel in the stream be scheduled at once (its blocks become resident and run their own
+// prologue) and then waits until the kernels before it have completed and their writes are visible.
+// What is gained is the launch gap between dependent kernels; what keeps it correct is that no
+// kernel reads or writes global memory before its wait, and that every block of every kernel
+// waits, so "the kernel before me is complete" carries over the whole chain.  Launched without the
+// attribute (MIE_B200_PDL=0), both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_launch_dependents(); pdl_wait(); }
+
+#include <stdlib.h>
+static inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("MIE_B200_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v == 1;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return e != cudaSuccess ? (int)e : launch_status();
+}

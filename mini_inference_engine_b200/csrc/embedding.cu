@@ -6,6 +6,7 @@
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
+    pdl_enter();
     const int t = blockIdx.x;
     int id = ids[t];
     // ids are checked on the host when a request is added; the clamp only keeps a bad id from
@@ -22,10 +23,8 @@ extern "C" int mie_embedding(const void* table, int table_tag, const int* ids, f
     if (hidden <= 0 || vocab <= 0) return MIE_ERR_BAD_ARG;
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     if (table_tag == MIE_F32)
-        embedding_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+        return launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, hidden, vocab);
     else if (table_tag == MIE_BF16)
-        embedding_kernel<bf16><<<num_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
-    else
-        return MIE_ERR_BAD_ARG;
-    return launch_status();
+        return launch_kernel(embedding_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab);
+    return MIE_ERR_BAD_ARG;
 }

@@ -52,6 +52,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_tiled_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const void* __restrict__ bias,
                   int bias_tag, TC* __restrict__ C, int M, int N, int K, bool vec_a, bool vec_w) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
+    pdl_enter();
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Ws[BK][BN + 4];
     const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
@@ -107,6 +108,7 @@ template <typename TA, typename TW, typename TC, int ROWS>
 __global__ void __launch_bounds__(256)
 gemm_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const void* __restrict__ bias,
                  int bias_tag, TC* __restrict__ C, int M, int N, int K, bool vec_ok) {
+    pdl_enter();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
     const int m0 = blockIdx.y * ROWS;
@@ -156,18 +158,17 @@ static int launch_gemm(const void* A, const void* W, const void* bias, int bias_
     if (M <= 16) {
         constexpr int ROWS = 8;
         const dim3 grid((N + 7) / 8, (M + ROWS - 1) / ROWS);
-        gemm_rows_kernel<TA, TW, TC, ROWS><<<grid, 256, 0, stream>>>(
-            (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a && al_w);
+        return launch_kernel(gemm_rows_kernel<TA, TW, TC, ROWS>, grid, dim3(256), 0, stream,
+                             (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a && al_w);
     } else if (M <= 192 || N < 128) {
         const dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_tiled_kernel<TA, TW, TC, 64, 64, 4, 4><<<grid, 256, 0, stream>>>(
-            (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a, al_w);
+        return launch_kernel(gemm_tiled_kernel<TA, TW, TC, 64, 64, 4, 4>, grid, dim3(256), 0, stream,
+                             (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a, al_w);
     } else {
         const dim3 grid((N + 127) / 128, (M + 127) / 128);
-        gemm_tiled_kernel<TA, TW, TC, 128, 128, 8, 8><<<grid, 256, 0, stream>>>(
-            (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a, al_w);
+        return launch_kernel(gemm_tiled_kernel<TA, TW, TC, 128, 128, 8, 8>, grid, dim3(256), 0, stream,
+                             (const TA*)A, (const TW*)W, bias, bias_tag, (TC*)C, M, N, K, al_a, al_w);
     }
-    return launch_status();
 }
 
 // Tags: MIE_F32 / MIE_BF16 for x, W and y.  bias may be null.

@@ -168,11 +168,17 @@ __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.w
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+// The address of `local_addr` (a shared::cta address of this block) in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// Plain (not volatile) so that the loads of all ranks are in flight together; ordering against the
+// peers' writes comes from the cluster barrier before the first load.
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+    float4 v;
+    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
@@ -191,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    constexpr int RED_LD = BN + 1;                            // padded row of the float32 partial tile
+    constexpr int RED_LD = BN + 4;                            // padded row of the float32 partial tile, 16-byte aligned
     const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;        // swizzled tiles sit on 1024-byte lines
     unsigned char* tiles = smem_dyn + (tiles_base - smem_u32(smem_dyn));
 
@@ -346,37 +352,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         const int S = p.splits;
         const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
         const int r_lo = split * rows_per;
-        const uint32_t red_addr = tiles_base;
         if (warp >= 2 && !aborted) {
             const int tid = threadIdx.x - 64;                // 0..127
-            if (!SWAPPED) {
-                // rows are tokens, columns output features: consecutive threads take consecutive columns
-                const int pairs = p.swiglu ? 2 : 1;
-                for (int idx = tid; idx < rows_per * (BN / pairs); idx += 128) {
-                    const int rr = r_lo + idx / (BN / pairs), c = (idx % (BN / pairs)) * pairs;
+            uint32_t peer[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) peer[s] = cluster_addr(tiles_base, s < S ? s : 0);
+            // one thread: one row of the tile, four consecutive columns, summed over the blocks in rank order
+            for (int idx = tid; idx < rows_per * (BN / 4); idx += 128) {
+                int rr, c;
+                if (SWAPPED) { rr = r_lo + idx % rows_per; c = (idx / rows_per) * 4; }     // neighbours: consecutive features
+                else { rr = r_lo + idx / (BN / 4); c = (idx % (BN / 4)) * 4; }             // neighbours: consecutive columns
+                const uint32_t off = (uint32_t)(rr * RED_LD + c) * 4u;
+                float4 part[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s) if (s < S) part[s] = ld_cluster_f32x4(peer[s] + off);
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < S) { acc[0] += part[s].x; acc[1] += part[s].y; acc[2] += part[s].z; acc[3] += part[s].w; }
+                if (!SWAPPED) {
                     const int m = a0 + rr, n = b0 + c;
                     if (m >= p.M || n >= p.N) continue;
-                    float acc[2] = {0.f, 0.f};
-                    for (int s = 0; s < S; ++s)
-                        for (int j = 0; j < pairs; ++j) acc[j] += ld_cluster_f32(red_addr + (rr * RED_LD + c + j) * 4, s);
-                    if (p.bias) for (int j = 0; j < pairs; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
-                    if (p.swiglu) store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
-                    else store_out<OUT_F32>(p.out, (int64_t)m * p.N + n, acc[0]);
-                }
-            } else {
-                // rows are output features, columns tokens: consecutive threads take consecutive features
-                const int pairs = p.swiglu ? 2 : 1;
-                const int feats = rows_per / pairs;
-                for (int idx = tid; idx < feats * BN; idx += 128) {
-                    const int t = b0 + idx / feats, rr = r_lo + (idx % feats) * pairs;
-                    const int n = a0 + rr, c = idx / feats;
-                    if (t >= p.M || n >= p.N) continue;
-                    float acc[2] = {0.f, 0.f};
-                    for (int s = 0; s < S; ++s)
-                        for (int j = 0; j < pairs; ++j) acc[j] += ld_cluster_f32(red_addr + ((rr + j) * RED_LD + c) * 4, s);
-                    if (p.bias) for (int j = 0; j < pairs; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
-                    if (p.swiglu) store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
-                    else store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, acc[0]);
+                    if (p.bias) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
+                    }
+                    if (p.swiglu) {
+                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
+                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2 + 1, silu_mul(acc[2], acc[3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) store_out<OUT_F32>(p.out, (int64_t)m * p.N + n + j, acc[j]);
+                    }
+                } else {
+                    const int n = a0 + rr;
+                    const float b = (p.bias && n < p.N) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int t = b0 + c + j;
+                        const float val = acc[j] + b;
+                        if (p.swiglu) {                        // gate on the even feature, up on the odd one: neighbouring threads
+                            const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                            if (!(rr & 1) && t < p.M && n < p.N)
+                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                        } else if (t < p.M && n < p.N) {
+                            store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
+                        }
+                    }
                 }
             }
         }
@@ -434,7 +456,7 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 template <int BN, bool SWAPPED, bool OUT_F32>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int pdl, cudaStream_t stream) {
     size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2);
-    const size_t red = (size_t)TC_BM * (BN + 1) * sizeof(float);           // the partial tile reuses the ring
+    const size_t red = (size_t)TC_BM * (BN + 4) * sizeof(float);           // the partial tile reuses the ring
     if (p.splits > 1 && red > smem) smem = red;
     smem += 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAPPED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

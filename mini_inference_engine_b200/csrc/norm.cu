@@ -16,6 +16,7 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restri
                                    const int* __restrict__ rows, int n, float eps, int use_smem) {
     extern __shared__ float row_cache[];
     __shared__ float red[33];
+    pdl_enter();
     const int b = blockIdx.x;
     const int64_t r = rows ? rows[b] : b;
     float* res_row = res + r * n;
@@ -52,12 +53,10 @@ extern "C" int mie_add_rmsnorm(const void* delta, float* res, const void* w, int
     const int use_smem = smem_bytes <= 40 * 1024;
     const size_t smem = use_smem ? smem_bytes : 0;
     if (act_tag == MIE_F32)
-        add_rmsnorm_kernel<float, float><<<num_rows, threads, smem, stream>>>(
-            (const float*)delta, res, w, w_tag, (float*)out, rows, n, eps, use_smem);
+        return launch_kernel(add_rmsnorm_kernel<float, float>, dim3(num_rows), dim3(threads), smem, stream,
+                             (const float*)delta, res, w, w_tag, (float*)out, rows, n, eps, use_smem);
     else if (act_tag == MIE_BF16)
-        add_rmsnorm_kernel<bf16, bf16><<<num_rows, threads, smem, stream>>>(
-            (const bf16*)delta, res, w, w_tag, (bf16*)out, rows, n, eps, use_smem);
-    else
-        return MIE_ERR_BAD_ARG;
-    return launch_status();
+        return launch_kernel(add_rmsnorm_kernel<bf16, bf16>, dim3(num_rows), dim3(threads), smem, stream,
+                             (const bf16*)delta, res, w, w_tag, (bf16*)out, rows, n, eps, use_smem);
+    return MIE_ERR_BAD_ARG;
 }

@@ -38,6 +38,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ v_cache, int num_heads, int num_kv_heads,
                                   int head_dim, int rotary_dim, int page_size, int max_pos,
                                   int write_cache) {
+    pdl_enter();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
     int pos = positions[t];
@@ -87,14 +88,12 @@ extern "C" int mie_rope_cache_write(void* qkv, int act_tag, const int* positions
     int threads = 64;
     while (threads < 512 && threads < work) threads <<= 1;
     if (act_tag == MIE_F32)
-        rope_cache_kernel<float><<<num_tokens, threads, 0, stream>>>(
+        return launch_kernel(rope_cache_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
             (float*)qkv, positions, slots, cos_t, sin_t, (float*)k_cache, (float*)v_cache, num_heads,
             num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache);
     else if (act_tag == MIE_BF16)
-        rope_cache_kernel<bf16><<<num_tokens, threads, 0, stream>>>(
+        return launch_kernel(rope_cache_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream,
             (bf16*)qkv, positions, slots, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache, num_heads,
             num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache);
-    else
-        return MIE_ERR_BAD_ARG;
-    return launch_status();
+    return MIE_ERR_BAD_ARG;
 }

@@ -19,6 +19,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
                               uint64_t seed, int* __restrict__ out, int vocab) {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
+    pdl_enter();
     const int row = blockIdx.x;
     const float* lg = logits + (int64_t)row * vocab;
     const float t = temperature[row];
@@ -67,6 +68,5 @@ extern "C" int mie_sample(const float* logits, const float* temperature, const i
     if (rows <= 0) return 0;
     if (vocab <= 0) return MIE_ERR_BAD_ARG;
     const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 64);
-    sample_kernel<<<rows, threads, 0, stream>>>(logits, temperature, request, position, seed, out, vocab);
-    return launch_status();
+    return launch_kernel(sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, temperature, request, position, seed, out, vocab);
 }

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from ..config import EngineConfig, load_config
-from ..kernels import ops
+from ..kernels import gemm_tc, ops
 from ..models.decoder import DecoderModel
 from ..parts.base import Runtime
 from ..sampling.params import SamplingParams
@@ -255,6 +255,7 @@ class LLMEngine:
             else:
                 torch.cuda.current_stream().synchronize()
 
+        gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result
         self.num_steps += 1
         for seq, n in batch:
             self.cache.advance(seq.cache, n)

@@ -2,28 +2,41 @@
 
 * float32 activations (the true 32-bit mode), or a weight the checkpoint holds in 32 bits:
   the CUDA-core FMA kernel of ``csrc/gemm_simt.cu``.
-* bfloat16 activations and weights: the tensor-core product.  The reference calls the vendor
-  library for these (F.linear, inference_engine/model.py:172,178,180,181,185); ``LIBRARY`` is that
-  product, and kernels of this package replace it where they are faster (see ``set_bf16_backend``).
+* bfloat16 activations and weights: a tensor-core product.  The reference calls the vendor library
+  for these (F.linear, inference_engine/model.py:172,178,180,181,185).  ``auto`` (the default) uses
+  this package's tcgen05 kernel (``csrc/gemm_tcgen05.cu``) where it is the faster one -- few tokens,
+  i.e. decode steps, where it streams the weights, overlaps their fetch with the kernel before it
+  and fuses SwiGLU -- and the library product for many tokens; ``tcgen05`` and ``library`` force one.
 """
 from __future__ import annotations
 
 import torch
 
-from . import ops
+from . import gemm_tc, ops
 
-_bf16_backend = "library"
+_bf16_backend = "auto"
+AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen05 kernel
 
 
 def set_bf16_backend(name: str) -> None:
     global _bf16_backend
-    if name not in ("library", "simt", "tcgen05"):
+    if name not in ("auto", "library", "simt", "tcgen05"):
         raise ValueError(name)
     _bf16_backend = name
 
 
 def bf16_backend() -> str:
     return _bf16_backend
+
+
+def uses_tcgen05(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16) -> bool:
+    """Whether ``linear`` would run the tcgen05 kernel for these operands."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or _bf16_backend in ("library", "simt"):
+        return False
+    if _bf16_backend == "auto" and x.shape[0] > AUTO_MAX_TOKENS:
+        return False
+    K = x.shape[1]
+    return K % 8 == 0 and w.shape[0] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
@@ -34,10 +47,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> to
         return out
     if x.dtype == torch.float32 or w.dtype == torch.float32 or _bf16_backend == "simt":
         return ops.gemm_simt(x, w, out, bias)
-    if _bf16_backend == "tcgen05":
-        from . import gemm_tc
-        if gemm_tc.supports(x, w, out):
-            return gemm_tc.gemm(x, w, out, bias)
+    if uses_tcgen05(x, w, out_dtype) and gemm_tc.supports(x, w, out):
+        return gemm_tc.gemm(x, w, out, bias)
     if not x.is_cuda:
         raise ops.KernelError("linear runs on CUDA tensors only")
     if out_dtype == torch.bfloat16:
@@ -52,3 +63,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> to
     if bias is not None:
         out += bias
     return out
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for a weight whose rows alternate gate_i, up_i: fused into the
+    tcgen05 product's epilogue where that kernel runs, else the product followed by the SwiGLU kernel."""
+    M, inter = x.shape[0], w_interleaved.shape[0] // 2
+    out = torch.empty(M, inter, dtype=out_dtype, device=x.device)
+    if M == 0:
+        return out
+    if uses_tcgen05(x, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and gemm_tc.supports(x, w_interleaved, out):
+        return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
+    gu = linear(x, w_interleaved, None, out_dtype)
+    return ops.swiglu(gu, out, interleaved=True)

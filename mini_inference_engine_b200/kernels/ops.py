@@ -243,13 +243,14 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
 
 # --------------------------------------------------------------------------- activation
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]; with ``interleaved`` gate and up alternate:
+    out[:, i] = silu(gate_up[:, 2i]) * gate_up[:, 2i + 1]."""
     T, two_i = gate_up.shape
     _need(two_i % 2 == 0 and out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype
           and out.is_contiguous() and gate_up.is_contiguous(), "swiglu shapes/types do not match")
     lib = build.load("activation")
-    _check(lib.mie_swiglu(_ptr(gate_up), _ptr(out), tag(out), T, two_i // 2, _stream()), "swiglu")
+    _check(lib.mie_swiglu(_ptr(gate_up), _ptr(out), tag(out), T, two_i // 2, int(interleaved), _stream()), "swiglu")
     return out
 
 

@@ -480,3 +480,12 @@ def test_gemm_tc_refuses_what_it_cannot_align():
     assert not gemm_tc.supports(x, w, torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(gemm_tc.GemmTcError):
         gemm_tc.gemm(x, w, torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
+
+
+def test_swiglu_interleaved(ops):
+    torch.manual_seed(2)
+    g, u = torch.randn(13, 176) * 3, torch.randn(13, 176) * 3
+    gu = torch.stack((g, u), 2).reshape(13, 352).bfloat16().to(DEV)
+    out = torch.empty(13, 176, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gu, out, interleaved=True)
+    close(out, pl.swiglu(g.bfloat16(), u.bfloat16()), torch.bfloat16, "interleaved swiglu")
