@@ -12,19 +12,23 @@
 //   grid = (splits, kv heads x head chunks, rows).  A block owns one request row, one kv head, up
 //   to 16 query heads of its group (the MMA's 16 rows) and one contiguous part of the context.
 //   Keys and values arrive in tiles of 64 positions through cp.async into padded shared memory
-//   (two stages); warp w multiplies positions 16w..16w+15 of each tile, keeping its own running
+//   (three or four stages in flight); warp w multiplies positions 16w..16w+15 of each tile, keeping its own running
 //   max / sum / output, and the four warps are merged once at the end.
 //   scores, softmax and accumulators are float32; P is rounded to bfloat16 for the P.V product, as
 //   in the reference (decode_attention.py:69).
 //
-// With more than one split, each block writes its normalised partial output and its base-2
-// log-sum-exp to scratch memory and bumps a counter of its (row, kv head, chunk); the block that
-// sees the count complete merges all partials (weights 2^(lse_s - max)) and resets the counter, so
-// the scratch needs no clearing between launches.  Rows with q_len != 1 are left to the prefill
+// Merging the splits, two ways.  (1) 2, 4 or 8 splits and no scratch given: the splits of a
+// (row, kv head, chunk) are launched as one thread-block cluster; each block leaves its normalised
+// output and base-2 log-sum-exp in shared memory, the cluster synchronises, and every block merges
+// its share of the outputs straight out of the others' shared memory (weights 2^(lse_s - max)).
+// No global round trip, no atomics.  (2) Any number of splits with scratch memory: each block writes
+// its partial output and log-sum-exp to the scratch and bumps a counter of its unit; the block that
+// sees the count complete merges all partials and resets the counter, so the scratch needs no
+// clearing between launches.  Rows with q_len != 1 are left to the prefill
 // kernel (their blocks exit at once).
 #include "attention_decode.cuh"
 
-// Scratch (needed when splits > 1): part_o float32 [rows * heads * splits * head_dim], part_lse
+// Scratch (optional; without it splits must be 1, 2, 4 or 8): part_o float32 [rows * heads * splits * head_dim], part_lse
 // float32 [rows * heads * splits], counters int32 [rows * kv_heads * chunks], the counters zero
 // before the first launch (the kernel leaves them zero).
 extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,

@@ -7,6 +7,7 @@
 #define DEC_WARPS 4
 #define DEC_TILE 64
 #define DEC_MAX_D 128
+#define DEC_PAGE_SLOTS 1024
 
 struct DecodeParams {
     const bf16* q; int64_t q_stride;
@@ -16,18 +17,24 @@ struct DecodeParams {
     bf16* out;
     float* part_o; float* part_lse; int* counters;      // scratch (splits > 1)
     int num_heads, num_kv_heads, page_size, page_shift, window, splits, chunks;
+    int cluster;             // 1: the splits of a (row, kv head, chunk) are a thread-block cluster and merge through shared memory
     float scale_log2e;
 };
+
+template <int D> struct DecodeStages { static constexpr int value = D <= 64 ? 4 : 3; };
 
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const DecodeParams p) {
     constexpr int DP = D + 8;                    // padded row: ldmatrix rows fall into different banks
     constexpr int KSTEPS = D / 16, NBLK = D / 8;
+    constexpr int NSTAGE = DecodeStages<D>::value;               // tiles in flight: the loop is bound by memory latency
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [2][DEC_TILE][DP]
-    bf16* v_s = k_s + 2 * DEC_TILE * DP;                           // [2][DEC_TILE][DP]
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [NSTAGE][DEC_TILE][DP]
+    bf16* v_s = k_s + NSTAGE * DEC_TILE * DP;                      // [NSTAGE][DEC_TILE][DP]
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
+    __shared__ __align__(16) float c_lse[16];
+    __shared__ int s_pages[DEC_PAGE_SLOTS];                        // this block's page ids, fetched once
     __shared__ int s_last;
 
     pdl_enter();
@@ -70,7 +77,13 @@ decode_attention_kernel(const DecodeParams p) {
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+    // The page ids of this block's part go to shared memory first: a lookup in global memory inside the
+    // tile loop would put a memory round trip in front of every tile's copies.
     const int* table = p.block_tables + (int64_t)row * p.table_stride;
+    const int first_page = kbeg >> p.page_shift;
+    const int n_pages = ntiles > 0 ? ((kend - 1) >> p.page_shift) - first_page + 1 : 0;
+    for (int i = threadIdx.x; i < min(n_pages, DEC_PAGE_SLOTS); i += DEC_WARPS * 32) s_pages[i] = table[first_page + i];
+    __syncthreads();
     constexpr int CHUNKS_PER_ROW = D / 8;                          // 16-byte pieces per key
     auto load_tile = [&](int t, int stage) {
         const int k0 = kbeg + t * DEC_TILE;
@@ -80,7 +93,8 @@ decode_attention_kernel(const DecodeParams p) {
             const int r = idx / CHUNKS_PER_ROW, c = (idx - r * CHUNKS_PER_ROW) * 8;
             const int key = k0 + r;
             if (key < kend) {
-                const int page = table[key >> p.page_shift];
+                const int pi = (key >> p.page_shift) - first_page;
+                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1))) * D + c;
                 cp_async16(kd + r * DP + c, p.k_cache + src);
                 cp_async16(vd + r * DP + c, p.v_cache + src);
@@ -91,13 +105,16 @@ decode_attention_kernel(const DecodeParams p) {
         }
     };
 
-    if (ntiles > 0) load_tile(0, 0);
-    cp_async_commit();
-    for (int t = 0; t < ntiles; ++t) {
-        const int stage = t & 1;
-        if (t + 1 < ntiles) load_tile(t + 1, stage ^ 1);
+#pragma unroll
+    for (int t = 0; t < NSTAGE - 1; ++t) {
+        if (t < ntiles) load_tile(t, t);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (int t = 0; t < ntiles; ++t) {
+        const int stage = t % NSTAGE;
+        if (t + NSTAGE - 1 < ntiles) load_tile(t + NSTAGE - 1, (t + NSTAGE - 1) % NSTAGE);
+        cp_async_commit();
+        cp_async_wait<NSTAGE - 1>();                               // tile t has landed; NSTAGE - 1 younger ones may be in flight
         __syncthreads();
         const bf16* kt = k_s + stage * DEC_TILE * DP + warp * 16 * DP;
         const bf16* vt = v_s + stage * DEC_TILE * DP + warp * 16 * DP;
@@ -188,6 +205,7 @@ decode_attention_kernel(const DecodeParams p) {
     }
     __syncthreads();
     const int unit = (row * p.num_kv_heads + kvh) * p.chunks + chunk;
+    float* c_o = o_s + DEC_WARPS * 16 * D;                         // [16][D]: this block's normalised output (cluster merge)
     for (int idx = threadIdx.x; idx < gn * D; idx += DEC_WARPS * 32) {
         const int g = idx / D, d = idx - g * D;
         float mm = -INFINITY;
@@ -206,6 +224,9 @@ decode_attention_kernel(const DecodeParams p) {
         const int head = kvh * G + g0 + g;
         if (p.splits == 1) {
             p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(val);
+        } else if (p.cluster) {
+            c_o[g * D + d] = val;
+            if (d == 0) c_lse[g] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         } else {
             const int64_t slot = ((int64_t)row * p.num_heads + head) * p.splits + split;
             p.part_o[slot * D + d] = val;
@@ -213,6 +234,48 @@ decode_attention_kernel(const DecodeParams p) {
         }
     }
     if (p.splits == 1) return;
+
+    if (p.cluster) {
+        // The splits are the blocks of one cluster: every block merges its share of the outputs
+        // straight out of the others' shared memory, weights 2^(lse_s - max), in rank order.
+        cluster_sync_all();
+        const int S = p.splits;                                    // 2, 4 or 8
+        const int rank = (int)cluster_rank();
+        const uint32_t o_base = (uint32_t)__cvta_generic_to_shared(c_o), l_base = (uint32_t)__cvta_generic_to_shared(c_lse);
+        // one thread: one head, four consecutive dimensions
+        for (int quad_id = threadIdx.x * S + rank; quad_id < gn * (D / 4); quad_id += DEC_WARPS * 32 * S) {
+            const int g = quad_id / (D / 4), d4 = (quad_id - g * (D / 4)) * 4;
+            float lse[8];
+            float4 part[8];
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) {
+                if (s2 < S) {
+                    lse[s2] = ld_cluster_f32(cluster_addr(l_base + g * 4, s2));
+                    part[s2] = ld_cluster_f32x4(cluster_addr(o_base + (g * D + d4) * 4, s2));
+                }
+            }
+            float mm = -INFINITY;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) mm = fmaxf(mm, lse[s2]);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) {
+                if (s2 < S) {
+                    const float w = lse[s2] == -INFINITY ? 0.f : exp2f(lse[s2] - mm);
+                    acc[0] += w * part[s2].x; acc[1] += w * part[s2].y; acc[2] += w * part[s2].z; acc[3] += w * part[s2].w;
+                    wsum += w;
+                }
+            }
+            const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+            const int head = kvh * G + g0 + g;
+            uint2 packed;
+            packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+            packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+            *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d4) = packed;
+        }
+        cluster_sync_all();                                        // nobody leaves while its shared memory is being read
+        return;
+    }
 
     // the last block of this (row, kv head, chunk) merges the splits
     __threadfence();
@@ -245,16 +308,18 @@ decode_attention_kernel(const DecodeParams p) {
 
 template <int D>
 static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t stream) {
-    const size_t smem = (size_t)2 * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
+    const size_t smem = (size_t)DecodeStages<D>::value * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
-    return launch_kernel(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, p);
+    const dim3 cluster(p.cluster ? p.splits : 1, 1, 1);
+    return launch_kernel_cluster(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster, p);
 }
 
 
-// Checks the sizes, fills the parameter block and launches.  `part_o`, `part_lse` and `counters`
-// may be null when splits == 1.
+// Checks the sizes, fills the parameter block and launches.  With splits > 1 and all three scratch
+// pointers null, the splits (2, 4 or 8) form a thread-block cluster and merge through distributed
+// shared memory; with scratch given, any number of splits merges through it.
 static int decode_attention_launch(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                    const int* block_tables, int table_stride, const int* row_q_start,
                                    const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
@@ -265,7 +330,9 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
     if (page_size < 1 || (page_size & (page_size - 1))) return MIE_ERR_BAD_ARG;
-    if (splits < 1 || (splits > 1 && (!part_o || !part_lse || !counters))) return MIE_ERR_BAD_ARG;
+    const bool cluster = splits > 1 && !part_o && !part_lse && !counters;     // no scratch given: merge inside a cluster
+    if (splits < 1 || (splits > 1 && !cluster && (!part_o || !part_lse || !counters))) return MIE_ERR_BAD_ARG;
+    if (cluster && splits != 2 && splits != 4 && splits != 8) return MIE_ERR_BAD_ARG;
     if (num_rows > 65535) return MIE_ERR_TOO_LARGE;
     DecodeParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride;
@@ -276,7 +343,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
-    p.window = window; p.splits = splits;
+    p.window = window; p.splits = splits; p.cluster = cluster ? 1 : 0;
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;

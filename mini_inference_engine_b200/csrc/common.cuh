@@ -79,20 +79,64 @@ static inline bool pdl_enabled() {
     return v == 1;
 }
 
-// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute.
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute and,
+// when `cluster` has more than one block, as thread-block clusters of that shape.
 template <typename... KArgs, typename... Args>
-static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                Args... args) {
+static inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, dim3 cluster, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster.x; attr[n].val.clusterDim.y = cluster.y; attr[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     return e != cudaSuccess ? (int)e : launch_status();
+}
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, dim3(1, 1, 1), args...);
+}
+
+// Thread-block clusters: a barrier over all threads of all blocks of the cluster, and loads from
+// another block's shared memory (distributed shared memory).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address of `local_addr` (a shared::cta address of this block) in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// Plain (not volatile) so that the loads of all ranks are in flight together; ordering against the
+// peers' writes comes from the cluster barrier before the first load.
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+    float4 v;
+    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
 }

@@ -165,22 +165,6 @@ __device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, i
 
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// The address of `local_addr` (a shared::cta address of this block) in block `rank` of the cluster.
-__device__ __forceinline__ uint32_t cluster_addr(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    return remote;
-}
-// Plain (not volatile) so that the loads of all ranks are in flight together; ordering against the
-// peers' writes comes from the cluster barrier before the first load.
-__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
-    float4 v;
-    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 template <int BN, bool SWAPPED, bool OUT_F32>

@@ -205,17 +205,20 @@ def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
     does not give them, never parts shorter than one 64-key tile (the reference's rule keeps 256 keys
     a part, inference_engine/kernels/decode_attention.py:117-125)."""
     blocks = max(1, rows * kv_units)
-    if blocks >= 2 * NUM_SMS:
-        return 1
-    return max(1, min(-(-2 * NUM_SMS // blocks), -(-max_ctx // 64), 64))
+    splits = 1
+    while splits < 8 and blocks * splits < 2 * NUM_SMS and splits * 64 < max_ctx:
+        splits *= 2                      # a cluster of 2, 4 or 8 blocks
+    return splits
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
-                     splits: int | None = None) -> torch.Tensor:
+                     splits: int | None = None, merge: str = "cluster") -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
-    blocks and merged in the same launch).  Rows with more new tokens are skipped."""
+    blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
+    "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
+    splits merged through scratch memory in global memory."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "decode attention is bfloat16")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the decode kernel takes multiples of 16 from 16 to 128")
@@ -228,7 +231,9 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
     if splits is None:
         splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
     part_o = part_lse = counters = None
-    if splits > 1:
+    if merge == "cluster" and splits not in (1, 2, 4, 8):
+        merge = "scratch"
+    if splits > 1 and merge == "scratch":
         part_o = _workspace(q.device, "decode_part_o", rows * num_heads * splits * head_dim, torch.float32)
         part_lse = _workspace(q.device, "decode_part_lse", rows * num_heads * splits, torch.float32)
         counters = _workspace(q.device, "decode_counters", rows * num_kv_heads * chunks, torch.int32)

@@ -276,7 +276,8 @@ def test_sampling_temperature_matches_plain(ops, vocab):
 
 # --------------------------------------------------------------------------- tensor-core decode attention
 
-def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=None, q_lens=None, max_ctx=None):
+def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=None, q_lens=None, max_ctx=None,
+                 merge="cluster"):
     """Rows with one new token each (or q_lens given: rows with more are to be skipped)."""
     dt = torch.bfloat16
     torch.manual_seed(seed)
@@ -315,8 +316,16 @@ def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=
     out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
     ops.decode_attention(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV),
                          q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV), out, H, Hkv, D, page, scale, window,
-                         max_ctx=max_ctx or max(ctxs), splits=splits)
+                         max_ctx=max_ctx or max(ctxs), splits=splits, merge=merge)
     return out, torch.cat(want, 0), q_start.tolist()
+
+
+@pytest.mark.parametrize("merge", ["cluster", "scratch"])
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_decode_attention_merges_through_cluster_or_scratch(ops, splits, merge):
+    for shape in ((32, 4, 64, 16), (16, 1, 128, 16), (6, 2, 48, 32)):
+        out, want, _ = _decode_case(ops, *shape, [700, 33, 1, 512, 65, 2048], splits, merge=merge, seed=splits)
+        close(out, want, torch.bfloat16, f"decode {shape} splits {splits} merged by {merge}")
 
 
 @pytest.mark.parametrize("splits", [None, 1, 3, 8])
