@@ -18,12 +18,56 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// Eight outputs per thread with 16-byte loads and stores (bfloat16, inter % 8 == 0).
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int inter8,
+                                     int interleaved) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / inter8;
+        const int i8 = (int)(idx - t * inter8);
+        const bf16* row = gu + t * 16 * inter8;
+        float g[8], u[8];
+        if (interleaved) {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + 16 * i8), b = *reinterpret_cast<const uint4*>(row + 16 * i8 + 8);
+            const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(ha[j]), y = __bfloat1622float2(hb[j]);
+                g[j] = x.x; u[j] = x.y; g[4 + j] = y.x; u[4 + j] = y.y;
+            }
+        } else {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + 8 * i8), b = *reinterpret_cast<const uint4*>(row + 8 * inter8 + 8 * i8);
+            const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(ha[j]), y = __bfloat1622float2(hb[j]);
+                g[2 * j] = x.x; g[2 * j + 1] = x.y; u[2 * j] = y.x; u[2 * j + 1] = y.y;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            ho[j] = __floats2bfloat162_rn(g[2 * j] / (1.0f + expf(-g[2 * j])) * u[2 * j],
+                                          g[2 * j + 1] / (1.0f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + idx * 8) = o;
+    }
+}
+
 extern "C" int mie_swiglu(const void* gu, void* out, int act_tag, int num_tokens, int inter, int interleaved,
                           cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (inter <= 0) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)num_tokens * inter;
     const int threads = 256;
+    if (act_tag == MIE_BF16 && inter % 8 == 0 && (reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        int64_t blocks8 = (total / 8 + threads - 1) / threads;
+        if (blocks8 > 148 * 16) blocks8 = 148 * 16;
+        return launch_kernel(swiglu_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out,
+                             total / 8, inter / 8, interleaved);
+    }
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (act_tag == MIE_F32)

@@ -75,6 +75,68 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
+// bfloat16 with 16-byte accesses: eight rotation pairs per thread (rotary_dim % 16 == 0, head_dim % 8 == 0).
+__device__ __forceinline__ void rotate8(const uint4& lo, const uint4& hi, const float* cs, const float* sn, uint4& out_lo, uint4& out_hi) {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
+    __nv_bfloat162* oa = reinterpret_cast<__nv_bfloat162*>(&out_lo);
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out_hi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(a[j]), y = __bfloat1622float2(b[j]);
+        const float c0 = cs[2 * j], c1 = cs[2 * j + 1], s0 = sn[2 * j], s1 = sn[2 * j + 1];
+        oa[j] = __floats2bfloat162_rn(x.x * c0 - y.x * s0, x.y * c1 - y.y * s1);
+        ob[j] = __floats2bfloat162_rn(y.x * c0 + x.x * s0, y.y * c1 + x.y * s1);
+    }
+}
+
+__global__ void rope_cache_bf16x8_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int num_heads, int num_kv_heads,
+                                         int head_dim, int rotary_dim, int page_size, int max_pos, int write_cache) {
+    pdl_enter();
+    const int t = blockIdx.x;
+    const int half = rotary_dim >> 1, h8 = half >> 3, d8 = head_dim >> 3, tail8 = (head_dim - rotary_dim) >> 3;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_t + (int64_t)pos * half;
+    const float* sn = sin_t + (int64_t)pos * half;
+    bf16* row = qkv + (int64_t)t * (num_heads + 2 * num_kv_heads) * head_dim;
+    for (int idx = threadIdx.x; idx < num_heads * h8; idx += blockDim.x) {
+        const int h = idx / h8, j = (idx - h * h8) * 8;
+        bf16* x = row + h * head_dim;
+        uint4 lo = *reinterpret_cast<const uint4*>(x + j), hi = *reinterpret_cast<const uint4*>(x + j + half), olo, ohi;
+        rotate8(lo, hi, cs + j, sn + j, olo, ohi);
+        *reinterpret_cast<uint4*>(x + j) = olo;
+        *reinterpret_cast<uint4*>(x + j + half) = ohi;
+    }
+    if (!write_cache) return;
+    const int slot = slots[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    const bf16* k_row = row + num_heads * head_dim;
+    const bf16* v_row = k_row + num_kv_heads * head_dim;
+    for (int idx = threadIdx.x; idx < num_kv_heads * h8; idx += blockDim.x) {
+        const int h = idx / h8, j = (idx - h * h8) * 8;
+        const bf16* x = k_row + h * head_dim;
+        const int64_t dst = (((int64_t)page * num_kv_heads + h) * page_size + off) * head_dim;
+        uint4 lo = *reinterpret_cast<const uint4*>(x + j), hi = *reinterpret_cast<const uint4*>(x + j + half), olo, ohi;
+        rotate8(lo, hi, cs + j, sn + j, olo, ohi);
+        *reinterpret_cast<uint4*>(k_cache + dst + j) = olo;
+        *reinterpret_cast<uint4*>(k_cache + dst + j + half) = ohi;
+    }
+    for (int idx = threadIdx.x; idx < num_kv_heads * (tail8 + d8); idx += blockDim.x) {
+        const int h = idx / (tail8 + d8), c = idx - h * (tail8 + d8);
+        const int64_t dst = (((int64_t)page * num_kv_heads + h) * page_size + off) * head_dim;
+        if (c < tail8) {       // dimensions of k beyond the rotated ones pass through
+            const int d = rotary_dim + c * 8;
+            *reinterpret_cast<uint4*>(k_cache + dst + d) = *reinterpret_cast<const uint4*>(k_row + h * head_dim + d);
+        } else {
+            const int d = (c - tail8) * 8;
+            *reinterpret_cast<uint4*>(v_cache + dst + d) = *reinterpret_cast<const uint4*>(v_row + h * head_dim + d);
+        }
+    }
+}
+
 extern "C" int mie_rope_cache_write(void* qkv, int act_tag, const int* positions, const int* slots,
                                     const float* cos_t, const float* sin_t, void* k_cache, void* v_cache,
                                     int num_tokens, int num_heads, int num_kv_heads, int head_dim,
@@ -87,6 +149,14 @@ extern "C" int mie_rope_cache_write(void* qkv, int act_tag, const int* positions
                                                                              : num_kv_heads * head_dim;
     int threads = 64;
     while (threads < 512 && threads < work) threads <<= 1;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) % 16) == 0;
+    if (act_tag == MIE_BF16 && rotary_dim > 0 && rotary_dim % 16 == 0 && head_dim % 8 == 0 && aligned) {
+        int t8 = 32;
+        while (t8 < 256 && t8 * 8 < work) t8 <<= 1;
+        return launch_kernel(rope_cache_bf16x8_kernel, dim3(num_tokens), dim3(t8), 0, stream, (bf16*)qkv, positions, slots, cos_t,
+                             sin_t, (bf16*)k_cache, (bf16*)v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
+                             max_pos, write_cache);
+    }
     if (act_tag == MIE_F32)
         return launch_kernel(rope_cache_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
             (float*)qkv, positions, slots, cos_t, sin_t, (float*)k_cache, (float*)v_cache, num_heads,
