@@ -1,0 +1,373 @@
+// Paged causal prefill attention on the 5th-generation tensor cores (head_dim 64 or 128, bfloat16).
+//
+// One block = 128 consecutive queries of one request and one query head.  Both products of
+// attention run as tcgen05.mma with accumulators in tensor memory:
+//
+//   S = Q K^T   Q [128 x D] and the key tile [128 keys x D] are K-major tiles in shared memory, brought
+//               by TMA with the 128-byte swizzle -- Q out of the fused qkv activation, keys out of the
+//               cache one page per copy through the request's block table.  S is 128 x 128 float32 in
+//               TMEM: one query row per TMEM lane.
+//   softmax     four warps, one thread per query row: the thread reads its row of S out of TMEM
+//               (tcgen05.ld), masks by position (key <= query, key > query - window), keeps a running
+//               max and sum in base 2, and writes P, rounded to bfloat16, back into TMEM (tcgen05.st).
+//               No shuffles: a row never leaves its thread.
+//   O += P V    P is the A operand straight out of TMEM; V [128 keys x D] sits in shared memory as TMA
+//               wrote it, which for this product is an MN-major B operand.  O is 128 x D float32 in
+//               TMEM; when the running max of a row moves, its thread rescales its row of O in place.
+//
+// The reference does this with a library attention call per prompt portion
+// (inference_engine/model.py:146-158).  A block works through its key tiles one after the other
+// (S, softmax, PV); two blocks share an SM at head_dim 64 (256 TMEM columns and 80 KB of shared
+// memory each), so one block's softmax runs under the other's products.
+//
+// Roles: warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane), warps 2..5 =
+// softmax and epilogue.  Barriers: q_full, kv_full[2] / kv_empty[2] (two key/value stages), s_full
+// (S is complete; also means the PV product before it has finished), p_full (128 arrivals: P is
+// written and O rescaled), o_full.  Every wait is bounded (see tcgen05_common.cuh).
+#include "tcgen05_common.cuh"
+
+#define FA_BM 128
+#define FA_BN 128
+#define FA_THREADS 192
+
+struct FaParams {
+    const int* block_tables; int table_stride;
+    const int* row_q_start; const int* row_q_len; const int* row_ctx_len; int num_rows;
+    bf16* out;
+    int* error;
+    int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
+    float scale_log2e;
+};
+
+// MN-major B operand tile with the 128-byte swizzle: 64 elements of N contiguous in a 128-byte row,
+// one row per k, 8 rows = one 1024-byte swizzle atom.  Stride between atoms along K (stride byte
+// offset) 1024; between 64-element groups along N (leading byte offset) `n_group_bytes`.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t n_group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((n_group_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv activation [tokens, q_stride], box {64, 128}
+                            const __grid_constant__ CUtensorMap map_k,   // key pages as rows [pages * kv_heads * page_size, D], box {64, page rows}
+                            const __grid_constant__ CUtensorMap map_v,
+                            const FaParams p) {
+    constexpr int PARTS = D / 64;                               // 64-column sub-tiles (128 bytes = one swizzle row)
+    constexpr uint32_t SUB_BYTES = 128 * 64 * 2;                // one [128 rows x 64] sub-tile
+    constexpr uint32_t Q_BYTES = PARTS * SUB_BYTES, KV_BYTES = PARTS * SUB_BYTES;
+    constexpr uint32_t TMEM_S = 0, TMEM_P = 128, TMEM_O = 192;  // column offsets: S 128 cols, P 64 cols (bf16 pairs), O D cols
+    constexpr uint32_t TMEM_COLS = D == 64 ? 256 : 512;
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag, s_row, s_q0;
+
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_dyn + (base - smem_u32(smem_dyn));
+    // layout: Q | K stage 0 | V stage 0 | K stage 1 | V stage 1
+    const uint32_t q_addr = base;
+    auto k_addr = [&](int s) { return base + Q_BYTES + (uint32_t)s * 2 * KV_BYTES; };
+    auto v_addr = [&](int s) { return base + Q_BYTES + (uint32_t)s * 2 * KV_BYTES + KV_BYTES; };
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&q_full, 1);
+        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
+        mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
+        mbar_init(&s_full, 1); mbar_init(&p_full, 128); mbar_init(&o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // key/value rows that no copy fills (beyond the context) must hold finite values: 0 * NaN is NaN
+    for (uint32_t i = threadIdx.x * 16; i < 4 * KV_BYTES; i += FA_THREADS * 16)
+        *reinterpret_cast<uint4*>(tiles + Q_BYTES + i) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the TMA unit must see the zeros before it overwrites them
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pdl_wait();                                                  // everything below reads what earlier kernels wrote
+
+    if (threadIdx.x == 0) {
+        // tiles are numbered from the end of each row backwards: the longest key ranges start first
+        int tile = blockIdx.x, r = 0;
+        for (; r < p.num_rows; ++r) {
+            const int ql = p.row_q_len[r];
+            const int tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
+            if (tile < tiles_r) { tile = tiles_r - 1 - tile; break; }
+            tile -= tiles_r;
+        }
+        s_row = r < p.num_rows ? r : -1;
+        s_q0 = tile * FA_BM;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+    const int row = s_row;
+
+    if (row >= 0) {
+        const int q0 = s_q0;
+        const int q_len = p.row_q_len[row], ctx = p.row_ctx_len[row], q_start = p.row_q_start[row];
+        const int head = blockIdx.y;
+        const int kvh = head / (p.num_heads / p.num_kv_heads);
+        const int pos0 = ctx - q_len + q0;                       // position of the tile's first query
+        const int nq = min(FA_BM, q_len - q0);
+        const int k_hi = pos0 + nq;                              // one past the last key any query here reads
+        const int k_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+        const int kbeg = k_lo & ~(FA_BN - 1);
+        const int ntiles = (k_hi - kbeg + FA_BN - 1) / FA_BN;
+        const int rows_per_copy = min(p.page_size, FA_BN);       // one TMA copy = one page (or a 128-row piece of it)
+
+        if (warp == 0) {
+            if (lane == 0) {
+                const int* table = p.block_tables + (int64_t)row * p.table_stride;
+                mbar_expect_tx(&q_full, Q_BYTES);
+#pragma unroll
+                for (int part = 0; part < PARTS; ++part)
+                    tma_load_2d(tiles + part * SUB_BYTES, &map_q, &q_full, head * D + part * 64, q_start + q0);
+                for (int t = 0; t < ntiles; ++t) {
+                    const int s = t & 1, round = t >> 1;
+                    if (!mbar_wait(&kv_empty[s], (round & 1) ^ 1, abort_p)) break;
+                    const int key0 = kbeg + t * FA_BN;
+                    const int key_end = min(key0 + FA_BN, k_hi);
+                    const int copies = (key_end - key0 + rows_per_copy - 1) / rows_per_copy;
+                    mbar_expect_tx(&kv_full[s], (uint32_t)copies * rows_per_copy * 128u * PARTS * 2u);
+                    for (int c = 0; c < copies; ++c) {
+                        const int key = key0 + c * rows_per_copy;
+                        const int page = table[key >> p.page_shift];
+                        const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
+#pragma unroll
+                        for (int part = 0; part < PARTS; ++part) {
+                            const uint32_t off = part * SUB_BYTES + (uint32_t)c * rows_per_copy * 128u;
+                            tma_load_2d(tiles + (k_addr(s) - base) + off, &map_k, &kv_full[s], part * 64, src_row);
+                            tma_load_2d(tiles + (v_addr(s) - base) + off, &map_v, &kv_full[s], part * 64, src_row);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                // S: M 128, N 128, both operands K-major.  PV: M 128, N D, B (values) MN-major.
+                const uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN);
+                const uint32_t idesc_o = umma_idesc_bf16(FA_BM, D) | (1u << 16);
+                bool ok = mbar_wait(&q_full, 0, abort_p);
+                for (int t = 0; t < ntiles && ok; ++t) {
+                    const int s = t & 1, round = t >> 1;
+                    ok = mbar_wait(&kv_full[s], round & 1, abort_p);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t off = (ks / 4) * SUB_BYTES + (ks % 4) * 32;
+                        umma_bf16(tmem_base + TMEM_S, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr(s) + off), idesc_s,
+                                  ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&s_full);                          // S is ready (and the PV before it is done)
+                    ok = mbar_wait(&p_full, t & 1, abort_p);       // P written, O rescaled
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < FA_BN / 16; ++kk) {      // 16 keys per MMA: 8 TMEM columns of P, 2 atoms of V
+                        umma_bf16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + kk * 8,
+                                     umma_desc_sw128_mn(v_addr(s) + kk * 2048, SUB_BYTES), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&kv_empty[s]);                     // the stage may be refilled once these have read it
+                }
+                if (ok) umma_commit(&o_full);
+            }
+        } else {
+            const int q = warp & 3;
+            const int r = q * 32 + lane;                           // this thread's query row within the tile
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const int qpos = pos0 + r;
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int t = 0; t < ntiles && ok; ++t) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full, t & 1, abort_p));     // the warp goes on or gives up as one
+                if (!ok) break;
+                tc_fence_after();
+                const int key0 = kbeg + t * FA_BN;
+                // masks are needed only where the tile touches the diagonal, the window's edge or the range's start
+                const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
+                float mx = -INFINITY;
+                // pass 1: the row maximum
+#pragma unroll 1
+                for (int c = 0; c < FA_BN; c += 16) {
+                    float v[16];
+                    tmem_ld16(lane_addr + TMEM_S + c, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float x = v[i] * p.scale_log2e;
+                        if (need_mask) {
+                            const int key = key0 + c + i;
+                            if (!(key <= qpos && (p.window <= 0 || key > qpos - p.window))) x = -INFINITY;
+                        }
+                        mx = fmaxf(mx, x);
+                    }
+                }
+                const float m_new = fmaxf(m_run, mx);
+                const float alpha = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+                // pass 2: P = 2^(S - max) as bfloat16 into TMEM, and the row sum
+                float sum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < FA_BN; c += 16) {
+                    float v[16];
+                    tmem_ld16(lane_addr + TMEM_S + c, v);
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        float x0 = v[i] * p.scale_log2e, x1 = v[i + 1] * p.scale_log2e;
+                        if (need_mask) {
+                            const int key = key0 + c + i;
+                            if (!(key <= qpos && (p.window <= 0 || key > qpos - p.window))) x0 = -INFINITY;
+                            if (!(key + 1 <= qpos && (p.window <= 0 || key + 1 > qpos - p.window))) x1 = -INFINITY;
+                        }
+                        const float p0 = m_new == -INFINITY ? 0.f : exp2f(x0 - m_new);
+                        const float p1 = m_new == -INFINITY ? 0.f : exp2f(x1 - m_new);
+                        sum += p0 + p1;
+                        packed[i >> 1] = pack2_bf16(p0, p1);
+                    }
+                    tmem_st8(lane_addr + TMEM_P + (c >> 1), packed);
+                }
+                l_run = l_run * alpha + sum;
+                m_run = m_new;
+                // rescale this row of O (the PV product of the tile before has finished: s_full came after it)
+                // (tcgen05.ld / st are warp-wide instructions: the whole warp rescales if any of its rows moved)
+                if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 16) {
+                        float v[16];
+                        tmem_ld16(lane_addr + TMEM_O + c, v);
+                        uint32_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i] * alpha);
+                        tmem_st8(lane_addr + TMEM_O + c, w);
+                        tmem_st8(lane_addr + TMEM_O + c + 8, w + 8);
+                    }
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&p_full);
+            }
+            // epilogue: O / l -> bfloat16 -> out[token, head, :]
+            if (ok) ok = mbar_wait(&o_full, 0, abort_p);
+            tc_fence_after();
+            __syncwarp();
+            if (__all_sync(0xffffffffu, ok)) {                      // warp-wide loads: every lane reads, rows inside the tile store
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                bf16* op = p.out + ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 16) {
+                    float v[16];
+                    tmem_ld16(lane_addr + TMEM_O + c, v);
+                    if (r >= nq) continue;
+                    uint4 w0, w1;
+                    w0.x = pack2_bf16(v[0] * inv, v[1] * inv); w0.y = pack2_bf16(v[2] * inv, v[3] * inv);
+                    w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
+                    w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
+                    w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
+                    *reinterpret_cast<uint4*>(op + c) = w0;
+                    *reinterpret_cast<uint4*>(op + c + 8) = w1;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.error, 1);
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);           // let copies that are still in flight land
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+
+static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride_elems, int box_rows) {
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {row_stride_elems * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int D>
+static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
+                     cudaStream_t stream) {
+    const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 5 + 1024;     // Q + 2 x (K + V)
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const dim3 grid((num_tokens + FA_BM - 1) / FA_BM + p.num_rows, p.num_heads);
+    return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, p);
+}
+
+// q: the fused qkv activation [num_tokens, q_stride] bfloat16 (query head h at columns h*D ..), caches
+// [num_pages, kv_heads, page_size, D] bfloat16, out [num_tokens, heads, D] bfloat16.  head_dim 64 or
+// 128, page_size a power of two >= 8, q_stride % 8 == 0.  Rows with fewer than min_q_len new tokens
+// are skipped.
+extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                        int64_t num_pages, const int* block_tables, int table_stride, const int* row_q_start,
+                                        const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens, void* out,
+                                        int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
+                                        int min_q_len, cudaStream_t stream) {
+    if (num_rows <= 0 || num_tokens <= 0) return 0;
+    if (head_dim != 64 && head_dim != 128) return MIE_ERR_BAD_ARG;
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return MIE_ERR_BAD_ARG;
+    if (page_size < 8 || (page_size & (page_size - 1)) || q_stride % 8) return MIE_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+         reinterpret_cast<uintptr_t>(out)) & 15) return MIE_ERR_BAD_ARG;
+    int rc = tc_setup();
+    if (rc) return rc;
+    FaParams p;
+    p.block_tables = block_tables; p.table_stride = table_stride;
+    p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.num_rows = num_rows;
+    p.out = (bf16*)out; p.error = g_error_dev;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window; p.min_q_len = min_q_len;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    CUtensorMap mq, mk, mv;
+    const int box_rows = page_size < FA_BN ? page_size : FA_BN;
+    const uint64_t cache_rows = (uint64_t)num_pages * num_kv_heads * page_size;
+    if ((rc = make_map_2d(&mq, q, (uint64_t)num_tokens, (uint64_t)q_stride, (uint64_t)q_stride, FA_BM))) return rc;
+    if ((rc = make_map_2d(&mk, k_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
+    if ((rc = make_map_2d(&mv, v_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
+    if (head_dim == 64) return launch_fa<64>(mq, mk, mv, p, num_tokens, stream);
+    return launch_fa<128>(mq, mk, mv, p, num_tokens, stream);
+}
+
+extern "C" int mie_prefill_attention_tc_error(void) { return g_error_host ? *g_error_host : 0; }
+extern "C" void mie_prefill_attention_tc_clear_error(void) { if (g_error_host) *g_error_host = 0; }

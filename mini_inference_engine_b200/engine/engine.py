@@ -255,6 +255,7 @@ class LLMEngine:
             else:
                 torch.cuda.current_stream().synchronize()
 
+        ops.check_tc_errors()
         gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result
         self.num_steps += 1
         for seq, n in batch:

@@ -2,8 +2,9 @@
 
 float32 (the true 32-bit path): the CUDA-core kernel serves every row.
 bfloat16: rows with one new token go to the tensor-core decode kernel (context split across
-blocks), rows with more go to the prefill kernel; head sizes beyond those kernels fall back to the
-CUDA-core kernel, which takes every size up to 256.  ``set_backend("simt")`` forces the CUDA-core
+blocks), rows with more go to a prefill kernel -- the tcgen05 one for head sizes 64 and 128, the
+mma.sync one for the other multiples of 16 up to 128; head sizes beyond those kernels fall back to
+the CUDA-core kernel, which takes every size up to 256.  ``set_backend("simt")`` forces the CUDA-core
 kernel everywhere (used by tests to compare the two)."""
 from __future__ import annotations
 
@@ -12,6 +13,14 @@ import torch
 from . import ops
 
 _backend = "auto"
+_prefill_backend = "tcgen05"
+
+
+def set_prefill_backend(name: str) -> None:
+    global _prefill_backend
+    if name not in ("tcgen05", "mma"):
+        raise ValueError(name)
+    _prefill_backend = name
 
 
 def set_backend(name: str) -> None:
@@ -36,6 +45,8 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
                              max_ctx=ctx.max_ctx_len)
     if has_prefill:
-        ops.prefill_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale,
-                              window, min_q_len=2)
+        # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
+        tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
+        fn = ops.prefill_attention_tc if tc else ops.prefill_attention
+        fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window, min_q_len=2)
     return out

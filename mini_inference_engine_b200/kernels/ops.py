@@ -185,6 +185,39 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
     return out
 
 
+def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
+                         row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         head_dim: int, page_size: int, scale: float, window: int | None = None,
+                         min_q_len: int = 2) -> torch.Tensor:
+    """Causal attention of prompt portions on tcgen05 (S and O in tensor memory, operands by TMA);
+    head_dim 64 or 128."""
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
+    _need(head_dim in (64, 128), f"head_dim {head_dim}: the tcgen05 prefill kernel takes 64 and 128")
+    _need(q_stride % 8 == 0 and page_size >= 8, "the tcgen05 prefill kernel needs q rows and pages of whole 16-byte pieces")
+    _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
+    for t, n in ((block_tables, "block_tables"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"),
+                 (row_ctx_len, "row_ctx_len")):
+        _i32(t, n)
+    _need(out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(), "contiguous caches and output")
+    lib = build.load("attention_prefill_tc")
+    _check(lib.mie_prefill_attention_tc(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
+                                        ctypes.c_int64(k_cache.shape[0]), _ptr(block_tables), block_tables.shape[1],
+                                        _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len), row_q_len.numel(),
+                                        num_tokens, _ptr(out), num_heads, num_kv_heads, head_dim, page_size,
+                                        ctypes.c_float(scale), int(window or 0), int(min_q_len), _stream()),
+           "prefill_attention_tc")
+    return out
+
+
+def check_tc_errors() -> None:
+    """Raises if a block of a tensor-core kernel gave up a bounded wait (call after a synchronise)."""
+    for name, fn in (("attention_prefill_tc", "mie_prefill_attention_tc"),):
+        lib = build._libs.get(name)
+        if lib is not None and getattr(lib, fn + "_error")():
+            getattr(lib, fn + "_clear_error")()
+            raise KernelError(f"a block of {name} gave up waiting on a barrier; its output is not valid")
+
+
 NUM_SMS = 148
 _workspaces: dict = {}
 

@@ -153,9 +153,11 @@ def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None,
     ctx_len = torch.tensor([c for _, c in rows], dtype=torch.int32)
     q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
     out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
-    fn = ops.paged_attention if kernel == "simt" else ops.prefill_attention
+    fn = {"simt": ops.paged_attention, "prefill": ops.prefill_attention, "prefill_tc": ops.prefill_attention_tc}[kernel]
     fn(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV), q_start.to(DEV),
        q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window, min_q_len=min_q_len)
+    torch.cuda.synchronize()
+    ops.check_tc_errors()
     return out, torch.cat(want, 0)
 
 
@@ -498,3 +500,42 @@ def test_swiglu_interleaved(ops):
     out = torch.empty(13, 176, dtype=torch.bfloat16, device=DEV)
     ops.swiglu(gu, out, interleaved=True)
     close(out, pl.swiglu(g.bfloat16(), u.bfloat16()), torch.bfloat16, "interleaved swiglu")
+
+
+# --------------------------------------------------------------------------- tcgen05 prefill attention
+
+@pytest.mark.parametrize("rows", [[(5, 5)], [(128, 128)], [(129, 129)], [(300, 300)], [(5, 5), (17, 17), (33, 33)],
+                                  [(7, 40), (2, 18), (1, 129), (16, 16), (31, 300)], [(2, 2), (127, 127), (128, 128), (257, 257)],
+                                  [(2048, 2048)], [(2, 1000), (64, 1024), (100, 2047), (200, 700)]])
+def test_prefill_attention_tc_ragged(ops, rows):
+    out, want = _paged_case(ops, torch.bfloat16, 32, 4, 64, 16, rows, kernel="prefill_tc")
+    close(out, want, torch.bfloat16, f"tcgen05 prefill rows {rows}")
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 64, 16), (3, 1, 64, 32), (6, 6, 128, 16), (16, 1, 128, 64), (8, 2, 64, 128),
+                                          (2, 2, 128, 8)])
+def test_prefill_attention_tc_head_shapes(ops, H, Hkv, D, page):
+    out, want = _paged_case(ops, torch.bfloat16, H, Hkv, D, page, [(1, 70), (9, 41), (135, 135), (2, 2), (270, 400)],
+                            seed=H + D, kernel="prefill_tc")
+    close(out, want, torch.bfloat16, f"tcgen05 prefill H{H} Hkv{Hkv} D{D} page{page}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 128, 129, 200])
+def test_prefill_attention_tc_window_edges(ops, window):
+    out, want = _paged_case(ops, torch.bfloat16, 4, 2, 64, 16, [(1, 90), (20, 60), (150, 150), (70, 300), (2, 3), (400, 400)],
+                            window=window, seed=window, kernel="prefill_tc")
+    close(out, want, torch.bfloat16, f"tcgen05 prefill window {window}")
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 127, 128, 511, 777])
+def test_prefill_attention_tc_one_far_key(ops, far):
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(100, 800), (3, 800)], boost=far, seed=far, kernel="prefill_tc")
+    assert (want[99] - 5.0).abs().max() < 1e-3
+    close(out, want, torch.bfloat16, f"tcgen05 prefill far key {far}")
+
+
+def test_prefill_attention_tc_skips_single_token_rows(ops):
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(1, 100), (5, 50), (1, 300), (2, 7)], kernel="prefill_tc", min_q_len=2)
+    assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
+    close(out[1:6], want[1:6], torch.bfloat16, "row 1")
+    close(out[7:9], want[7:9], torch.bfloat16, "row 3")
