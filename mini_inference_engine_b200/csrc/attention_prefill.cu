@@ -18,6 +18,7 @@
 #define PRE_BM 64
 #define PRE_BN 64
 #define PRE_MAX_D 128
+#define PRE_PAGE_SLOTS 1024
 
 struct PrefillParams {
     const bf16* q; int64_t q_stride;
@@ -38,6 +39,7 @@ prefill_attention_kernel(const PrefillParams p) {
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [2][PRE_BN][DP]
     bf16* v_s = k_s + 2 * PRE_BN * DP;                             // [2][PRE_BN][DP]
     __shared__ int s_row, s_q0;
+    __shared__ int s_pages[PRE_PAGE_SLOTS];                        // this block's page ids, fetched once
 
     pdl_enter();
     if (threadIdx.x == 0) {
@@ -89,7 +91,13 @@ prefill_attention_kernel(const PrefillParams p) {
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+    // page ids go to shared memory first: a look-up in global memory inside the tile loop would put a
+    // memory round trip in front of every tile's copies
     const int* table = p.block_tables + (int64_t)row * p.table_stride;
+    const int first_page = kbeg >> p.page_shift;
+    const int n_pages = ((k_hi - 1) >> p.page_shift) - first_page + 1;
+    for (int i = threadIdx.x; i < min(n_pages, PRE_PAGE_SLOTS); i += PRE_WARPS * 32) s_pages[i] = table[first_page + i];
+    __syncthreads();
     constexpr int CHUNKS_PER_ROW = D / 8;
     auto load_tile = [&](int t, int stage) {
         const int k0 = kbeg + t * PRE_BN;
@@ -99,7 +107,8 @@ prefill_attention_kernel(const PrefillParams p) {
             const int r = idx / CHUNKS_PER_ROW, c = (idx - r * CHUNKS_PER_ROW) * 8;
             const int key = k0 + r;
             if (key >= k_lo && key < k_hi) {
-                const int page = table[key >> p.page_shift];
+                const int pi = (key >> p.page_shift) - first_page;
+                const int page = pi < PRE_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1))) * D + c;
                 cp_async16(kd + r * DP + c, p.k_cache + src);
                 cp_async16(vd + r * DP + c, p.v_cache + src);

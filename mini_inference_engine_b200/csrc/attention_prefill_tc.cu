@@ -22,7 +22,7 @@
 //
 // Roles: warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane), warps 2..5 =
 // softmax and epilogue.  Barriers: q_full, kv_full[2] / kv_empty[2] (two key/value stages), s_full
-// (S is complete; also means the PV product before it has finished), p_full (128 arrivals: P is
+// (S is complete; also means the PV product before it has finished), p_full (one arrival per softmax warp: P is
 // written and O rescaled), o_full.  Every wait is bounded (see tcgen05_common.cuh).
 #include "tcgen05_common.cuh"
 
@@ -66,6 +66,25 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+
+// A quarter of one thread's row of S: 32 float32 columns, asynchronous.  The registers may be read
+// only after tmem_ld_wait(r); passing them through the wait keeps the compiler from using them early.
+__device__ __forceinline__ void tmem_ld32_async(uint32_t addr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) :: "memory");
+}
+// 16 columns (32 entries of P as bfloat16 pairs); completion is awaited by tmem_st_wait().
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" :: "r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv activation [tokens, q_stride], box {64, 128}
@@ -97,7 +116,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
         mbar_init(&q_full, 1);
         mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
         mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
-        mbar_init(&s_full, 1); mbar_init(&p_full, 128); mbar_init(&o_full, 1);
+        mbar_init(&s_full, 1); mbar_init(&p_full, 4); mbar_init(&o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -144,29 +163,44 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
         const int rows_per_copy = min(p.page_size, FA_BN);       // one TMA copy = one page (or a 128-row piece of it)
 
         if (warp == 0) {
+            // The producer warp: lane c issues the copies of page c of a tile, and fetches the page id
+            // of the NEXT tile one tile ahead, so that no look-up in global memory sits between a
+            // freed stage and its refill.
+            const int* table = p.block_tables + (int64_t)row * p.table_stride;
             if (lane == 0) {
-                const int* table = p.block_tables + (int64_t)row * p.table_stride;
                 mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
                 for (int part = 0; part < PARTS; ++part)
                     tma_load_2d(tiles + part * SUB_BYTES, &map_q, &q_full, head * D + part * 64, q_start + q0);
-                for (int t = 0; t < ntiles; ++t) {
-                    const int s = t & 1, round = t >> 1;
-                    if (!mbar_wait(&kv_empty[s], (round & 1) ^ 1, abort_p)) break;
-                    const int key0 = kbeg + t * FA_BN;
-                    const int key_end = min(key0 + FA_BN, k_hi);
-                    const int copies = (key_end - key0 + rows_per_copy - 1) / rows_per_copy;
-                    mbar_expect_tx(&kv_full[s], (uint32_t)copies * rows_per_copy * 128u * PARTS * 2u);
-                    for (int c = 0; c < copies; ++c) {
-                        const int key = key0 + c * rows_per_copy;
-                        const int page = table[key >> p.page_shift];
-                        const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
+            }
+            auto copies_of = [&](int t) {
+                const int key0 = kbeg + t * FA_BN;
+                return (min(key0 + FA_BN, k_hi) - key0 + rows_per_copy - 1) / rows_per_copy;
+            };
+            auto page_of = [&](int t) {                           // lane's page id in tile t (0 if it has no copy there)
+                const int key = kbeg + t * FA_BN + lane * rows_per_copy;
+                return (t < ntiles && lane < copies_of(t)) ? table[key >> p.page_shift] : 0;
+            };
+            int page_next = page_of(0);
+            for (int t = 0; t < ntiles; ++t) {
+                const int s = t & 1, round = t >> 1;
+                const int page = page_next;
+                page_next = page_of(t + 1);
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(&kv_empty[s], (round & 1) ^ 1, abort_p) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const int copies = copies_of(t);
+                if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)copies * rows_per_copy * 128u * PARTS * 2u);
+                __syncwarp();
+                if (lane < copies) {
+                    const int key = kbeg + t * FA_BN + lane * rows_per_copy;
+                    const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
 #pragma unroll
-                        for (int part = 0; part < PARTS; ++part) {
-                            const uint32_t off = part * SUB_BYTES + (uint32_t)c * rows_per_copy * 128u;
-                            tma_load_2d(tiles + (k_addr(s) - base) + off, &map_k, &kv_full[s], part * 64, src_row);
-                            tma_load_2d(tiles + (v_addr(s) - base) + off, &map_v, &kv_full[s], part * 64, src_row);
-                        }
+                    for (int part = 0; part < PARTS; ++part) {
+                        const uint32_t off = part * SUB_BYTES + (uint32_t)lane * rows_per_copy * 128u;
+                        tma_load_2d(tiles + (k_addr(s) - base) + off, &map_k, &kv_full[s], part * 64, src_row);
+                        tma_load_2d(tiles + (v_addr(s) - base) + off, &map_v, &kv_full[s], part * 64, src_row);
                     }
                 }
             }
@@ -214,48 +248,76 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 const int key0 = kbeg + t * FA_BN;
                 // masks are needed only where the tile touches the diagonal, the window's edge or the range's start
                 const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
-                float mx = -INFINITY;
-                // pass 1: the row maximum
-#pragma unroll 1
-                for (int c = 0; c < FA_BN; c += 16) {
-                    float v[16];
-                    tmem_ld16(lane_addr + TMEM_S + c, v);
+                // The row of S comes out of TMEM in four chunks of 32 columns; the load of the next chunk is
+                // in flight while the current one is worked on.
+                auto for_each_chunk = [&](auto&& body) {
+                    uint32_t ca[32], cb[32];
+                    tmem_ld32_async(lane_addr + TMEM_S, ca);
+                    tmem_ld_wait(ca);
+                    tmem_ld32_async(lane_addr + TMEM_S + 32, cb);
+                    body(0, ca);
+                    tmem_ld_wait(cb);
+                    tmem_ld32_async(lane_addr + TMEM_S + 64, ca);
+                    body(1, cb);
+                    tmem_ld_wait(ca);
+                    tmem_ld32_async(lane_addr + TMEM_S + 96, cb);
+                    body(2, ca);
+                    tmem_ld_wait(cb);
+                    body(3, cb);
+                };
+                auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
+                // Reference point of the exponent.  Reading S once per tile is what matters here (TMEM
+                // loads are the slowest part of the step), so the running max is not recomputed up front:
+                // P is formed against the running max as it stands, the row's true max is found on the
+                // way, and only if some entry would exceed 2^8 is the tile redone against the new max
+                // (then O and l are rescaled).  The first tile has no running max and takes a max pass.
+                if (t == 0) {
+                    float mx = -INFINITY;
+                    for_each_chunk([&](int ch, const uint32_t* c) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float x = v[i] * p.scale_log2e;
-                        if (need_mask) {
-                            const int key = key0 + c + i;
-                            if (!(key <= qpos && (p.window <= 0 || key > qpos - p.window))) x = -INFINITY;
+                        for (int i = 0; i < 32; ++i) {
+                            float x = __uint_as_float(c[i]);
+                            if (need_mask && masked(key0 + ch * 32 + i)) x = -INFINITY;
+                            mx = fmaxf(mx, x);
                         }
-                        mx = fmaxf(mx, x);
-                    }
+                    });
+                    m_run = mx * p.scale_log2e;                    // the scale is positive: max and scaling commute
                 }
-                const float m_new = fmaxf(m_run, mx);
-                const float alpha = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-                // pass 2: P = 2^(S - max) as bfloat16 into TMEM, and the row sum
-                float sum = 0.f;
-#pragma unroll 1
-                for (int c = 0; c < FA_BN; c += 16) {
-                    float v[16];
-                    tmem_ld16(lane_addr + TMEM_S + c, v);
-                    uint32_t packed[8];
+                float alpha = 1.f, sum = 0.f;
+                for (int attempt = 0; attempt < 2; ++attempt) {
+                    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+                    // four independent sums and maxima: one warp per scheduler has nothing else to hide
+                    // the latency of a dependent chain behind
+                    float xm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, sm[4] = {0.f, 0.f, 0.f, 0.f};
+                    for_each_chunk([&](int ch, const uint32_t* c) {
+                        uint32_t packed[16];
 #pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        float x0 = v[i] * p.scale_log2e, x1 = v[i + 1] * p.scale_log2e;
-                        if (need_mask) {
-                            const int key = key0 + c + i;
-                            if (!(key <= qpos && (p.window <= 0 || key > qpos - p.window))) x0 = -INFINITY;
-                            if (!(key + 1 <= qpos && (p.window <= 0 || key + 1 > qpos - p.window))) x1 = -INFINITY;
+                        for (int i = 0; i < 32; i += 2) {
+                            float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
+                            float x1 = fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
+                            if (need_mask) {
+                                if (masked(key0 + ch * 32 + i)) x0 = -INFINITY;
+                                if (masked(key0 + ch * 32 + i + 1)) x1 = -INFINITY;
+                            }
+                            xm[(i >> 1) & 3] = fmaxf(xm[(i >> 1) & 3], fmaxf(x0, x1));
+                            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                            sm[(i >> 1) & 3] += p0 + p1;
+                            packed[i >> 1] = pack2_bf16(p0, p1);
                         }
-                        const float p0 = m_new == -INFINITY ? 0.f : exp2f(x0 - m_new);
-                        const float p1 = m_new == -INFINITY ? 0.f : exp2f(x1 - m_new);
-                        sum += p0 + p1;
-                        packed[i >> 1] = pack2_bf16(p0, p1);
+                        tmem_st16(lane_addr + TMEM_P + ch * 16, packed);
+                    });
+                    const float xmax = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
+                    sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+                    // the running max moves only when it has to (warp-wide decision: the loads are warp-wide)
+                    const bool moved = xmax > 8.0f || (m_run == -INFINITY && xmax > -INFINITY);
+                    if (attempt == 1 || !__any_sync(0xffffffffu, moved)) break;
+                    if (moved) {
+                        const float m_new = (m_run == -INFINITY ? 0.f : m_run) + xmax;
+                        alpha = m_run == -INFINITY ? 1.f : ex2_approx(m_run - m_new);
+                        m_run = m_new;
                     }
-                    tmem_st8(lane_addr + TMEM_P + (c >> 1), packed);
                 }
                 l_run = l_run * alpha + sum;
-                m_run = m_new;
                 // rescale this row of O (the PV product of the tile before has finished: s_full came after it)
                 // (tcgen05.ld / st are warp-wide instructions: the whole warp rescales if any of its rows moved)
                 if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -272,7 +334,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 }
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&p_full);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full);              // one arrival per warp
             }
             // epilogue: O / l -> bfloat16 -> out[token, head, :]
             if (ok) ok = mbar_wait(&o_full, 0, abort_p);

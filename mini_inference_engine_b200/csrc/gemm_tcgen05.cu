@@ -32,7 +32,7 @@
 // `stages` shared-memory slots is handed back and forth through mbarriers: full[s] (TMA bytes have
 // landed) and empty[s] (tcgen05.commit: the MMAs that read the slot are done).
 //
-// Every wait on an mbarrier is bounded: after WAIT_LIMIT_NS the block raises an error word in
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT_CYCLES the block raises an error word in
 // host-visible memory, stops issuing work, lets copies in flight land, still takes part in the
 // cluster's barriers, frees its TMEM and returns.
 #include "tcgen05_common.cuh"

@@ -7,7 +7,7 @@
 
 #include "common.cuh"
 
-#define WAIT_LIMIT_NS 2000000000ull     // 2 s
+#define WAIT_LIMIT_CYCLES 4000000000ll   // about 2 s of SM clock
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -27,22 +27,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: bounded in TIME (a poll of try_wait may itself block for an implementation-defined
-// while, so a poll count bounds nothing).  False when WAIT_LIMIT_NS ran out here or another role of
-// the block gave up.  The limit is far above any legitimate wait (a kernel launched early by
-// programmatic dependent launch may wait for as long as its predecessor runs).
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// while, so a poll count bounds nothing), measured with the SM's cycle counter (cheap to read, unlike
+// the global timer).  False when WAIT_LIMIT_CYCLES ran out here or another role of the block gave up.
+// The limit (about two seconds) is far above any legitimate wait: a kernel launched early by
+// programmatic dependent launch may wait for as long as its predecessor runs.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 15u) == 0u) {
+        if ((i & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
         }
     }
     *abort_flag = 1;
