@@ -98,6 +98,7 @@ def decode_point(eng, batch, context, steps, warmup, e2e=False):
         eng.step()
     for _ in range(warmup):
         eng.step()
+    eng.drain()
     bucket = next(s for s in eng.graph_sizes if s >= batch)
     g = eng.graphs[bucket]
     out = {}
@@ -116,10 +117,12 @@ def decode_point(eng, batch, context, steps, warmup, e2e=False):
         t0 = time.perf_counter()
         for _ in range(steps):
             eng.step()
+        eng.drain()
         torch.cuda.synchronize()
         out["e2e_ms"] = (time.perf_counter() - t0) * 1e3 / steps
         out["h2d"] = (eng.h2d_bytes - h0) // steps
         out["d2h"] = (eng.d2h_bytes - d0) // steps
+    eng.drain()
     for s in list(eng.scheduler.running):
         eng.scheduler.finish(s)
     return out
@@ -136,11 +139,12 @@ def prefill_point(eng, tokens, steps, warmup):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         eng.step()
+        eng.drain()
         end.record()
         torch.cuda.synchronize()
         if i >= warmup:
             times.append(start.elapsed_time(end))
-        assert not eng.scheduler.has_work()
+        assert not eng.has_work()
     return statistics.median(times)
 
 

@@ -82,9 +82,10 @@ def decode_latency(eng, batch: int, prompt: int, steps: int) -> float:
     for _ in range(steps):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        eng.step()                       # ends with the read of the sampled tokens, so it is synchronous
+        eng.step()
+        eng.drain()                      # read this step's tokens: the measurement is of one whole step
         times.append(time.perf_counter() - t0)
-    while eng.scheduler.has_work():
+    while eng.has_work():
         eng.step()
     return statistics.median(times) * 1e3
 

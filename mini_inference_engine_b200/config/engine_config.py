@@ -20,6 +20,7 @@ class EngineConfig:
     cuda_graph_batch_sizes: tuple = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256)
     num_blocks: int | None = None           # explicit pool size in pages (page 0 included); None = from memory
     seed: int = 0                           # sampling seed
+    overlap_steps: bool = True              # launch step N+1 before reading step N's tokens (they are fed back on the device)
 
     def __post_init__(self):
         if self.block_size < 16 or self.block_size & (self.block_size - 1) or self.block_size > 128:

@@ -25,7 +25,7 @@ from ..sampling.sampler import Sampler
 from ..weights import read_model_folder
 from .runner import ModelRunner
 from .scheduler import Scheduler
-from .sequence import Sequence
+from .sequence import Sequence, Status
 
 ACTIVATION_RESERVE = 768 * 2 ** 20      # kept free for activations when sizing the cache (inference_engine/engine.py:51)
 
@@ -38,6 +38,16 @@ class RequestOutput:
     text: str | None
     ttft: float | None          # seconds from arrival to the first generated token
     latency: float | None       # seconds from arrival to the end
+
+
+PENDING = -1          # in token_ids: a token that the step in flight is sampling
+
+
+class _InFlight:
+    """A launched step whose sampled tokens the host has not read yet."""
+
+    def __init__(self, seqs, places, ending, pinned, event):
+        self.seqs, self.places, self.ending, self.pinned, self.event = seqs, places, ending, pinned, event
 
 
 class _DecodeGraph:
@@ -100,8 +110,11 @@ class LLMEngine:
             from transformers import AutoTokenizer          # text in/out only; never on the token path
             self.tokenizer = AutoTokenizer.from_pretrained(model)
 
-        self._pinned_tokens = torch.empty(max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs, 256),
-                                          dtype=torch.int32, pin_memory=True)
+        most = max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs, 256, *self.cfg.cuda_graph_batch_sizes)
+        self._pinned_tokens = [torch.empty(most, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._sampled = torch.zeros(most, dtype=torch.int32, device=self.device)     # the last step's tokens, on the device
+        self._turn = 0
+        self._in_flight = None
         self.graphs: dict = {}
         self.graph_sizes: list = []
         self.num_steps = 0
@@ -147,7 +160,8 @@ class LLMEngine:
             layout["max_ctx_len"] = self.cfg.max_model_len          # static bound for kernels that plan by it
             static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
             ctx = b.to_device(buf, layout, into=static)
-            tokens = torch.zeros(bs, dtype=torch.int32, device=self.device)
+            ctx.token_feedback = self._sampled
+            tokens = self._sampled[:bs]
             self._forward_and_sample(ctx, tokens)                   # warm-up: builds kernels, sizes buffers
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -189,19 +203,47 @@ class LLMEngine:
         return seq
 
     # ------------------------------------------------------------------ one engine step
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._in_flight is not None
+
     @torch.inference_mode()
     def step(self) -> list:
-        """One scheduling + model step; returns the requests that finished in it."""
+        """One scheduling + model step; returns the requests whose end became known in it.
+
+        With ``overlap_steps`` the host runs one step ahead of the device: step N+1 is scheduled,
+        packed and launched while step N still runs, and only then are step N's tokens read.  The
+        tokens a step samples stay on the device and are fed to the next step there (a token id
+        -(k+1) in the batch means "entry k of the previous step's samples"), so nothing but the stop
+        rules waits for the host: a request that ends by count is known beforehand, one that ends by
+        EOS runs one step too many, whose token is dropped."""
+        launched = self._launch()
+        finished = self._complete(self._in_flight) if self._in_flight is not None else []
+        self._in_flight = launched
+        # nothing to run ahead of: read the step's tokens now (also keeps the reference's loop
+        # `while engine.scheduler.has_work(): engine.step()` complete)
+        if launched is not None and (not self.cfg.overlap_steps or not self.scheduler.has_work()):
+            finished += self.drain()
+        return finished
+
+    def drain(self) -> list:
+        """Reads the tokens of the step in flight, if any; returns the requests that ended with it."""
+        fl, self._in_flight = self._in_flight, None
+        return self._complete(fl) if fl is not None else []
+
+    def _launch(self):
         with _nvtx_range("schedule"):
             batch = self.scheduler.schedule()
         if not batch:
-            return []
+            return None
         with _nvtx_range("prepare"):
             rows, sample_seqs = [], []
             for seq, n in batch:
                 nc = seq.num_computed
                 last = nc + n == seq.num_tokens
-                rows.append(self.runner.make_row(seq.cache, seq.token_ids[nc:nc + n], [n - 1] if last else []))
+                tokens = seq.token_ids[nc:nc + n]
+                if tokens[-1] == PENDING:                  # sampled by the step in flight: read on the device
+                    tokens[-1] = -(seq.pending_index + 1)
+                rows.append(self.runner.make_row(seq.cache, tokens, [n - 1] if last else []))
                 if last:
                     sample_seqs.append(seq)
             extras = self._sampling_extras(
@@ -216,6 +258,7 @@ class LLMEngine:
 
         with _nvtx_range("forward"):
             b = self.runner.builder
+            k = len(sample_seqs)
             if use_graph:
                 bs = next(s for s in self.graph_sizes if s >= len(batch))
                 g = self.graphs[bs]
@@ -224,52 +267,65 @@ class LLMEngine:
                 assert layout["size"] == g.layout["size"]
                 b.to_device(buf, g.layout, into=g.buffer)
                 g.graph.replay()
-                tokens = g.tokens
                 self.num_graph_steps += 1
                 self.h2d_bytes += buf.nbytes
             else:
                 buf, layout = b.pack(rows, extras=extras)
                 ctx = b.to_device(buf, layout)
+                ctx.token_feedback = self._sampled
                 self.h2d_bytes += buf.nbytes
                 logits = self.model.step(ctx)
-                tokens = None
                 if sample_seqs and len(seeds) <= 1:
-                    tokens = self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
-                                                 ctx.extras["out_position"],
-                                                 seed=next(iter(seeds)) if seeds else None)
+                    self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
+                                        ctx.extras["out_position"], out=self._sampled[:k],
+                                        seed=next(iter(seeds)) if seeds else None)
                 elif sample_seqs:           # requests with different seeds of their own: one launch per row
-                    tokens = torch.empty(len(sample_seqs), dtype=torch.int32, device=self.device)
                     for i, sd in enumerate(row_seeds):
                         self.sampler.sample(logits[i:i + 1], ctx.extras["temperature"][i:i + 1],
                                             ctx.extras["request"][i:i + 1], ctx.extras["out_position"][i:i + 1],
-                                            out=tokens[i:i + 1], seed=sd)
-
-        with _nvtx_range("sample"):
-            new_tokens = []
-            if sample_seqs:
-                k = len(sample_seqs)
-                self._pinned_tokens[:k].copy_(tokens[:k], non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                new_tokens = self._pinned_tokens[:k].tolist()
+                                            out=self._sampled[i:i + 1], seed=sd)
+            self._turn ^= 1
+            pinned = self._pinned_tokens[self._turn]
+            if k:
+                pinned[:k].copy_(self._sampled[:k], non_blocking=True)
                 self.d2h_bytes += 4 * k
-            else:
-                torch.cuda.current_stream().synchronize()
+            done_event = torch.cuda.Event()
+            done_event.record()
 
-        ops.check_tc_errors()
-        gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result
+        # bookkeeping that does not need the tokens: progress, the place each token will take, and the
+        # requests that end by count with this step
         self.num_steps += 1
         for seq, n in batch:
             self.cache.advance(seq.cache, n)
+        ending = []
+        for i, seq in enumerate(sample_seqs):
+            seq.pending_index = i
+            seq.token_ids.append(PENDING)
+            if seq.num_output_tokens >= seq.params.max_tokens or seq.num_tokens >= self.cfg.max_model_len:
+                self.scheduler.finish(seq)                 # its pages may go to the next step: that one runs after this one
+                ending.append(seq)
+        return _InFlight(sample_seqs, [s.num_tokens - 1 for s in sample_seqs], ending, pinned, done_event)
+
+    def _complete(self, fl) -> list:
+        with _nvtx_range("sample"):
+            fl.event.synchronize()
+            new_tokens = fl.pinned[:len(fl.seqs)].tolist()
+        ops.check_tc_errors()
+        gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result
         now = time.perf_counter()
         finished = []
-        for seq, tok in zip(sample_seqs, new_tokens):
-            seq.token_ids.append(tok)
+        for seq, place, tok in zip(fl.seqs, fl.places, new_tokens):
+            if seq.status is Status.FINISHED and seq not in fl.ending:
+                del seq.token_ids[place:]                  # it ended by EOS a step ago: this token is one too many
+                continue
+            seq.token_ids[place] = tok
             if seq.first_token_time is None:
                 seq.first_token_time = now
-            done = (seq.num_output_tokens >= seq.params.max_tokens
-                    or seq.num_tokens >= self.cfg.max_model_len
-                    or (tok == self.eos_token_id and not seq.params.ignore_eos))    # inference_engine/engine.py:222-224
-            if done:
+            if seq in fl.ending:
+                seq.finish_time = now
+                finished.append(seq)
+            elif tok == self.eos_token_id and not seq.params.ignore_eos:      # inference_engine/engine.py:222-224
+                del seq.token_ids[place + 1:]              # a token pending from the step already in flight
                 seq.finish_time = now
                 self.scheduler.finish(seq)
                 finished.append(seq)
@@ -282,7 +338,7 @@ class LLMEngine:
         if len(params) != len(prompts):
             raise ValueError("one SamplingParams per prompt")
         seqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         outs = []
         for s in seqs:

@@ -115,6 +115,11 @@ class Scheduler:
         return decodes + prefills
 
     def finish(self, seq: Sequence) -> None:
+        """Ends a request wherever it is: running (its pages and slot go back) or waiting again after
+        a preemption (it holds nothing)."""
+        if seq.status is Status.RUNNING:
+            self.running.remove(seq)
+            self.cache.free(seq.cache)
+        elif seq.status is Status.WAITING and seq in self.waiting:
+            self.waiting.remove(seq)
         seq.status = Status.FINISHED
-        self.running.remove(seq)
-        self.cache.free(seq.cache)

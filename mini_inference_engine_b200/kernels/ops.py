@@ -65,15 +65,18 @@ def _i32(t, name):
 
 # --------------------------------------------------------------------------- embedding
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[ids[t]] as float32 (the residual stream)."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, feedback: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] as float32 (the residual stream).  An id -(k+1) is replaced on the device
+    by ``feedback[k]`` (a token the previous step sampled and the host has not read yet)."""
+    if feedback is not None:
+        _i32(feedback, "feedback")
     _i32(ids, "ids")
     V, h = table.shape
     _need(out.dtype == torch.float32 and out.shape == (ids.numel(), h) and out.is_contiguous(),
           "embedding output must be contiguous float32 [tokens, hidden]")
     _need(table.is_contiguous(), "embedding table must be contiguous")
     lib = build.load("embedding")
-    _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(out), ids.numel(), h, V, _stream()),
+    _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(feedback), _ptr(out), ids.numel(), h, V, _stream()),
            "embedding")
     return out
 

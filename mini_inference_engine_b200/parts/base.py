@@ -105,6 +105,7 @@ class StepContext:
     max_ctx_len: int = 1
     host: dict = field(default_factory=dict)
     extras: dict = field(default_factory=dict)   # small per-step device arrays that rode along (sampling inputs)
+    token_feedback: torch.Tensor | None = None   # int32: tokens the previous step sampled; a token id -(k+1) means entry k
 
 
 class Runtime:

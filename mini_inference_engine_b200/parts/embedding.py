@@ -23,7 +23,7 @@ class Embedding(Part):
 
     def forward(self, ctx):
         res = self.rt.empty(ctx.num_tokens, self.hidden_size, dtype=torch.float32)
-        return ops.embedding(self.weight, ctx.token_ids, res)
+        return ops.embedding(self.weight, ctx.token_ids, res, ctx.token_feedback)
 
 
 class LinearHead(Part):

@@ -164,7 +164,43 @@ def test_step_api_and_counters(model_folders):
     a = eng.add_request([1, 2, 3], SamplingParams(max_tokens=2, ignore_eos=True))
     b = eng.add_request([4] * 20, SamplingParams(max_tokens=3, ignore_eos=True))
     finished = []
-    while eng.scheduler.has_work():
+    while eng.has_work():
         finished += eng.step()
     assert finished == [a, b] and a.num_output_tokens == 2 and b.num_output_tokens == 3
     assert eng.num_steps == 3 and eng.h2d_bytes > 0 and eng.d2h_bytes == 4 * 5
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_overlapped_steps_give_the_same_tokens_and_stop_at_eos(overlap, model_folders, tmp_path):
+    """With overlapped steps the host launches step N+1 before it reads step N's tokens (they are fed
+    back on the device).  Tokens must not change, a request that ends by EOS must not keep the token
+    of the step that was already in flight, and the reference's loop over scheduler.has_work() must
+    still see every end."""
+    import json
+    import os
+    import shutil
+    from mini_inference_engine_b200 import SamplingParams
+    folder = model_folders["tiny_a"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(5)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (9, 30, 2, 17)]
+    plain = [pl.generate(cfg, W, p, 14) for p in prompts]
+    eos = plain[1][6]                                   # request 1 meets EOS at its 7th token (or earlier)
+    d = str(tmp_path / "m")
+    shutil.copytree(folder, d)
+    with open(os.path.join(d, "config.json")) as f:
+        c = json.load(f)
+    c["eos_token_id"] = eos
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(c, f)
+    want = [o[:o.index(eos) + 1] if eos in o else o for o in plain]
+    eng = engine_for(d, torch.float32, overlap_steps=overlap, max_num_batched_tokens=16, num_blocks=9)
+    seqs = [eng.add_request(p, SamplingParams(max_tokens=14)) for p in prompts]
+    finished = []
+    while eng.scheduler.has_work():
+        finished += eng.step()
+    assert sorted(s.seq_id for s in finished) == sorted(s.seq_id for s in seqs)
+    assert [s.output_ids for s in seqs] == want
+    assert all(s.finish_time is not None and s.first_token_time is not None for s in seqs)
+    eng.cache.check()
+    assert eng.cache.num_free() == eng.cache.pools[0].num_usable and not eng.has_work()
