@@ -315,7 +315,7 @@ class LLMEngine:
         now = time.perf_counter()
         finished = []
         for seq, place, tok in zip(fl.seqs, fl.places, new_tokens):
-            if seq.status is Status.FINISHED and seq not in fl.ending:
+            if seq.ended_by_eos:
                 del seq.token_ids[place:]                  # it ended by EOS a step ago: this token is one too many
                 continue
             seq.token_ids[place] = tok
@@ -326,6 +326,7 @@ class LLMEngine:
                 finished.append(seq)
             elif tok == self.eos_token_id and not seq.params.ignore_eos:      # inference_engine/engine.py:222-224
                 del seq.token_ids[place + 1:]              # a token pending from the step already in flight
+                seq.ended_by_eos = True
                 seq.finish_time = now
                 self.scheduler.finish(seq)
                 finished.append(seq)

@@ -31,6 +31,8 @@ class Sequence:
         self.arrival_time = time.perf_counter()
         self.first_token_time: float | None = None
         self.finish_time: float | None = None
+        self.pending_index = 0           # where the step in flight will leave this request's next token
+        self.ended_by_eos = False        # ended by EOS while a further step was already in flight
 
     @property
     def num_computed(self) -> int:

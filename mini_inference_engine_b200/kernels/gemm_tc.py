@@ -14,6 +14,7 @@ from . import build, ops
 NUM_SMS = 148
 SMEM_BUDGET = 226 * 1024
 TWO_PER_SM = 112 * 1024
+THREE_PER_SM = 75 * 1024
 
 
 class GemmTcError(RuntimeError):
@@ -43,10 +44,11 @@ def plan(M: int, N: int, K: int) -> dict:
         tiles = -(-M // 128) * -(-N // bn)
     stage = 128 * 64 * 2 + bn * 64 * 2
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= 2 * NUM_SMS and k_tiles // (splits * 2) >= 2:
+    while splits < 8 and tiles * splits * 2 <= 3 * NUM_SMS and k_tiles // (splits * 2) >= 2:
         splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
     per_split = -(-k_tiles // splits)
-    stages = max(2, min(8, per_split, (TWO_PER_SM - 1024) // stage))
+    budget = THREE_PER_SM if tiles * splits > 2 * NUM_SMS else TWO_PER_SM      # all blocks resident at once
+    stages = max(2, min(8, per_split, (budget - 1024) // stage))
     if stages < 3 and per_split > 2:
         stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024) // stage))
     return dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
