@@ -30,14 +30,15 @@
 
 // Scratch (optional; without it splits must be 1, 2, 4 or 8): part_o float32 [rows * heads * splits * head_dim], part_lse
 // float32 [rows * heads * splits], counters int32 [rows * kv_heads * chunks], the counters zero
-// before the first launch (the kernel leaves them zero).
+// before the first launch (the kernel leaves them zero).  `stages`: key/value tiles in flight per
+// block (2, 3 or 4; 0 = 4).
 extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_tables, int table_stride, const int* row_q_start,
                                     const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                     int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                     int window, int splits, float* part_o, float* part_lse, int* counters,
-                                    cudaStream_t stream) {
+                                    int stages, cudaStream_t stream) {
     return decode_attention_launch(q, q_stride, k_cache, v_cache, block_tables, table_stride, row_q_start, row_q_len,
                                    row_ctx_len, num_rows, out, num_heads, num_kv_heads, head_dim, page_size, scale,
-                                   window, splits, part_o, part_lse, counters, stream);
+                                   window, splits, part_o, part_lse, counters, stream, stages);
 }

@@ -17,18 +17,17 @@ struct DecodeParams {
     bf16* out;
     float* part_o; float* part_lse; int* counters;      // scratch (splits > 1)
     int num_heads, num_kv_heads, page_size, page_shift, window, splits, chunks;
+    int stages;              // tiles in flight per block (2, 3 or 4)
     int cluster;             // 1: the splits of a (row, kv head, chunk) are a thread-block cluster and merge through shared memory
     float scale_log2e;
 };
 
-template <int D> struct DecodeStages { static constexpr int value = D <= 64 ? 4 : 3; };
 
-template <int D>
+template <int D, int NSTAGE>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const DecodeParams p) {
     constexpr int DP = D + 8;                    // padded row: ldmatrix rows fall into different banks
     constexpr int KSTEPS = D / 16, NBLK = D / 8;
-    constexpr int NSTAGE = DecodeStages<D>::value;               // tiles in flight: the loop is bound by memory latency
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [NSTAGE][DEC_TILE][DP]
     bf16* v_s = k_s + NSTAGE * DEC_TILE * DP;                      // [NSTAGE][DEC_TILE][DP]
@@ -306,14 +305,26 @@ decode_attention_kernel(const DecodeParams p) {
     }
 }
 
-template <int D>
-static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t stream) {
-    const size_t smem = (size_t)DecodeStages<D>::value * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int D, int NSTAGE>
+static int launch_decode_stages(const DecodeParams& p, int num_rows, cudaStream_t stream) {
+    // at least the four-warp merge buffer (4 x 16 x D float32) plus the block's output (16 x D) must fit
+    size_t smem = (size_t)NSTAGE * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
+    const size_t merge = (size_t)(DEC_WARPS + 1) * 16 * D * sizeof(float);
+    if (smem < merge) smem = merge;
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
     const dim3 cluster(p.cluster ? p.splits : 1, 1, 1);
-    return launch_kernel_cluster(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster, p);
+    return launch_kernel_cluster(decode_attention_kernel<D, NSTAGE>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster, p);
+}
+
+// Tiles in flight per block.  Few tiles per block (short contexts, many splits): two stages, so that
+// more blocks share an SM and hide one another's latencies.  Many tiles per block: a deeper ring.
+template <int D>
+static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t stream) {
+    if (p.stages <= 2) return launch_decode_stages<D, 2>(p, num_rows, stream);
+    if (p.stages == 3 || D > 64) return launch_decode_stages<D, 3>(p, num_rows, stream);
+    return launch_decode_stages<D, 4>(p, num_rows, stream);
 }
 
 
@@ -325,7 +336,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                    int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, int stages = 0) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -344,6 +355,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.splits = splits; p.cluster = cluster ? 1 : 0;
+    p.stages = stages > 0 ? stages : 4;
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;

@@ -23,6 +23,12 @@
 // tiles first and only then waits for the predecessor (griddepcontrol.wait) to fetch the activations:
 // the weight stream of one product overlaps the tail of the kernel before it.
 //
+// Optional rotation epilogue for the fused q|k|v projection (few tokens, split-K): the block that adds
+// up a row of the tile also adds up the row's rotation partner (rotate-half pairs are half a head
+// apart, inside the same 128-row tile when the head size divides 128), rotates by the token's
+// position, and writes q to the activation and k, v straight into their cache pages -- the work of the
+// separate rotation kernel (inference_engine/model.py:174-176,130-134), on float32 sums.
+//
 // Optional SwiGLU epilogue: with gate and up rows interleaved in W (row 2i = gate_i, row 2i+1 = up_i)
 // the epilogue writes silu(gate) * up, N/2 wide, from the float32 accumulators
 // (inference_engine/model.py:180-181 does this with two more kernels on rounded values).
@@ -51,6 +57,16 @@ struct TcParams {
     int M, N, K;             // tokens, output features (rows of W), inner size
     int k_tiles, tiles_per_split, splits, stages;
     int swiglu;              // 1: rows 2i / 2i+1 of W are gate_i / up_i; the output is silu(gate) * up, N/2 wide
+    // Optional fused rotation + cache write for a q|k|v projection (see the header comment): rows of W
+    // are [heads*D of q | kv_heads*D of k | kv_heads*D of v]; q is rotated and written to `out`, k is
+    // rotated and v copied into their cache pages at slots[token]; the k and v columns of `out` are not
+    // written.
+    int rope;
+    const int* positions; const int* slots;
+    const float* cos_t; const float* sin_t;          // [max_pos, rotary_dim / 2]
+    bf16* k_cache; bf16* v_cache;                    // [pages, kv_heads, page_size, head_dim]
+    int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
+    uint32_t rope_smem_offset;                       // where the rotation's tables start inside dynamic shared memory
 };
 
 template <bool OUT_F32>
@@ -102,6 +118,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     constexpr int RED_LD = BN + 4;                            // padded row of the float32 partial tile, 16-byte aligned
     const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;        // swizzled tiles sit on 1024-byte lines
     unsigned char* tiles = smem_dyn + (tiles_base - smem_u32(smem_dyn));
+    // behind the ring (only with the rotation epilogue): positions, slots, cos | sin rows of the tile's tokens
+    int* rope_pos = reinterpret_cast<int*>(tiles + p.rope_smem_offset);
+    int* rope_slot = rope_pos + BN;
+    float* rope_cs = reinterpret_cast<float*>(rope_slot + BN);
 
     grid_dep_launch_dependents();                             // the next kernel may start its own prologue now
 
@@ -178,6 +198,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         // epilogue: warp q reads TMEM lanes 32q .. 32q+31; thread r owns row r of the MMA tile
         const int q = warp & 3;
         const int r = q * 32 + lane;
+        if (p.rope) {
+            // what the rotation needs of this step -- positions, cache slots and the cos/sin rows of the
+            // tile's tokens -- goes to shared memory now, while the weights stream, so that no look-up in
+            // global memory is left for the end of the kernel
+            grid_dep_wait();
+            const int half = p.rotary_dim >> 1, et = threadIdx.x - 64;
+            for (int i = et; i < BN; i += 128) {
+                const int t = b0 + i;
+                int pos = t < p.M ? p.positions[t] : 0;
+                rope_pos[i] = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+                rope_slot[i] = t < p.M ? p.slots[t] : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
+            for (int i = et; i < BN * half; i += 128) {
+                const int tt = i / half, jj = i - tt * half;
+                rope_cs[i] = p.cos_t[(int64_t)rope_pos[tt] * half + jj];
+                rope_cs[BN * half + i] = p.sin_t[(int64_t)rope_pos[tt] * half + jj];
+            }
+        }
         const bool have_work = n_kt > 0;                     // a split beyond the last k-tile adds a zero tile
         const bool ready = have_work ? mbar_wait(&tmem_full_bar, 0, abort_p) : true;
         tc_fence_after();
@@ -286,6 +325,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 #pragma unroll
                         for (int j = 0; j < 4; ++j) store_out<OUT_F32>(p.out, (int64_t)m * p.N + n + j, acc[j]);
                     }
+                } else if (p.rope) {
+                    const int n = a0 + rr;
+                    if (n < p.N) {
+                        const int D = p.head_dim, half = p.rotary_dim >> 1;
+                        const int hd = n / D, d = n - hd * D;                 // head (over q, k, v together) and place in it
+                        const bool rotated = hd < p.num_heads + p.num_kv_heads && d < p.rotary_dim;
+                        float pacc[4] = {0.f, 0.f, 0.f, 0.f};
+                        int np = n;
+                        if (rotated) {                                       // the partner row: half a rotation apart, same tile
+                            np = d < half ? n + half : n - half;
+                            const uint32_t poff = (uint32_t)((rr + (np - n)) * RED_LD + c) * 4u;
+                            float4 pp[8];
+#pragma unroll
+                            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) pp[s2] = ld_cluster_f32x4(peer[s2] + poff);
+#pragma unroll
+                            for (int s2 = 0; s2 < 8; ++s2)
+                                if (s2 < S) { pacc[0] += pp[s2].x; pacc[1] += pp[s2].y; pacc[2] += pp[s2].z; pacc[3] += pp[s2].w; }
+                        }
+                        const float b = p.bias ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+                        const float bp = (p.bias && rotated) ? load_tagged(p.bias, np, p.bias_tag) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int t = b0 + c + j;
+                            if (t >= p.M) continue;
+                            float val = acc[j] + b;
+                            if (rotated) {
+                                const int jj = d < half ? d : d - half;
+                                const float cs = rope_cs[(c + j) * half + jj], sn = rope_cs[BN * half + (c + j) * half + jj];
+                                const float other = pacc[j] + bp;
+                                val = d < half ? val * cs - other * sn : val * cs + other * sn;
+                            }
+                            if (hd < p.num_heads) {
+                                store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
+                            } else if (p.write_cache) {
+                                const int slot = rope_slot[c + j];
+                                const int page = slot / p.page_size, off = slot - page * p.page_size;
+                                const bool is_k = hd < p.num_heads + p.num_kv_heads;
+                                const int kvh = hd - p.num_heads - (is_k ? 0 : p.num_kv_heads);
+                                const int64_t dst = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + off) * D + d;
+                                (is_k ? p.k_cache : p.v_cache)[dst] = __float2bfloat16_rn(val);
+                            }
+                        }
+                    }
                 } else {
                     const int n = a0 + rr;
                     const float b = (p.bias && n < p.N) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
@@ -337,6 +419,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2);
     const size_t red = (size_t)TC_BM * (BN + 4) * sizeof(float);           // the partial tile reuses the ring
     if (p.splits > 1 && red > smem) smem = red;
+    TcParams pp = p;
+    pp.rope_smem_offset = (uint32_t)smem;
+    if (p.rope) smem += (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float);
     smem += 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAPPED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -359,7 +444,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAPPED, OUT_F32>, ma, mb, p);
+    e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAPPED, OUT_F32>, ma, mb, pp);
     return e != cudaSuccess ? (int)e : launch_status();
 }
 
@@ -380,8 +465,14 @@ static int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, con
 // tile (16..256), `splits` in {1, 2, 4, 8} cuts K across a cluster, `pdl` launches with programmatic
 // stream serialization.  Needs K % 8 == 0, N % 8 == 0 (N % 16 == 0 with swiglu) and 16-byte aligned
 // pointers; refuses anything else.
-extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
-                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, cudaStream_t stream) {
+struct RopeFuseArgs {
+    const int* positions; const int* slots; const float* cos_t; const float* sin_t; void* k_cache; void* v_cache;
+    int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
+};
+
+static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
+                          int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, const RopeFuseArgs* rope,
+                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
@@ -392,10 +483,26 @@ extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int b
     TcParams p;
     p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.error = g_error_dev;
     p.M = M; p.N = N; p.K = K; p.swiglu = swiglu;
+    p.rope = 0;
+    if (rope) {
+        // needs the cluster reduction with the weight on the 128-row side, heads that do not straddle tiles
+        if (!swapped || splits < 2 || swiglu || y_tag != MIE_BF16 || rope->head_dim <= 0 || TC_BM % rope->head_dim ||
+            (rope->rotary_dim & 1) || rope->rotary_dim > rope->head_dim ||
+            (rope->num_heads + 2 * rope->num_kv_heads) * rope->head_dim != N)
+            return MIE_ERR_BAD_ARG;
+        if ((size_t)bn * rope->rotary_dim * sizeof(float) > 16 * 1024) return MIE_ERR_BAD_ARG;   // the tables must stay small
+        p.rope = 1;
+        p.positions = rope->positions; p.slots = rope->slots; p.cos_t = rope->cos_t; p.sin_t = rope->sin_t;
+        p.k_cache = (bf16*)rope->k_cache; p.v_cache = (bf16*)rope->v_cache;
+        p.num_heads = rope->num_heads; p.num_kv_heads = rope->num_kv_heads; p.head_dim = rope->head_dim;
+        p.rotary_dim = rope->rotary_dim; p.page_size = rope->page_size; p.max_pos = rope->max_pos;
+        p.write_cache = rope->write_cache;
+    }
     p.k_tiles = (K + TC_BK - 1) / TC_BK;
     while (splits > 1 && splits > p.k_tiles) splits >>= 1;
     p.tiles_per_split = (p.k_tiles + splits - 1) / splits;
     p.splits = splits;             // a block whose range is empty still joins the cluster with a zero tile
+    if (p.rope && p.splits < 2) return MIE_ERR_BAD_ARG;      // the fused rotation lives in the cluster reduction
     p.stages = stages;
     CUtensorMap ma, mb;
     dim3 grid;
@@ -412,6 +519,24 @@ extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int b
     const bool f32 = y_tag == MIE_F32;
     if (swapped) return f32 ? dispatch_bn<true, true>(bn, ma, mb, p, grid, pdl, stream) : dispatch_bn<true, false>(bn, ma, mb, p, grid, pdl, stream);
     return f32 ? dispatch_bn<false, true>(bn, ma, mb, p, grid, pdl, stream) : dispatch_bn<false, false>(bn, ma, mb, p, grid, pdl, stream);
+}
+
+extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
+                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, cudaStream_t stream) {
+    return gemm_tc_launch(x, w, bias, bias_tag, y, y_tag, M, N, K, swapped, bn, splits, stages, swiglu, pdl, nullptr, stream);
+}
+
+// The q|k|v projection with the rotation and the cache write in its epilogue: y [M, N] bfloat16
+// receives the rotated q columns only; rotated k and plain v go to slots[token] of the caches.
+// Needs swapped = 1, splits in {2, 4, 8}, head_dim dividing 128.
+extern "C" int mie_gemm_tc_qkv_rope(const void* x, const void* w, const void* bias, int bias_tag, void* y, int M, int N, int K,
+                                    int bn, int splits, int stages, int pdl, const int* positions, const int* slots,
+                                    const float* cos_t, const float* sin_t, void* k_cache, void* v_cache, int num_heads,
+                                    int num_kv_heads, int head_dim, int rotary_dim, int page_size, int max_pos,
+                                    int write_cache, cudaStream_t stream) {
+    RopeFuseArgs r = {positions, slots, cos_t, sin_t, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim,
+                      page_size, max_pos, write_cache};
+    return gemm_tc_launch(x, w, bias, bias_tag, y, MIE_BF16, M, N, K, 1, bn, splits, stages, 0, pdl, &r, stream);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait.  Reads host memory that the

@@ -14,7 +14,6 @@ from . import build, ops
 NUM_SMS = 148
 SMEM_BUDGET = 226 * 1024
 TWO_PER_SM = 112 * 1024
-THREE_PER_SM = 75 * 1024
 
 
 class GemmTcError(RuntimeError):
@@ -29,6 +28,7 @@ def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
+plan_overrides: dict = {}      # {(N, K): {"splits": .., "stages": ..}} for few-token products: a tuning hook
 pdl_enabled = True      # launch with programmatic stream serialization (see csrc/gemm_tcgen05.cu)
 
 
@@ -44,14 +44,15 @@ def plan(M: int, N: int, K: int) -> dict:
         tiles = -(-M // 128) * -(-N // bn)
     stage = 128 * 64 * 2 + bn * 64 * 2
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= 3 * NUM_SMS and k_tiles // (splits * 2) >= 2:
+    while splits < 8 and tiles * splits * 2 <= 2 * NUM_SMS and k_tiles // (splits * 2) >= 2:
         splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
     per_split = -(-k_tiles // splits)
-    budget = THREE_PER_SM if tiles * splits > 2 * NUM_SMS else TWO_PER_SM      # all blocks resident at once
-    stages = max(2, min(8, per_split, (budget - 1024) // stage))
+    stages = max(2, min(8, per_split, (TWO_PER_SM - 1024) // stage))
     if stages < 3 and per_split > 2:
         stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024) // stage))
-    return dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
+    pl = dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
+    pl.update(plan_overrides.get((N, K), {}) if swapped else {})
+    return pl
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, **force) -> torch.Tensor:
@@ -71,6 +72,42 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu:
                          ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], pl["splits"], pl["stages"],
                          int(swiglu), int(pl.get("pdl", pdl_enabled)), ops._stream())
     ops._check(rc, f"gemm_tc M{M} N{N} K{K} {pl}")
+    return out
+
+
+def can_fuse_rope(x: torch.Tensor, w: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                  rotary_dim: int) -> bool:
+    """Whether the q|k|v projection of ``x`` can rotate and store in its epilogue: the plan must put the
+    weight on the 128-row side and split K (the rotation lives in the cluster reduction), and heads
+    must not straddle 128-row tiles."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or N % 8 or 128 % head_dim or rotary_dim % 2:
+        return False
+    if N != (num_heads + 2 * num_kv_heads) * head_dim:
+        return False
+    pl = plan(M, N, K)
+    return (pl["swapped"] and pl["splits"] >= 2 and -(-K // 64) >= pl["splits"]
+            and pl["bn"] * rotary_dim * 4 <= 16 * 1024)          # the tile's cos/sin rows ride in shared memory
+
+
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias, positions, slots, cos, sin, k_cache, v_cache,
+                  num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                  write_cache: bool = True) -> torch.Tensor:
+    """The fused q|k|v projection with rotation and cache write in the epilogue: ``out`` [M, N] gets the
+    rotated q columns (the k and v columns are left unwritten); rotated k and v go to their pages."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not supports(x, w, out) or not can_fuse_rope(x, w, num_heads, num_kv_heads, head_dim, rotary_dim):
+        raise GemmTcError("these operands cannot take the fused rotation epilogue")
+    pl = plan(M, N, K)
+    lib = build.load("gemm_tcgen05")
+    rc = lib.mie_gemm_tc_qkv_rope(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
+                                  ops._ptr(out), M, N, K, pl["bn"], pl["splits"], pl["stages"], int(pdl_enabled),
+                                  ops._ptr(positions), ops._ptr(slots), ops._ptr(cos), ops._ptr(sin), ops._ptr(k_cache),
+                                  ops._ptr(v_cache), num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
+                                  cos.shape[0], int(write_cache), ops._stream())
+    ops._check(rc, f"gemm_tc_qkv_rope M{M} N{N} K{K} {pl}")
     return out
 
 

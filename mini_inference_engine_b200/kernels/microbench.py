@@ -75,6 +75,22 @@ def cmd_gemm(args):
             byts, flops = N * K * 2 + M * K * 2 + M * N * 2, 2 * M * N * K
             print(f"{name:15s} M={M:5d} N={N:6d} K={K:5d}  tcgen05 {t_ours:8.1f} us ({byts / t_ours / 1e3:6.0f} GB/s, "
                   f"{flops / t_ours / 1e6:7.1f} TFLOP/s)  library {t_lib:8.1f} us  plan {gemm_tc.plan(M, N, K)}", flush=True)
+            H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+            if name == "qkv" and gemm_tc.can_fuse_rope(x, ws[0], H, Hkv, D, D):
+                # the same product with the rotation and the cache write in its epilogue, against product + rotation kernel
+                inv = (1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+                cos, sin = ops.rope_tables(inv, cfg.max_position_embeddings)
+                kc = torch.zeros(M + 2, Hkv, 16, D, device=DEV, dtype=torch.bfloat16)
+                vc = torch.zeros_like(kc)
+                pos = torch.full((M,), 100, dtype=torch.int32, device=DEV)
+                slots = (torch.arange(M, dtype=torch.int32, device=DEV) + 1) * 16
+                fused = lambda i: gemm_tc.gemm_qkv_rope(x, ws[i % copies], y, None, pos, slots, cos, sin, kc, vc, H, Hkv, D, D, 16)  # noqa: E731
+
+                def two(i):
+                    gemm_tc.gemm(x, ws[i % copies], y)
+                    ops.rope_cache_write(y, pos, slots, cos, sin, kc, vc, H, Hkv, D, D, 16)
+                print(f"{'qkv + rotation':15s} M={M:5d} fused epilogue {graph_time_us(fused, copies):8.1f} us   "
+                      f"product then rotation kernel {graph_time_us(two, copies):8.1f} us", flush=True)
         del ws
 
 
@@ -100,7 +116,8 @@ def cmd_decode_attention(args):
         ctx = torch.full((B,), args.context, dtype=torch.int32, device=DEV)
         out = torch.empty(B, H, D, device=DEV, dtype=torch.bfloat16)
         fn = lambda i: ops.decode_attention(qkv, stride, k, v, bt, rows, ones, ctx, out, H, Hkv, D, args.page,   # noqa: E731
-                                            1 / math.sqrt(D), max_ctx=args.max_context or args.context, splits=args.splits)
+                                            1 / math.sqrt(D), max_ctx=args.max_context or args.context, splits=args.splits,
+                                            stages=args.stages)
         if args.once:
             run_plain(fn, 3)
             continue
@@ -185,6 +202,7 @@ def main(argv=None):
     d.add_argument("--context", type=int, default=512)
     d.add_argument("--max-context", type=int, default=0)
     d.add_argument("--splits", type=int, default=None)
+    d.add_argument("--stages", type=int, default=None)
     d.add_argument("--page", type=int, default=16)
     d.set_defaults(fn=cmd_decode_attention)
     p = sub.add_parser("prefill-attention")

@@ -237,20 +237,22 @@ def _workspace(device, name: str, numel: int, dtype) -> torch.Tensor:
 
 
 def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
-    """How many parts to cut the context into: enough blocks for two per SM when the batch alone
-    does not give them, never parts shorter than one 64-key tile (the reference's rule keeps 256 keys
-    a part, inference_engine/kernels/decode_attention.py:117-125)."""
+    """How many parts to cut the context into (a cluster of 2, 4 or 8 blocks).  Splitting pays while the
+    batch alone leaves SMs idle; measured on B200, once rows x kv heads reaches the SM count the
+    cluster launches cost more than they bring (batch 64, 4 kv heads, 512 keys: 12.5 us unsplit, 18.6 us
+    with 2 splits, 50 us with 8).  Parts are never shorter than one 64-key tile (the reference keeps
+    256 keys a part, inference_engine/kernels/decode_attention.py:117-125)."""
     blocks = max(1, rows * kv_units)
     splits = 1
-    while splits < 8 and blocks * splits < 2 * NUM_SMS and splits * 64 < max_ctx:
-        splits *= 2                      # a cluster of 2, 4 or 8 blocks
+    while splits < 8 and blocks * splits * 2 <= 2 * NUM_SMS and splits * 64 < max_ctx:
+        splits *= 2
     return splits
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
-                     splits: int | None = None, merge: str = "cluster") -> torch.Tensor:
+                     splits: int | None = None, merge: str = "cluster", stages: int | None = None) -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
     blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
     "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
@@ -278,7 +280,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                     _ptr(row_ctx_len), rows, _ptr(out), num_heads, num_kv_heads, head_dim,
                                     page_size, ctypes.c_float(scale), int(window or 0), int(splits),
-                                    _ptr(part_o), _ptr(part_lse), _ptr(counters), _stream()), "decode_attention")
+                                    _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0), _stream()),
+           "decode_attention")
     return out
 
 

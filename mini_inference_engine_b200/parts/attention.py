@@ -61,8 +61,7 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.rt.linear(x, self.w_qkv, self.b_qkv)
-        self.position.rotate_and_store(qkv, ctx, cache, H, Hkv)
+        qkv = self.position.project_rotate_and_store(x, self.w_qkv, self.b_qkv, ctx, cache, H, Hkv)
         out = self.rt.empty(ctx.num_tokens, H * D)
         attn_kernels.attention(qkv, ctx, cache, out, H, Hkv, D, self.scale, self.window)
         return self.rt.linear(out, self.w_o)

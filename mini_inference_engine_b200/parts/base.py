@@ -14,7 +14,8 @@ Interfaces (duck-typed; the base classes below only document them and hold the d
   mixer           cache_need() -> KVNeed | StateNeed | None
                   forward(x[T, hidden], ctx: StepContext, cache: LayerCache) -> [T, hidden]
   feed-forward    forward(x[T, hidden], ctx) -> [T, hidden]
-  position        prepare(rt); rotate_and_store(qkv, ctx, cache, heads, kv_heads, head_dim)
+  position        rotate_and_store(qkv, ctx, cache, heads, kv_heads)   rotate q (in place) and k, write k, v to the cache
+                  project_rotate_and_store(x, w_qkv, b_qkv, ctx, cache, heads, kv_heads) -> qkv   (may fuse the three)
   block           forward(delta, res, ctx, cache) -> delta'            (arrangement of the above)
   embedding       forward(ctx) -> res [T, hidden] float32
   head            forward(x[W, hidden]) -> logits [W, vocab] float32

@@ -43,6 +43,21 @@ class Rope(Part):
                 _table_cache[key] = (z, z)
         self.cos, self.sin = _table_cache[key]
 
+    def project_rotate_and_store(self, x, w_qkv, b_qkv, ctx, cache, num_heads, num_kv_heads):
+        """The q|k|v projection followed by rotate_and_store.  Where the tensor-core product can do
+        the rotation and the cache write in its epilogue (few tokens, bfloat16), that is one kernel."""
+        from ..kernels import gemm_tc, linear as linear_kernels
+        if (linear_kernels.uses_tcgen05(x, w_qkv) and cache.k is not None and cache.k.dtype == torch.bfloat16
+                and gemm_tc.can_fuse_rope(x, w_qkv, num_heads, num_kv_heads, self.head_dim, self.rotary_dim)):
+            qkv = self.rt.empty(x.shape[0], w_qkv.shape[0])
+            if gemm_tc.supports(x, w_qkv, qkv):
+                return gemm_tc.gemm_qkv_rope(x, w_qkv, qkv, b_qkv, ctx.positions, ctx.slots[cache.group], self.cos, self.sin,
+                                             cache.k, cache.v, num_heads, num_kv_heads, self.head_dim, self.rotary_dim,
+                                             cache.page_size, write_cache=cache.writes)
+        qkv = self.rt.linear(x, w_qkv, b_qkv)
+        self.rotate_and_store(qkv, ctx, cache, num_heads, num_kv_heads)
+        return qkv
+
     def rotate_and_store(self, qkv, ctx, cache, num_heads, num_kv_heads):
         ops.rope_cache_write(qkv, ctx.positions, ctx.slots[cache.group], self.cos, self.sin, cache.k, cache.v,
                              num_heads, num_kv_heads, self.head_dim, self.rotary_dim, cache.page_size,

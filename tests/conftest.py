@@ -16,6 +16,11 @@ TINY = {
                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5,
                    rope_theta=10000.0, max_position_embeddings=128, tie_word_embeddings=False,
                    architectures=["LlamaForCausalLM"]),
+    # sizes that are multiples of nothing: odd vocabulary, width 100, feed-forward 52, five heads without grouping
+    "tiny_c": dict(vocab_size=131, hidden_size=100, intermediate_size=52, num_hidden_layers=1,
+                   num_attention_heads=5, num_key_value_heads=5, head_dim=16, rms_norm_eps=1e-4,
+                   rope_theta=1000.0, max_position_embeddings=96, tie_word_embeddings=True,
+                   architectures=["LlamaForCausalLM"]),
     "tiny_b": dict(vocab_size=384, hidden_size=96, intermediate_size=256, num_hidden_layers=3,
                    num_attention_heads=3, num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-6,
                    rope_theta=500000.0, max_position_embeddings=256, tie_word_embeddings=True,

@@ -539,3 +539,50 @@ def test_prefill_attention_tc_skips_single_token_rows(ops):
     assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
     close(out[1:6], want[1:6], torch.bfloat16, "row 1")
     close(out[7:9], want[7:9], torch.bfloat16, "row 3")
+
+
+@pytest.mark.parametrize("H,Hkv,D,rot,M,K", [(32, 4, 64, 64, 8, 2048), (4, 2, 16, 16, 3, 256), (3, 1, 32, 32, 16, 384),
+                                             (8, 8, 128, 64, 5, 512), (2, 1, 64, 0, 7, 256), (32, 8, 128, 128, 32, 4096)])
+def test_gemm_tc_fused_rotation_and_cache_write(ops, H, Hkv, D, rot, M, K):
+    """The q|k|v product with rotation and cache write in its epilogue against the plain formulas."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(H + D + M)
+    N, page, num_pages, theta, max_pos = (H + 2 * Hkv) * D, 16, 40, 10000.0, 600
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    b = (torch.randn(N) * 0.1).bfloat16()
+    positions = torch.randint(0, max_pos, (M,), dtype=torch.int32)
+    slots = torch.randperm((num_pages - 1) * page)[:M].to(torch.int32) + page
+    if rot:
+        j = torch.arange(0, rot, 2, dtype=torch.int64).float()
+        cos, sin = ops.rope_tables((1.0 / (theta ** (j / rot))).to(DEV), max_pos)
+    else:
+        cos = sin = torch.zeros(max_pos, 0, device=DEV)
+    assert gemm_tc.can_fuse_rope(x.to(DEV), w.to(DEV), H, Hkv, D, rot)
+    k_cache = torch.full((num_pages, Hkv, page, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.full_like(k_cache, 7.0)
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_qkv_rope(x.to(DEV), w.to(DEV), out, b.to(DEV), positions.to(DEV), slots.to(DEV), cos, sin, k_cache, v_cache,
+                          H, Hkv, D, rot, page)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    qkv = x.float() @ w.float().t() + b.float()
+    q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], -1)
+    q, k, v = q.view(M, H, D), k.view(M, Hkv, D), v.view(M, Hkv, D)
+
+    def rotate(t):
+        if not rot:
+            return t
+        ang = pl.rope_angles(positions, rot, theta)
+        return torch.cat((pl.apply_rope(t[..., :rot], ang), t[..., rot:]), -1)
+
+    close(out[:, :H * D].reshape(M, H, D), rotate(q), torch.bfloat16, "fused rotated q")
+    kc, vc = k_cache.cpu().float(), v_cache.cpu().float()
+    for t in range(M):
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        close(kc[pg, :, off], rotate(k)[t], torch.bfloat16, f"fused cached k of token {t}")
+        close(vc[pg, :, off], v[t], torch.bfloat16, f"fused cached v of token {t}")
+    untouched = torch.ones(num_pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert (kc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()
+    assert (vc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()
