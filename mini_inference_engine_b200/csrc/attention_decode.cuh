@@ -131,14 +131,18 @@ decode_attention_kernel(const DecodeParams p) {
             }
             // mask, scale to base 2, running max
             float mx[2] = {-INFINITY, -INFINITY};
+            const bool whole = key0 + 16 <= kend && key0 >= first_key;   // no key of the warp's 16 needs a mask (warp-uniform)
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int key = key0 + n * 8 + tq * 2 + (i & 1);
-                    const bool ok = key < kend && key >= first_key;
-                    s[n][i] = ok ? s[n][i] * p.scale_log2e : -INFINITY;
-                    mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
+                    float v = s[n][i] * p.scale_log2e;
+                    if (!whole) {
+                        const int key = key0 + n * 8 + tq * 2 + (i & 1);
+                        if (!(key < kend && key >= first_key)) v = -INFINITY;
+                    }
+                    s[n][i] = v;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], v);
                 }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {

@@ -24,6 +24,8 @@
 // softmax and epilogue.  Barriers: q_full, kv_full[2] / kv_empty[2] (two key/value stages), s_full
 // (S is complete; also means the PV product before it has finished), p_full (one arrival per softmax warp: P is
 // written and O rescaled), o_full.  Every wait is bounded (see tcgen05_common.cuh).
+#include <type_traits>
+
 #include "tcgen05_common.cuh"
 
 #define FA_BM 128
@@ -86,7 +88,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, 2)       // two blocks per SM: at most 168 registers
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv activation [tokens, q_stride], box {64, 128}
                             const __grid_constant__ CUtensorMap map_k,   // key pages as rows [pages * kv_heads * page_size, D], box {64, page rows}
                             const __grid_constant__ CUtensorMap map_v,
@@ -271,21 +273,28 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 // P is formed against the running max as it stands, the row's true max is found on the
                 // way, and only if some entry would exceed 2^8 is the tile redone against the new max
                 // (then O and l are rescaled).  The first tile has no running max and takes a max pass.
-                if (t == 0) {
-                    float mx = -INFINITY;
+                // The two loops below exist in a masked and an unmasked version, chosen once per tile: a
+                // test per element would double the instructions of the common, unmasked tiles.
+                auto row_max = [&](auto mask_tag) {
+                    constexpr bool MASK = decltype(mask_tag)::value;
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     for_each_chunk([&](int ch, const uint32_t* c) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             float x = __uint_as_float(c[i]);
-                            if (need_mask && masked(key0 + ch * 32 + i)) x = -INFINITY;
-                            mx = fmaxf(mx, x);
+                            if (MASK && masked(key0 + ch * 32 + i)) x = -INFINITY;
+                            mx4[i & 3] = fmaxf(mx4[i & 3], x);
                         }
                     });
+                    return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                };
+                if (t == 0) {
+                    const float mx = need_mask ? row_max(std::true_type{}) : row_max(std::false_type{});
                     m_run = mx * p.scale_log2e;                    // the scale is positive: max and scaling commute
                 }
                 float alpha = 1.f, sum = 0.f;
-                for (int attempt = 0; attempt < 2; ++attempt) {
-                    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+                auto p_pass = [&](auto mask_tag, float neg_m, float& xmax_out) {
+                    constexpr bool MASK = decltype(mask_tag)::value;
                     // four independent sums and maxima: one warp per scheduler has nothing else to hide
                     // the latency of a dependent chain behind
                     float xm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, sm[4] = {0.f, 0.f, 0.f, 0.f};
@@ -295,7 +304,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         for (int i = 0; i < 32; i += 2) {
                             float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
                             float x1 = fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
-                            if (need_mask) {
+                            if (MASK) {
                                 if (masked(key0 + ch * 32 + i)) x0 = -INFINITY;
                                 if (masked(key0 + ch * 32 + i + 1)) x1 = -INFINITY;
                             }
@@ -306,8 +315,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         }
                         tmem_st16(lane_addr + TMEM_P + ch * 16, packed);
                     });
-                    const float xmax = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
-                    sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+                    xmax_out = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
+                    return (sm[0] + sm[1]) + (sm[2] + sm[3]);
+                };
+                for (int attempt = 0; attempt < 2; ++attempt) {
+                    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+                    float xmax;
+                    sum = need_mask ? p_pass(std::true_type{}, neg_m, xmax) : p_pass(std::false_type{}, neg_m, xmax);
                     // the running max moves only when it has to (warp-wide decision: the loads are warp-wide)
                     const bool moved = xmax > 8.0f || (m_run == -INFINITY && xmax > -INFINITY);
                     if (attempt == 1 || !__any_sync(0xffffffffu, moved)) break;
