@@ -117,6 +117,9 @@ static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of the cluster barrier, for a barrier whose arrival and wait lie apart.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -134,6 +137,11 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
     float4 v;
     asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
+}
+// A store into another block's shared memory; the cluster barrier after it (release / acquire)
+// makes it visible there.
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float v;

@@ -12,10 +12,14 @@
 //           {16, 32, 64, 128, 256}.  The step is then pure weight streaming.
 //
 // Split-K without scratch memory: the blocks that share an output tile form a thread-block cluster
-// along grid.z (2, 4 or 8 blocks).  Each leaves its float32 partial tile in its own shared memory,
-// the cluster synchronises, and every block adds up its share of the tile's rows straight out of the
-// others' shared memory (distributed shared memory, ld.shared::cluster) in rank order -- the same
-// order every time -- and writes the result.  No global partial sums, no atomics, no second kernel.
+// along grid.z (2, 4 or 8 blocks), and every block owns a share of the tile's rows.  SWAPPED (the
+// decode path, where the tail of the kernel is most of its time): each block sends its float32
+// partial rows straight from TMEM into the owner's shared memory (st.shared::cluster, one slot per
+// sender), one cluster barrier follows, and the owner adds up its slots locally.  NORMAL: each
+// block leaves its partial tile in its own shared memory and, after a barrier, reads its share out
+// of the others' (ld.shared::cluster); a second barrier keeps everyone's memory alive meanwhile.
+// Either way the sum runs in rank order -- the same order every time -- with no global partial
+// sums, no atomics and no second kernel.
 //
 // Programmatic dependent launch: the kernel lets its successor start at once
 // (griddepcontrol.launch_dependents) and itself may start while its predecessor still runs.  Weights
@@ -67,6 +71,8 @@ struct TcParams {
     bf16* k_cache; bf16* v_cache;                    // [pages, kv_heads, page_size, head_dim]
     int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
     uint32_t rope_smem_offset;                       // where the rotation's tables start inside dynamic shared memory
+    uint32_t recv_smem_offset;                       // with `push`: where the slots for the peers' partial rows start
+    int push;                                        // split-K by sending partial rows to their owners (SWAPPED, when the slots fit)
 };
 
 template <bool OUT_F32>
@@ -124,6 +130,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     float* rope_cs = reinterpret_cast<float*>(rope_slot + BN);
 
     grid_dep_launch_dependents();                             // the next kernel may start its own prologue now
+    // SWAPPED split-K sends partial rows into the peers' shared memory.  A block may be written to only
+    // once it runs: everybody arrives here, and waits (long since satisfied) before its first send.
+    const bool push = SWAPPED && p.push;
+    if (push) cluster_arrive_relaxed();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TC_BM;          // first row of the 128-row operand
@@ -175,6 +185,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 tma_load_2d(slot + x_off, map_x, &full_bar[s], k, x0);
             }
         }
+        __syncwarp();
+        if (push) cluster_wait();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
@@ -194,7 +206,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             }
             if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
         }
+        __syncwarp();
+        if (push) cluster_wait();
     } else {
+        if (push) cluster_wait();                            // every block of the cluster runs: its memory may be written
         // epilogue: warp q reads TMEM lanes 32q .. 32q+31; thread r owns row r of the MMA tile
         const int q = warp & 3;
         const int r = q * 32 + lane;
@@ -223,6 +238,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         if (ready) {
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
             float* red = reinterpret_cast<float*>(tiles);     // the ring is free: every MMA has read its slot
+            // where row r of the partial tile goes: the owner's slot for this sender (see the sum below)
+            uint32_t send_to = 0;
+            if (push) {
+                const int S = p.splits, rows_per = TC_BM / S;
+                const int owner = p.rope ? r % S : r / rows_per, li = p.rope ? r / S : r % rows_per;
+                send_to = cluster_addr(tiles_base + p.recv_smem_offset, owner) + (uint32_t)((split * rows_per + li) * RED_LD) * 4u;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
@@ -231,7 +253,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-                if (p.splits > 1) {                            // leave the partial tile for the cluster
+                if (push) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) st_cluster_f32x4(send_to + (uint32_t)(c + i) * 4u, v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else if (p.splits > 1) {                     // leave the partial tile for the cluster
 #pragma unroll
                     for (int i = 0; i < 16; ++i) red[r * RED_LD + c + i] = v[i];
                 } else if (!SWAPPED) {
@@ -288,7 +313,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     const bool aborted = abort_flag != 0;
 
     if (p.splits > 1) {
-        // split-K: add the partial tiles of the cluster's blocks, each block its share of the rows
+        // split-K: add the partial tiles of the cluster's blocks, each block its share of the rows.
+        // With `push` the partial rows are in this block's slots already (slot s = what rank s sent), so one
+        // barrier and local loads do; with the rotation a block owns every S-th row, which keeps a row and
+        // its partner (half a rotation apart, a multiple of S) with the same owner.
         cluster_sync_all();
         const int S = p.splits;
         const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
@@ -297,16 +325,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             const int tid = threadIdx.x - 64;                // 0..127
             uint32_t peer[8];
 #pragma unroll
-            for (int s = 0; s < 8; ++s) peer[s] = cluster_addr(tiles_base, s < S ? s : 0);
+            for (int s = 0; s < 8; ++s) peer[s] = push ? 0u : cluster_addr(tiles_base, s < S ? s : 0);
+            const float* recv = reinterpret_cast<const float*>(tiles + p.recv_smem_offset);
+            const bool cyclic = push && p.rope;
             // one thread: one row of the tile, four consecutive columns, summed over the blocks in rank order
             for (int idx = tid; idx < rows_per * (BN / 4); idx += 128) {
-                int rr, c;
-                if (SWAPPED) { rr = r_lo + idx % rows_per; c = (idx / rows_per) * 4; }     // neighbours: consecutive features
+                int rr, c, li = 0;
+                if (SWAPPED) { li = idx % rows_per; c = (idx / rows_per) * 4; rr = cyclic ? li * S + split : r_lo + li; }   // neighbours: consecutive features
                 else { rr = r_lo + idx / (BN / 4); c = (idx % (BN / 4)) * 4; }             // neighbours: consecutive columns
                 const uint32_t off = (uint32_t)(rr * RED_LD + c) * 4u;
                 float4 part[8];
 #pragma unroll
-                for (int s = 0; s < 8; ++s) if (s < S) part[s] = ld_cluster_f32x4(peer[s] + off);
+                for (int s = 0; s < 8; ++s)
+                    if (s < S) part[s] = push ? *reinterpret_cast<const float4*>(recv + (s * rows_per + li) * RED_LD + c)
+                                              : ld_cluster_f32x4(peer[s] + off);
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int s = 0; s < 8; ++s)
@@ -335,10 +367,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         int np = n;
                         if (rotated) {                                       // the partner row: half a rotation apart, same tile
                             np = d < half ? n + half : n - half;
-                            const uint32_t poff = (uint32_t)((rr + (np - n)) * RED_LD + c) * 4u;
+                            const int pli = li + (np - n) / S;               // the partner's place in this block's slots
                             float4 pp[8];
 #pragma unroll
-                            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) pp[s2] = ld_cluster_f32x4(peer[s2] + poff);
+                            for (int s2 = 0; s2 < 8; ++s2)
+                                if (s2 < S) pp[s2] = *reinterpret_cast<const float4*>(recv + (s2 * rows_per + pli) * RED_LD + c);
 #pragma unroll
                             for (int s2 = 0; s2 < 8; ++s2)
                                 if (s2 < S) { pacc[0] += pp[s2].x; pacc[1] += pp[s2].y; pacc[2] += pp[s2].z; pacc[3] += pp[s2].w; }
@@ -386,7 +419,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 }
             }
         }
-        cluster_sync_all();                                  // nobody leaves while its shared memory is being read
+        if (!push) cluster_sync_all();                       // nobody leaves while its shared memory is being read
     }
 
     if (aborted) {
@@ -416,10 +449,23 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 
 template <int BN, bool SWAPPED, bool OUT_F32>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int pdl, cudaStream_t stream) {
-    size_t smem = (size_t)p.stages * (TC_BM * TC_BK * 2 + BN * TC_BK * 2);
-    const size_t red = (size_t)TC_BM * (BN + 4) * sizeof(float);           // the partial tile reuses the ring
-    if (p.splits > 1 && red > smem) smem = red;
+    const size_t red = (size_t)TC_BM * (BN + 4) * sizeof(float);           // the partial tile: S slots of 128 / S rows
+    const size_t stage = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    const size_t tables = p.rope ? (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float) : 0;
+    const size_t limit = 227 * 1024 - 1024 - 512;                           // less the alignment slack and the static barriers
     TcParams pp = p;
+    // Peers write their partial rows while this block's ring is still live, so the slots lie beside the
+    // ring: where even a ring of two stages leaves no room for them, the partial tile stays at home
+    // (in the ring, once it is done) and the owners fetch it.  A ring that would not fit is made
+    // shorter, never refused.
+    pp.push = SWAPPED && p.splits > 1 && 2 * stage + red + tables <= limit;
+    if (p.rope && !pp.push) return MIE_ERR_BAD_ARG;
+    const size_t beside = (pp.push ? red : 0) + tables;
+    while (pp.stages > 2 && pp.stages * stage + beside > limit) --pp.stages;
+    size_t smem = (size_t)pp.stages * stage;
+    pp.recv_smem_offset = 0;
+    if (pp.push) { pp.recv_smem_offset = (uint32_t)smem; smem += red; }
+    else if (p.splits > 1 && red > smem) smem = red;
     pp.rope_smem_offset = (uint32_t)smem;
     if (p.rope) smem += (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float);
     smem += 1024;
@@ -503,6 +549,7 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
     p.tiles_per_split = (p.k_tiles + splits - 1) / splits;
     p.splits = splits;             // a block whose range is empty still joins the cluster with a zero tile
     if (p.rope && p.splits < 2) return MIE_ERR_BAD_ARG;      // the fused rotation lives in the cluster reduction
+    if (p.rope && (p.rotary_dim / 2) % p.splits) return MIE_ERR_BAD_ARG;   // a row and its partner must have one owner
     p.stages = stages;
     CUtensorMap ma, mb;
     dim3 grid;

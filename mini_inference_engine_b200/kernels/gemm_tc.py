@@ -47,9 +47,10 @@ def plan(M: int, N: int, K: int) -> dict:
     while splits < 8 and tiles * splits * 2 <= 2 * NUM_SMS and k_tiles // (splits * 2) >= 2:
         splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
     per_split = -(-k_tiles // splits)
-    stages = max(2, min(8, per_split, (TWO_PER_SM - 1024) // stage))
+    recv = 128 * (bn + 4) * 4 if swapped and splits > 1 else 0     # the slots for the peers' partial rows, beside the ring
+    stages = max(2, min(8, per_split, (TWO_PER_SM - 1024 - recv) // stage))
     if stages < 3 and per_split > 2:
-        stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024) // stage))
+        stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024 - recv) // stage))
     pl = dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
     pl.update(plan_overrides.get((N, K), {}) if swapped else {})
     return pl
@@ -87,7 +88,7 @@ def can_fuse_rope(x: torch.Tensor, w: torch.Tensor, num_heads: int, num_kv_heads
     if N != (num_heads + 2 * num_kv_heads) * head_dim:
         return False
     pl = plan(M, N, K)
-    return (pl["swapped"] and pl["splits"] >= 2 and -(-K // 64) >= pl["splits"]
+    return (pl["swapped"] and pl["splits"] >= 2 and -(-K // 64) >= pl["splits"] and (rotary_dim // 2) % pl["splits"] == 0
             and pl["bn"] * rotary_dim * 4 <= 16 * 1024)          # the tile's cos/sin rows ride in shared memory
 
 
