@@ -36,7 +36,11 @@ decode_attention_kernel(const DecodeParams p) {
     __shared__ int s_pages[DEC_PAGE_SLOTS];                        // this block's page ids, fetched once
     __shared__ int s_last;
 
-    pdl_enter();
+    // The row's lengths, its page table and every cached key and value except the newest token's are
+    // older than this step: nothing the kernel before this one writes.  So the block reads them and
+    // starts its first copies before it waits for that kernel, and fetches the newest token's key and
+    // value (and the queries) afterwards.
+    pdl_launch_dependents();
     const int row = blockIdx.z;
     if (p.row_q_len[row] != 1) return;
     const int G = p.num_heads / p.num_kv_heads;
@@ -56,20 +60,6 @@ decode_attention_kernel(const DecodeParams p) {
     const int kbeg = lo + split * tiles_per * DEC_TILE;
     const int kend = min(ctx, kbeg + tiles_per * DEC_TILE);
     const int ntiles = kend > kbeg ? (kend - kbeg + DEC_TILE - 1) / DEC_TILE : 0;
-
-    // Q fragments (A operand), rows = query heads of the group, zero beyond gn
-    unsigned qf[KSTEPS][4];
-    {
-        const bf16* qb = p.q + (int64_t)token * p.q_stride + (int64_t)(kvh * G + g0) * D;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = quad + (i & 1) * 8, c = ks * 16 + tq * 2 + (i >> 1) * 8;
-                qf[ks][i] = r < gn ? *reinterpret_cast<const unsigned*>(qb + (int64_t)r * D + c) : 0u;
-            }
-        }
-    }
 
     float o[NBLK][4];
 #pragma unroll
@@ -109,12 +99,41 @@ decode_attention_kernel(const DecodeParams p) {
         if (t < ntiles) load_tile(t, t);
         cp_async_commit();
     }
+    pdl_wait();                                                    // q and the newest key and value are the previous kernel's
+    // Q fragments (A operand), rows = query heads of the group, zero beyond gn
+    unsigned qf[KSTEPS][4];
+    {
+        const bf16* qb = p.q + (int64_t)token * p.q_stride + (int64_t)(kvh * G + g0) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = quad + (i & 1) * 8, c = ks * 16 + tq * 2 + (i >> 1) * 8;
+                qf[ks][i] = r < gn ? *reinterpret_cast<const unsigned*>(qb + (int64_t)r * D + c) : 0u;
+            }
+        }
+    }
+
+    const int newest = ctx - 1;                                    // the only cached position written during this step
     for (int t = 0; t < ntiles; ++t) {
         const int stage = t % NSTAGE;
         if (t + NSTAGE - 1 < ntiles) load_tile(t + NSTAGE - 1, (t + NSTAGE - 1) % NSTAGE);
         cp_async_commit();
         cp_async_wait<NSTAGE - 1>();                               // tile t has landed; NSTAGE - 1 younger ones may be in flight
         __syncthreads();
+        if (t < NSTAGE - 1 && newest >= kbeg + t * DEC_TILE && newest < min(kend, kbeg + (t + 1) * DEC_TILE)) {
+            // this tile was copied before the wait: its newest row may be stale, fetch it again (L2, not L1)
+            if (threadIdx.x < 2 * CHUNKS_PER_ROW) {
+                const int which = threadIdx.x / CHUNKS_PER_ROW, c = (threadIdx.x - which * CHUNKS_PER_ROW) * 8;
+                const int r = newest - (kbeg + t * DEC_TILE);
+                const int pi = (newest >> p.page_shift) - first_page;
+                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (newest & (p.page_size - 1))) * D + c;
+                const uint4 v = __ldcg(reinterpret_cast<const uint4*>((which ? p.v_cache : p.k_cache) + src));
+                *reinterpret_cast<uint4*>((which ? v_s : k_s) + stage * DEC_TILE * DP + r * DP + c) = v;
+            }
+            __syncthreads();
+        }
         const bf16* kt = k_s + stage * DEC_TILE * DP + warp * 16 * DP;
         const bf16* vt = v_s + stage * DEC_TILE * DP + warp * 16 * DP;
         const int key0 = kbeg + t * DEC_TILE + warp * 16;

@@ -350,6 +350,47 @@ def test_decode_attention_head_shapes(ops, H, Hkv, D, page):
         close(out, want, torch.bfloat16, f"decode H{H} Hkv{Hkv} D{D} page{page} splits {splits}")
 
 
+def test_decode_attention_reads_the_key_written_just_before_it(ops):
+    """The decode kernel starts copying cached keys before the kernel in front of it has finished
+    (programmatic dependent launch); the newest token's key and value, which that kernel writes, must
+    still be the ones it uses.  Contexts grow token by token, write and attention back to back with no
+    synchronisation; every new key dominates its query, so a stale row would show in full."""
+    torch.manual_seed(5)
+    H, Hkv, D, page, rows, start, steps = 8, 2, 64, 16, 3, 60, 44
+    pages_per_row = (start + steps + page - 1) // page
+    num_pages = rows * pages_per_row + 1
+    tables = torch.arange(1, num_pages, dtype=torch.int32).view(rows, pages_per_row).to(DEV)
+    k_cache = (torch.randn(num_pages, Hkv, page, D) * 0.1).bfloat16().to(DEV)
+    v_cache = (torch.randn(num_pages, Hkv, page, D) * 0.1).bfloat16().to(DEV)
+    cos = sin = torch.zeros(4096, 0, device=DEV)
+    q_start = torch.arange(rows, dtype=torch.int32, device=DEV)
+    q_len = torch.ones(rows, dtype=torch.int32, device=DEV)
+    outs, wants = [], []
+    ins = []
+    for i in range(steps):                                        # every input is on the device before the first launch
+        ctx = start + i + 1
+        qkv = torch.zeros(rows, (H + 2 * Hkv) * D)
+        qkv[:, :H * D].view(rows, H, D)[:, :, i % D] = 30.0        # the query looks along dimension i
+        qkv[:, H * D:(H + Hkv) * D].view(rows, Hkv, D)[:, :, i % D] = 30.0          # and so does the new key
+        val = torch.randn(rows, Hkv, D)
+        qkv[:, (H + Hkv) * D:] = val.view(rows, -1)
+        slots = torch.tensor([int(tables[r, (ctx - 1) // page]) * page + (ctx - 1) % page for r in range(rows)], dtype=torch.int32)
+        ins.append((qkv.bfloat16().to(DEV), torch.full((rows,), ctx - 1, dtype=torch.int32, device=DEV), slots.to(DEV),
+                    torch.full((rows,), ctx, dtype=torch.int32, device=DEV)))
+        wants.append(val.bfloat16().float().repeat_interleave(H // Hkv, 1))
+    torch.cuda.synchronize()
+    for qkv, pos, slots, ctx_len in ins:
+        ops.rope_cache_write(qkv, pos, slots, cos, sin, k_cache, v_cache, H, Hkv, D, 0, page)
+        out = torch.empty(rows, H * D, dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention(qkv, qkv.shape[1], k_cache, v_cache, tables, q_start, q_len, ctx_len, out, H, Hkv, D, page,
+                             1.0 / math.sqrt(D), max_ctx=start + steps)
+        outs.append(out)
+    torch.cuda.synchronize()
+    for i, (out, want) in enumerate(zip(outs, wants)):
+        err = (out.float().cpu().view(rows, H, D) - want).abs().max().item()
+        assert err < 0.05, f"step {i}: the newest value was not the one attended to (error {err})"
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
 def test_decode_attention_window(ops, window):
     for splits in (1, 3):
