@@ -33,6 +33,15 @@
 // position, and writes q to the activation and k, v straight into their cache pages -- the work of the
 // separate rotation kernel (inference_engine/model.py:174-176,130-134), on float32 sums.
 //
+// Optional residual epilogue, and the norm that goes with it (few tokens, split-K): the owner of a
+// row adds its sum to the float32 residual stream, res += y, in place.  For the RMSNorm that reads
+// the stream next it also writes xw = bf16(res * norm_weight) and its share of sum(res^2) per token
+// into a slot of its own (sq_out[slot][token]; slots = 128-row tiles x max(splits, 4)).  The product
+// that consumes xw then owes the factor rsqrt(mean(res^2) + eps), which is a scalar per token and so
+// commutes with the product: it adds up the slots (in slot order) while its weights stream and scales
+// its float32 sums by it before bias, rotation or SwiGLU.  Two kernels fewer per layer than norm
+// kernels between the products (inference_engine/model.py:169-184 launches a fused add+norm there).
+//
 // Optional SwiGLU epilogue: with gate and up rows interleaved in W (row 2i = gate_i, row 2i+1 = up_i)
 // the epilogue writes silu(gate) * up, N/2 wide, from the float32 accumulators
 // (inference_engine/model.py:180-181 does this with two more kernels on rounded values).
@@ -73,6 +82,13 @@ struct TcParams {
     uint32_t rope_smem_offset;                       // where the rotation's tables start inside dynamic shared memory
     uint32_t recv_smem_offset;                       // with `push`: where the slots for the peers' partial rows start
     int push;                                        // split-K by sending partial rows to their owners (SWAPPED, when the slots fit)
+    // Optional residual epilogue (see the header comment): res [M, N] float32 in place; with norm_w also
+    // xw_out [M, N] bfloat16 and sq_out [tiles * max(splits, 4)][sq_stride] float32.  `out` is not written.
+    float* res; const void* norm_w; int norm_w_tag; bf16* xw_out; float* sq_out; int sq_stride;
+    // Optional: the input x is xw of an earlier residual epilogue; scale the sums of token t by
+    // rsqrt(sum over slots of sq_in[slot][t] / sq_width + sq_eps).
+    const float* sq_in; int sq_slots, sq_in_stride; float sq_width, sq_eps;
+    uint32_t rstd_smem_offset;
 };
 
 template <bool OUT_F32>
@@ -128,6 +144,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     int* rope_pos = reinterpret_cast<int*>(tiles + p.rope_smem_offset);
     int* rope_slot = rope_pos + BN;
     float* rope_cs = reinterpret_cast<float*>(rope_slot + BN);
+    float* rstd_s = reinterpret_cast<float*>(tiles + p.rstd_smem_offset);      // [BN], only with sq_in
 
     grid_dep_launch_dependents();                             // the next kernel may start its own prologue now
     // SWAPPED split-K sends partial rows into the peers' shared memory.  A block may be written to only
@@ -231,6 +248,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 rope_cs[i] = p.cos_t[(int64_t)rope_pos[tt] * half + jj];
                 rope_cs[BN * half + i] = p.sin_t[(int64_t)rope_pos[tt] * half + jj];
             }
+        }
+        if (p.sq_in) {
+            // the factor the norm before this product left for it: 128 / BN threads add up a token's slots,
+            // each its share in slot order, then the shares in lane order -- the same order every time
+            if (!p.rope) grid_dep_wait();
+            constexpr int TPT = BN >= 128 ? 1 : 128 / BN;    // threads per token
+            const int et = threadIdx.x - 64;
+            for (int i0 = 0; i0 < BN; i0 += 128 / TPT) {
+                const int i = i0 + et / TPT, sub = et % TPT, t = b0 + i;
+                float sum = 0.f;
+                if (i < BN && t < p.M)
+                    for (int sl = sub; sl < p.sq_slots; sl += TPT) sum += __ldcg(p.sq_in + (int64_t)sl * p.sq_in_stride + t);
+#pragma unroll
+                for (int o = TPT >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (sub == 0 && i < BN) rstd_s[i] = t < p.M ? rsqrtf(sum / p.sq_width + p.sq_eps) : 1.f;
+            }                                                // read after the block-wide barrier below
         }
         const bool have_work = n_kt > 0;                     // a split beyond the last k-tile adds a zero tile
         const bool ready = have_work ? mbar_wait(&tmem_full_bar, 0, abort_p) : true;
@@ -343,6 +376,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 #pragma unroll
                 for (int s = 0; s < 8; ++s)
                     if (s < S) { acc[0] += part[s].x; acc[1] += part[s].y; acc[2] += part[s].z; acc[3] += part[s].w; }
+                if (SWAPPED && p.sq_in) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] *= rstd_s[c + j];
+                }
                 if (!SWAPPED) {
                     const int m = a0 + rr, n = b0 + c;
                     if (m >= p.M || n >= p.N) continue;
@@ -375,6 +412,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 #pragma unroll
                             for (int s2 = 0; s2 < 8; ++s2)
                                 if (s2 < S) { pacc[0] += pp[s2].x; pacc[1] += pp[s2].y; pacc[2] += pp[s2].z; pacc[3] += pp[s2].w; }
+                            if (p.sq_in) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) pacc[j] *= rstd_s[c + j];
+                            }
                         }
                         const float b = p.bias ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
                         const float bp = (p.bias && rotated) ? load_tagged(p.bias, np, p.bias_tag) : 0.f;
@@ -399,6 +440,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                                 const int64_t dst = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + off) * D + d;
                                 (is_k ? p.k_cache : p.v_cache)[dst] = __float2bfloat16_rn(val);
                             }
+                        }
+                    }
+                } else if (p.res) {
+                    // res += y in place; for the norm that reads the stream next, xw = bf16(res * w) and this
+                    // group of lanes' share of sum(res^2): min(rows_per, 32) neighbouring lanes hold the same four
+                    // tokens and consecutive features, so a shuffle tree over them adds up the features
+                    const int n = a0 + rr;
+                    const bool live = n < p.N;
+                    const float b = (p.bias && live) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+                    const float wn = (p.norm_w && live) ? load_tagged(p.norm_w, n, p.norm_w_tag) : 0.f;
+                    float sq[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int t = b0 + c + j;
+                        sq[j] = 0.f;
+                        if (live && t < p.M) {
+                            const int64_t at = (int64_t)t * p.N + n;
+                            const float rv = p.res[at] + acc[j] + b;
+                            p.res[at] = rv;
+                            if (p.xw_out) p.xw_out[at] = __float2bfloat16_rn(rv * wn);
+                            sq[j] = rv * rv;
+                        }
+                    }
+                    if (p.sq_out) {
+                        const int width = rows_per < 32 ? rows_per : 32;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            for (int o = width >> 1; o > 0; o >>= 1) sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], o);
+                        if ((li & (width - 1)) == 0) {
+                            const int groups = TC_BM / width;                     // slots per 128-row tile = max(S, 4)
+                            const int slot = blockIdx.x * groups + (split * rows_per + li) / width;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (b0 + c + j < p.sq_stride) p.sq_out[(int64_t)slot * p.sq_stride + b0 + c + j] = sq[j];
                         }
                     }
                 } else {
@@ -451,7 +526,8 @@ template <int BN, bool SWAPPED, bool OUT_F32>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int pdl, cudaStream_t stream) {
     const size_t red = (size_t)TC_BM * (BN + 4) * sizeof(float);           // the partial tile: S slots of 128 / S rows
     const size_t stage = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
-    const size_t tables = p.rope ? (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float) : 0;
+    const size_t tables = (p.rope ? (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float) : 0) +
+                          (p.sq_in ? (size_t)BN * sizeof(float) : 0);
     const size_t limit = 227 * 1024 - 1024 - 512;                           // less the alignment slack and the static barriers
     TcParams pp = p;
     // Peers write their partial rows while this block's ring is still live, so the slots lie beside the
@@ -459,7 +535,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     // (in the ring, once it is done) and the owners fetch it.  A ring that would not fit is made
     // shorter, never refused.
     pp.push = SWAPPED && p.splits > 1 && 2 * stage + red + tables <= limit;
-    if (p.rope && !pp.push) return MIE_ERR_BAD_ARG;
+    if ((p.rope || p.res || p.sq_in) && !pp.push) return MIE_ERR_BAD_ARG;   // these live in the owners' sum
     const size_t beside = (pp.push ? red : 0) + tables;
     while (pp.stages > 2 && pp.stages * stage + beside > limit) --pp.stages;
     size_t smem = (size_t)pp.stages * stage;
@@ -468,6 +544,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     else if (p.splits > 1 && red > smem) smem = red;
     pp.rope_smem_offset = (uint32_t)smem;
     if (p.rope) smem += (size_t)BN * 2 * sizeof(int) + (size_t)BN * p.rotary_dim * sizeof(float);
+    pp.rstd_smem_offset = (uint32_t)smem;
+    if (p.sq_in) smem += (size_t)BN * sizeof(float);
     smem += 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAPPED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -516,12 +594,20 @@ struct RopeFuseArgs {
     int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
 };
 
+// The residual epilogue and the deferred norm factor (see the header comment); null pointers switch a
+// half off.  Mirrored field by field by the Python wrapper.
+struct TcFuse {
+    void* res; const void* norm_w; int norm_w_tag; void* xw_out; void* sq_out; int sq_stride;
+    const void* sq_in; int sq_slots; int sq_in_stride; float sq_width; float sq_eps;
+};
+
 static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, const RopeFuseArgs* rope,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const TcFuse* fuse = nullptr) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
+    const bool to_res = fuse && fuse->res;
     if (stages < 2 || stages > TC_MAX_STAGES) return MIE_ERR_BAD_ARG;
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return MIE_ERR_BAD_ARG;
     int rc = tc_setup();
@@ -529,6 +615,23 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
     TcParams p;
     p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.error = g_error_dev;
     p.M = M; p.N = N; p.K = K; p.swiglu = swiglu;
+    p.res = nullptr; p.norm_w = nullptr; p.norm_w_tag = 0; p.xw_out = nullptr; p.sq_out = nullptr; p.sq_stride = 0;
+    p.sq_in = nullptr; p.sq_slots = 0; p.sq_in_stride = 0; p.sq_width = 1.f; p.sq_eps = 0.f;
+    if (fuse) {
+        if (to_res) {
+            // the owners' sum adds to the stream: needs the weight on the 128-row side and a split K
+            if (!swapped || splits < 2 || swiglu || rope || (reinterpret_cast<uintptr_t>(fuse->res) & 15)) return MIE_ERR_BAD_ARG;
+            if ((fuse->xw_out != nullptr) != (fuse->norm_w != nullptr) || (fuse->sq_out && !fuse->xw_out)) return MIE_ERR_BAD_ARG;
+            if (fuse->sq_out && fuse->sq_stride < M) return MIE_ERR_BAD_ARG;
+            p.res = (float*)fuse->res; p.norm_w = fuse->norm_w; p.norm_w_tag = fuse->norm_w_tag;
+            p.xw_out = (bf16*)fuse->xw_out; p.sq_out = (float*)fuse->sq_out; p.sq_stride = fuse->sq_stride;
+        }
+        if (fuse->sq_in) {
+            if (!swapped || splits < 2 || fuse->sq_slots < 1 || fuse->sq_in_stride < M || !(fuse->sq_width > 0.f)) return MIE_ERR_BAD_ARG;
+            p.sq_in = (const float*)fuse->sq_in; p.sq_slots = fuse->sq_slots; p.sq_in_stride = fuse->sq_in_stride;
+            p.sq_width = fuse->sq_width; p.sq_eps = fuse->sq_eps;
+        }
+    }
     p.rope = 0;
     if (rope) {
         // needs the cluster reduction with the weight on the 128-row side, heads that do not straddle tiles
@@ -548,7 +651,7 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
     while (splits > 1 && splits > p.k_tiles) splits >>= 1;
     p.tiles_per_split = (p.k_tiles + splits - 1) / splits;
     p.splits = splits;             // a block whose range is empty still joins the cluster with a zero tile
-    if (p.rope && p.splits < 2) return MIE_ERR_BAD_ARG;      // the fused rotation lives in the cluster reduction
+    if ((p.rope || p.res || p.sq_in) && p.splits < 2) return MIE_ERR_BAD_ARG;   // these live in the cluster reduction
     if (p.rope && (p.rotary_dim / 2) % p.splits) return MIE_ERR_BAD_ARG;   // a row and its partner must have one owner
     p.stages = stages;
     CUtensorMap ma, mb;
@@ -584,6 +687,20 @@ extern "C" int mie_gemm_tc_qkv_rope(const void* x, const void* w, const void* bi
     RopeFuseArgs r = {positions, slots, cos_t, sin_t, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim,
                       page_size, max_pos, write_cache};
     return gemm_tc_launch(x, w, bias, bias_tag, y, MIE_BF16, M, N, K, 1, bn, splits, stages, 0, pdl, &r, stream);
+}
+
+// The product with the residual epilogue and / or the deferred norm factor (`fuse`), optionally with
+// the rotation epilogue too (`positions` non-null; then as mie_gemm_tc_qkv_rope).  With fuse->res set
+// `y` is not written and may be null.
+extern "C" int mie_gemm_tc_fused(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
+                                 int K, int bn, int splits, int stages, int swiglu, int pdl, const TcFuse* fuse,
+                                 const int* positions, const int* slots, const float* cos_t, const float* sin_t,
+                                 void* k_cache, void* v_cache, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                                 int page_size, int max_pos, int write_cache, cudaStream_t stream) {
+    RopeFuseArgs r = {positions, slots, cos_t, sin_t, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim,
+                      page_size, max_pos, write_cache};
+    return gemm_tc_launch(x, w, bias, bias_tag, y, y_tag, M, N, K, 1, bn, splits, stages, swiglu, pdl, positions ? &r : nullptr,
+                          stream, fuse);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait.  Reads host memory that the

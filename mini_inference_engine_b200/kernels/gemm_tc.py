@@ -6,6 +6,7 @@ depth of the shared-memory ring."""
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 
 import torch
 
@@ -56,9 +57,100 @@ def plan(M: int, N: int, K: int) -> dict:
     return pl
 
 
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, **force) -> torch.Tensor:
+@dataclass
+class DeferredNorm:
+    """What a product with the residual epilogue leaves for the product that reads the normed stream:
+    ``xw`` = bfloat16(res * norm_weight) and, per token, sum(res^2) in ``slots`` shares.  The reader
+    scales its float32 sums by rsqrt(sum / width + eps): RMSNorm without a kernel of its own
+    (csrc/gemm_tcgen05.cu, the residual epilogue)."""
+    xw: torch.Tensor           # [M, width] bfloat16
+    sq: torch.Tensor           # [slots, M] float32
+    slots: int
+    width: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+
+class _Fuse(ctypes.Structure):
+    _fields_ = [("res", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("norm_w_tag", ctypes.c_int),
+                ("xw_out", ctypes.c_void_p), ("sq_out", ctypes.c_void_p), ("sq_stride", ctypes.c_int),
+                ("sq_in", ctypes.c_void_p), ("sq_slots", ctypes.c_int), ("sq_in_stride", ctypes.c_int),
+                ("sq_width", ctypes.c_float), ("sq_eps", ctypes.c_float)]
+
+
+def _fuse_struct(deferred: DeferredNorm | None = None, res=None, norm_weight=None, xw=None, sq=None) -> _Fuse:
+    f = _Fuse()
+    if res is not None:
+        f.res = res.data_ptr()
+        if norm_weight is not None:
+            f.norm_w, f.norm_w_tag = norm_weight.data_ptr(), ops.tag(norm_weight)
+            f.xw_out, f.sq_out, f.sq_stride = xw.data_ptr(), sq.data_ptr(), sq.shape[1]
+    if deferred is not None:
+        f.sq_in, f.sq_slots, f.sq_in_stride = deferred.sq.data_ptr(), deferred.slots, deferred.sq.shape[1]
+        f.sq_width, f.sq_eps = float(deferred.width), float(deferred.eps)
+    return f
+
+
+def splits_k(M: int, N: int, K: int) -> bool:
+    """Whether the plan for these sizes puts the weight on the 128-row side and splits K across a
+    cluster: the form whose owners' sum carries the rotation, residual and norm-factor epilogues."""
+    pl = plan(M, N, K)
+    return bool(pl["swapped"] and pl["splits"] >= 2 and -(-K // 64) >= pl["splits"] and pl["bn"] <= 128)
+
+
+def _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, fuse: _Fuse, rope_args=None):
+    lib = build.load("gemm_tcgen05")
+    null = ctypes.c_void_p(0)
+    if rope_args is None:
+        rope_c = (null, null, null, null, null, null, 0, 0, 0, 0, 0, 0, 0)
+    else:
+        positions, slots, cos, sin, k_cache, v_cache, H, Hkv, D, rot, page, write_cache = rope_args
+        rope_c = (ops._ptr(positions), ops._ptr(slots), ops._ptr(cos), ops._ptr(sin), ops._ptr(k_cache), ops._ptr(v_cache),
+                  H, Hkv, D, rot, page, cos.shape[0], int(write_cache))
+    rc = lib.mie_gemm_tc_fused(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
+                               ops._ptr(out), ops.tag(out) if out is not None else ops.tag(x), M, N, K, pl["bn"], pl["splits"],
+                               pl["stages"], int(swiglu), int(pl.get("pdl", pdl_enabled)), ctypes.byref(fuse), *rope_c,
+                               ops._stream())
+    ops._check(rc, f"gemm_tc fused M{M} N{N} K{K} {pl}")
+
+
+def gemm_residual(x, w: torch.Tensor, res: torch.Tensor, bias=None, norm_weight=None, eps: float = 0.0, **force):
+    """res[M, N] += x[M, K] @ w[N, K]^T (+ bias) in place on the float32 stream ``res``.  With
+    ``norm_weight`` (the RMSNorm that reads the stream next) returns the DeferredNorm for the product
+    behind that norm, else None.  ``x`` may itself be a DeferredNorm.  Needs ``splits_k`` sizes."""
+    deferred = x if isinstance(x, DeferredNorm) else None
+    xt = deferred.xw if deferred is not None else x
+    M, K = xt.shape
+    N = w.shape[0]
+    if (xt.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or res.dtype != torch.float32 or tuple(res.shape) != (M, N)
+            or not (xt.is_contiguous() and w.is_contiguous() and res.is_contiguous()) or K % 8 or N % 8):
+        raise GemmTcError(f"residual epilogue: x {tuple(xt.shape)} {xt.dtype}, w {tuple(w.shape)} {w.dtype}, "
+                          f"res {tuple(res.shape)} {res.dtype} do not fit")
+    pl = plan(M, N, K)
+    pl.update(force)
+    if not (pl["swapped"] and pl["splits"] >= 2):
+        raise GemmTcError("the residual epilogue needs few tokens and a split K")
+    out = None
+    xw = sq = None
+    if norm_weight is not None:
+        slots = -(-N // 128) * max(pl["splits"], 4)
+        xw = torch.empty(M, N, dtype=torch.bfloat16, device=res.device)
+        sq = torch.empty(slots, max(M, pl["bn"] * -(-M // pl["bn"])), dtype=torch.float32, device=res.device)
+        out = DeferredNorm(xw, sq, slots, N, eps)
+    _launch_fused(xt, w, bias, None, M, N, K, pl, False, _fuse_struct(deferred, res, norm_weight, xw, sq))
+    return out
+
+
+def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, **force) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) with bfloat16 operands on tcgen05.  With ``swiglu`` the
-    rows of ``w`` are gate/up interleaved and out is [M, N/2] = silu(gate) * up."""
+    rows of ``w`` are gate/up interleaved and out is [M, N/2] = silu(gate) * up.  ``x`` may be a
+    DeferredNorm (sizes must then satisfy ``splits_k``)."""
+    deferred = x if isinstance(x, DeferredNorm) else None
+    if deferred is not None:
+        x = deferred.xw
     M, K = x.shape
     N = w.shape[0]
     if not supports(x, w, out) or (swiglu and N % 16):
@@ -68,6 +160,11 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu:
         raise GemmTcError(f"output shape {tuple(out.shape)} does not match")
     pl = plan(M, N, K)
     pl.update(force)
+    if deferred is not None:
+        if not pl["swapped"]:
+            raise GemmTcError("a deferred norm factor needs few tokens and a split K")
+        _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, _fuse_struct(deferred))
+        return out
     lib = build.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                          ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], pl["splits"], pl["stages"],
@@ -92,16 +189,25 @@ def can_fuse_rope(x: torch.Tensor, w: torch.Tensor, num_heads: int, num_kv_heads
             and pl["bn"] * rotary_dim * 4 <= 16 * 1024)          # the tile's cos/sin rows ride in shared memory
 
 
-def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias, positions, slots, cos, sin, k_cache, v_cache,
+def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots, cos, sin, k_cache, v_cache,
                   num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
                   write_cache: bool = True) -> torch.Tensor:
     """The fused q|k|v projection with rotation and cache write in the epilogue: ``out`` [M, N] gets the
-    rotated q columns (the k and v columns are left unwritten); rotated k and v go to their pages."""
+    rotated q columns (the k and v columns are left unwritten); rotated k and v go to their pages.
+    ``x`` may be a DeferredNorm."""
+    deferred = x if isinstance(x, DeferredNorm) else None
+    if deferred is not None:
+        x = deferred.xw
     M, K = x.shape
     N = w.shape[0]
     if not supports(x, w, out) or not can_fuse_rope(x, w, num_heads, num_kv_heads, head_dim, rotary_dim):
         raise GemmTcError("these operands cannot take the fused rotation epilogue")
     pl = plan(M, N, K)
+    if deferred is not None:
+        _launch_fused(x, w, bias, out, M, N, K, pl, False, _fuse_struct(deferred),
+                      (positions, slots, cos, sin, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
+                       write_cache))
+        return out
     lib = build.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc_qkv_rope(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                                   ops._ptr(out), M, N, K, pl["bn"], pl["splits"], pl["stages"], int(pdl_enabled),

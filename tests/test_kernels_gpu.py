@@ -627,3 +627,103 @@ def test_gemm_tc_fused_rotation_and_cache_write(ops, H, Hkv, D, rot, M, K):
     untouched[slots.long()] = False
     assert (kc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()
     assert (vc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 2048, 2048), (1, 2048, 5632), (16, 2048, 5632), (13, 264, 320), (5, 1000, 840), (3, 128, 256)])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_gemm_tc_residual_epilogue(M, N, K, with_norm):
+    """res += x W^T + b on the float32 stream, and for the norm behind it xw = bf16(res * w_norm) and
+    sum(res^2) in slots, against the plain formulas."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + N + K)
+    assert gemm_tc.splits_k(M, N, K)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    b = (torch.randn(N) * 0.1).bfloat16()
+    res0 = torch.randn(M, N) * 2
+    nw = (torch.randn(N) * 0.2 + 1).bfloat16()
+    res = res0.clone().to(DEV)
+    d = gemm_tc.gemm_residual(x.to(DEV), w.to(DEV), res, b.to(DEV), nw.to(DEV) if with_norm else None, 1e-5)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    want = res0.double() + x.double() @ w.double().t() + b.double()
+    assert (res.cpu().double() - want).abs().max() <= 1e-5 * want.abs().max() + 1e-5     # float32 sums, another order
+    if not with_norm:
+        assert d is None
+        return
+    assert d.slots == d.sq.shape[0] and d.width == N and tuple(d.xw.shape) == (M, N)
+    close(d.xw, (want * nw.double()).float(), torch.bfloat16, "xw of the residual epilogue")
+    sq = d.sq[:, :M].sum(0).cpu().double()
+    assert ((sq - (want ** 2).sum(1)).abs() <= 1e-5 * (want ** 2).sum(1)).all()
+    # every launch writes every slot: run again on junk and compare (no stale share survives)
+    d.sq.fill_(1e9)
+    res2 = res0.clone().to(DEV)
+    d2 = gemm_tc.gemm_residual(x.to(DEV), w.to(DEV), res2, b.to(DEV), nw.to(DEV), 1e-5)
+    assert torch.equal(res2, res) and torch.equal(d2.sq[:, :M], gemm_tc.gemm_residual(
+        x.to(DEV), w.to(DEV), res0.clone().to(DEV), b.to(DEV), nw.to(DEV), 1e-5).sq[:, :M])
+
+
+@pytest.mark.parametrize("M,h,N", [(8, 2048, 2560), (16, 2048, 11264), (3, 264, 400), (1, 2048, 2048)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_gemm_tc_deferred_norm_factor(ops, M, h, N, swiglu):
+    """RMSNorm split across two products: the first leaves res * w and sum(res^2), the second scales its
+    sums by rsqrt(mean + eps).  Together they must match norm-then-product of the plain formulas."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + h + N)
+    eps, K0 = 1e-5, 512
+    a = (torch.randn(M, K0) * 0.5).bfloat16()
+    w0 = (torch.randn(h, K0) * 0.05).bfloat16()
+    res0 = torch.randn(M, h) * 3
+    nw = (torch.randn(h) * 0.2 + 1).bfloat16()
+    w1 = (torch.randn(N, h) * 0.05).bfloat16()
+    b1 = None if swiglu else (torch.randn(N) * 0.1).bfloat16().to(DEV)
+    assert gemm_tc.splits_k(M, h, K0) and gemm_tc.splits_k(M, N, h)
+    res = res0.clone().to(DEV)
+    d = gemm_tc.gemm_residual(a.to(DEV), w0.to(DEV), res, None, nw.to(DEV), eps)
+    out = torch.full((M, N // 2 if swiglu else N), 9.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm(d, w1.to(DEV), out, b1, swiglu=swiglu)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    r = res0.double() + a.double() @ w0.double().t()
+    normed = pl.rmsnorm(r.float(), nw.float(), eps).double()
+    y = normed @ w1.double().t()
+    if swiglu:
+        want = pl.swiglu(y[:, 0::2].float(), y[:, 1::2].float())
+    else:
+        want = (y + b1.cpu().double()).float()
+    close(out, want, torch.bfloat16, f"deferred norm factor {M}x{h}->{N} swiglu={swiglu}")
+
+
+def test_gemm_tc_deferred_norm_factor_with_rotation(ops):
+    """The q|k|v product with both epilogues: the norm factor first, then rotation and cache write."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(11)
+    H, Hkv, D, rot, M, h, page, num_pages, theta, max_pos, eps = 32, 4, 64, 64, 8, 2048, 16, 20, 10000.0, 600, 1e-5
+    N = (H + 2 * Hkv) * D
+    a = (torch.randn(M, 256) * 0.5).bfloat16()
+    w0 = (torch.randn(h, 256) * 0.05).bfloat16()
+    res0 = torch.randn(M, h) * 3
+    nw = (torch.randn(h) * 0.2 + 1).bfloat16()
+    w = (torch.randn(N, h) * 0.05).bfloat16()
+    positions = torch.randint(0, max_pos, (M,), dtype=torch.int32)
+    slots = torch.randperm((num_pages - 1) * page)[:M].to(torch.int32) + page
+    j = torch.arange(0, rot, 2, dtype=torch.int64).float()
+    cos, sin = ops.rope_tables((1.0 / (theta ** (j / rot))).to(DEV), max_pos)
+    k_cache = torch.full((num_pages, Hkv, page, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.full_like(k_cache, 7.0)
+    res = res0.clone().to(DEV)
+    d = gemm_tc.gemm_residual(a.to(DEV), w0.to(DEV), res, None, nw.to(DEV), eps)
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_qkv_rope(d, w.to(DEV), out, None, positions.to(DEV), slots.to(DEV), cos, sin, k_cache, v_cache, H, Hkv, D, rot, page)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    r = res0.double() + a.double() @ w0.double().t()
+    qkv = (pl.rmsnorm(r.float(), nw.float(), eps).double() @ w.double().t()).float()
+    q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], -1)
+    ang = pl.rope_angles(positions, rot, theta)
+    close(out[:, :H * D].reshape(M, H, D), pl.apply_rope(q.view(M, H, D), ang), torch.bfloat16, "rotated q behind a deferred norm")
+    kc, vc = k_cache.cpu().float(), v_cache.cpu().float()
+    for t in range(M):
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        close(kc[pg, :, off], pl.apply_rope(k.view(M, Hkv, D), ang)[t], torch.bfloat16, f"cached k of token {t}")
+        close(vc[pg, :, off], v.view(M, Hkv, D)[t], torch.bfloat16, f"cached v of token {t}")
