@@ -176,6 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_p = &abort_flag;
+    float pre_res[4] = {0.f, 0.f, 0.f, 0.f}, pre_wn = 0.f, pre_b = 0.f;     // residual epilogue: fetched ahead by the epilogue warps
 
     if (warp == 0) {
         if (lane == 0) {
@@ -233,8 +234,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         if (p.rope) {
             // what the rotation needs of this step -- positions, cache slots and the cos/sin rows of the
             // tile's tokens -- goes to shared memory now, while the weights stream, so that no look-up in
-            // global memory is left for the end of the kernel
-            grid_dep_wait();
+            // global memory is left for the end of the kernel.  Positions and slots are inputs of the step
+            // and the tables are constants: none of them is the previous kernel's output, so this does
+            // not wait for it.
             const int half = p.rotary_dim >> 1, et = threadIdx.x - 64;
             for (int i = et; i < BN; i += 128) {
                 const int t = b0 + i;
@@ -252,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         if (p.sq_in) {
             // the factor the norm before this product left for it: 128 / BN threads add up a token's slots,
             // each its share in slot order, then the shares in lane order -- the same order every time
-            if (!p.rope) grid_dep_wait();
+            grid_dep_wait();
             constexpr int TPT = BN >= 128 ? 1 : 128 / BN;    // threads per token
             const int et = threadIdx.x - 64;
             for (int i0 = 0; i0 < BN; i0 += 128 / TPT) {
@@ -264,6 +266,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 for (int o = TPT >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
                 if (sub == 0 && i < BN) rstd_s[i] = t < p.M ? rsqrtf(sum / p.sq_width + p.sq_eps) : 1.f;
             }                                                // read after the block-wide barrier below
+        }
+        if (p.res) {
+            // the stream values that this thread will add to (its first item of the owners' sum below) and
+            // the norm weight of its feature are fetched now, not at the end of the kernel
+            grid_dep_wait();
+            const int rows_per = TC_BM / p.splits, idx = threadIdx.x - 64;
+            if (idx < rows_per * (BN / 4)) {
+                const int n = a0 + split * rows_per + idx % rows_per, c = (idx / rows_per) * 4;
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (b0 + c + j < p.M) pre_res[j] = __ldcg(p.res + (int64_t)(b0 + c + j) * p.N + n);
+                    if (p.norm_w) pre_wn = load_tagged(p.norm_w, n, p.norm_w_tag);
+                    if (p.bias) pre_b = load_tagged(p.bias, n, p.bias_tag);
+                }
+            }
         }
         const bool have_work = n_kt > 0;                     // a split beyond the last k-tile adds a zero tile
         const bool ready = have_work ? mbar_wait(&tmem_full_bar, 0, abort_p) : true;
@@ -447,9 +465,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                     // group of lanes' share of sum(res^2): min(rows_per, 32) neighbouring lanes hold the same four
                     // tokens and consecutive features, so a shuffle tree over them adds up the features
                     const int n = a0 + rr;
-                    const bool live = n < p.N;
-                    const float b = (p.bias && live) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
-                    const float wn = (p.norm_w && live) ? load_tagged(p.norm_w, n, p.norm_w_tag) : 0.f;
+                    const bool live = n < p.N, ahead = idx == tid;           // the first item's values are here already
+                    float b = pre_b, wn = pre_wn, old[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) old[j] = pre_res[j];
+                    if (!ahead) {
+                        b = (p.bias && live) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+                        wn = (p.norm_w && live) ? load_tagged(p.norm_w, n, p.norm_w_tag) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)                        // all four loads before the first store
+                            old[j] = (live && b0 + c + j < p.M) ? __ldcg(p.res + (int64_t)(b0 + c + j) * p.N + n) : 0.f;
+                    }
                     float sq[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -457,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         sq[j] = 0.f;
                         if (live && t < p.M) {
                             const int64_t at = (int64_t)t * p.N + n;
-                            const float rv = p.res[at] + acc[j] + b;
+                            const float rv = old[j] + acc[j] + b;
                             p.res[at] = rv;
                             if (p.xw_out) p.xw_out[at] = __float2bfloat16_rn(rv * wn);
                             sq[j] = rv * rv;

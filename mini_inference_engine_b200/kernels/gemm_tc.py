@@ -69,9 +69,24 @@ class DeferredNorm:
     width: int
     eps: float
 
+    # enough of a tensor's face for the checks that size a product
     @property
     def shape(self):
         return self.xw.shape
+
+    @property
+    def dtype(self):
+        return self.xw.dtype
+
+    @property
+    def is_cuda(self):
+        return self.xw.is_cuda
+
+    def is_contiguous(self):
+        return self.xw.is_contiguous()
+
+    def data_ptr(self):
+        return self.xw.data_ptr()
 
 
 class _Fuse(ctypes.Structure):

@@ -40,12 +40,34 @@ def uses_tcgen05(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16) -> 
     return K % 8 == 0 and w.shape[0] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
+def splits_k_on_tcgen05(num_tokens: int, w: torch.Tensor) -> bool:
+    """Whether the product of ``num_tokens`` bfloat16 rows with ``w`` runs on the tcgen05 kernel with K
+    split across a cluster -- the form that carries the residual and the norm-factor epilogues."""
+    if w.dtype != torch.bfloat16 or _bf16_backend in ("library", "simt") or num_tokens < 1 or not w.is_cuda:
+        return False
+    if _bf16_backend == "auto" and num_tokens > AUTO_MAX_TOKENS:
+        return False
+    N, K = w.shape
+    return K % 8 == 0 and N % 8 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0 and gemm_tc.splits_k(num_tokens, N, K)
+
+
+def linear_into_stream(x, w: torch.Tensor, bias, res: torch.Tensor, norm_weight, eps: float):
+    """res += x W^T (+ b) inside the product (``res`` float32, in place) and, for the RMSNorm with
+    ``norm_weight`` that reads the stream next, the DeferredNorm for the product behind it.  Returns
+    False where this product cannot do that (the caller then adds the product's output as before)."""
+    if not splits_k_on_tcgen05(x.shape[0], w) or x.dtype != torch.bfloat16 or res.dtype != torch.float32:
+        return False
+    return gemm_tc.gemm_residual(x, w, res, bias, norm_weight, eps)
+
+
+def linear(x, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
     M = x.shape[0]
     N = w.shape[0]
-    out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    out = torch.empty(M, N, dtype=out_dtype, device=w.device)
     if M == 0:
         return out
+    if isinstance(x, gemm_tc.DeferredNorm):          # only handed out where splits_k_on_tcgen05 said yes
+        return gemm_tc.gemm(x, w, out, bias)
     if x.dtype == torch.float32 or w.dtype == torch.float32 or _bf16_backend == "simt":
         return ops.gemm_simt(x, w, out, bias)
     if uses_tcgen05(x, w, out_dtype) and gemm_tc.supports(x, w, out):
@@ -70,9 +92,11 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch
     """silu(x Wg^T) * (x Wu^T) for a weight whose rows alternate gate_i, up_i: fused into the
     tcgen05 product's epilogue where that kernel runs, else the product followed by the SwiGLU kernel."""
     M, inter = x.shape[0], w_interleaved.shape[0] // 2
-    out = torch.empty(M, inter, dtype=out_dtype, device=x.device)
+    out = torch.empty(M, inter, dtype=out_dtype, device=w_interleaved.device)
     if M == 0:
         return out
+    if isinstance(x, gemm_tc.DeferredNorm):
+        return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
     if uses_tcgen05(x, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and gemm_tc.supports(x, w_interleaved, out):
         return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
     gu = linear(x, w_interleaved, None, out_dtype)

@@ -9,6 +9,8 @@ pure-decode step; here the wanted positions are always explicit).
 """
 from __future__ import annotations
 
+import inspect
+
 import torch
 
 from ..cache.storage import CacheLayout, CacheStorage
@@ -81,6 +83,8 @@ class DecoderModel:
             sk.head.bind({}, rt, shared=sk.embedding.weight)
         self.embedding, self.final_norm, self.head, self.blocks = sk.embedding, sk.final_norm, sk.head, sk.blocks
         self.run_order = spec.run_order
+        # a block that can be told which block runs after it (to prepare that block's first norm)
+        self._takes_next = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]
         needs: dict = {}
         for e in self.run_order:                   # a cache's shape is what the layers that use it declare
             need = self.blocks[e.layer].mixer.cache_need()
@@ -120,8 +124,13 @@ class DecoderModel:
             raise RuntimeError("allocate_cache() must be called before step()")
         res = self.embedding.forward(ctx)
         delta = None
-        for entry, cache in zip(self.run_order, self._caches):
-            delta = self.blocks[entry.layer].forward(delta, res, ctx, cache)
+        last = len(self.run_order) - 1
+        for i, (entry, cache) in enumerate(zip(self.run_order, self._caches)):
+            block = self.blocks[entry.layer]
+            if self._takes_next[entry.layer] and i < last:
+                delta = block.forward(delta, res, ctx, cache, next_block=self.blocks[self.run_order[i + 1].layer])
+            else:
+                delta = block.forward(delta, res, ctx, cache)
         if ctx.want.numel() == 0:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.rt.device)
         x = self.final_norm(delta, res, rows=ctx.want)

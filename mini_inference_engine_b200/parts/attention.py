@@ -59,11 +59,20 @@ class Attention(Mixer):
     def cache_need(self):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, cache):
+    takes_sink = True
+
+    def defers_norm(self, num_tokens: int) -> bool:
+        return self.rt.defers_norm(num_tokens, self.w_qkv)
+
+    def forward(self, x, ctx, cache, sink=None):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = self.position.project_rotate_and_store(x, self.w_qkv, self.b_qkv, ctx, cache, H, Hkv)
         out = self.rt.empty(ctx.num_tokens, H * D)
         attn_kernels.attention(qkv, ctx, cache, out, H, Hkv, D, self.scale, self.window)
+        if sink is not None:
+            done = self.rt.linear_into_stream(out, self.w_o, None, sink)
+            if done is not None:
+                return done
         return self.rt.linear(out, self.w_o)
 
 

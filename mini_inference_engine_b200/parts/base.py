@@ -109,6 +109,23 @@ class StepContext:
     token_feedback: torch.Tensor | None = None   # int32: tokens the previous step sampled; a token id -(k+1) means entry k
 
 
+@dataclass
+class ResidualSink:
+    """What a block may offer a mixer or feed-forward in place of adding its output afterwards: the
+    float32 stream ``res`` and the norm that reads the stream next.  A part that takes the offer adds
+    its output to ``res`` itself (in its last product's epilogue) and returns a StreamUpdated."""
+    res: torch.Tensor
+    norm: object
+
+
+@dataclass
+class StreamUpdated:
+    """Returned instead of an output: the stream already holds the sum.  ``deferred`` is what the part
+    prepared for ``norm`` (see kernels/gemm_tc.py: DeferredNorm), or None."""
+    norm: object
+    deferred: object
+
+
 class Runtime:
     """Device, activation type and the matrix product for that type.  ``float32`` runs every
     product on CUDA cores in true 32-bit; ``bfloat16`` uses the tensor-core product for 16-bit
@@ -133,9 +150,27 @@ class Runtime:
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, bias=None, out_dtype=None) -> torch.Tensor:
+    def linear(self, x, w: torch.Tensor, bias=None, out_dtype=None) -> torch.Tensor:
         from ..kernels import linear as _linear
         return _linear.linear(x, w, bias, out_dtype or self.dtype)
+
+    def defers_norm(self, num_tokens: int, w: torch.Tensor) -> bool:
+        """Whether the product with ``w`` can take the norm in front of it as a factor on its sums
+        (its input then comes as a DeferredNorm from ``linear_into_stream``)."""
+        from ..kernels import linear as _linear
+        return self.dtype == torch.bfloat16 and _linear.splits_k_on_tcgen05(num_tokens, w)
+
+    def linear_into_stream(self, x, w: torch.Tensor, bias, sink: ResidualSink):
+        """The last product of a part, adding to the stream of ``sink`` in its epilogue and preparing
+        the input of the product behind ``sink.norm``.  Returns a StreamUpdated, or None where that
+        is not possible (the part then returns its output as usual)."""
+        from ..kernels import linear as _linear
+        args = getattr(sink.norm, "deferred_args", None)
+        if args is None or self.dtype != torch.bfloat16:
+            return None
+        weight, eps = args()
+        d = _linear.linear_into_stream(x, w, bias, sink.res, weight, eps)
+        return None if d is False else StreamUpdated(sink.norm, d)
 
 
 class Part:

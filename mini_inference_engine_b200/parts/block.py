@@ -5,7 +5,16 @@ is fused into the *next* norm, so a block takes the pending ``delta`` and return
 add+norm, after the last layer into the final norm)."""
 from __future__ import annotations
 
-from .base import Part, build_part, register_part
+from .base import Part, ResidualSink, build_part, register_part
+
+
+def _sink_for(producer, consumer, norm, res, num_tokens):
+    """The offer to ``producer`` (None if it would not take one): it may add to the stream itself when
+    the part behind ``norm`` can take that norm as a factor on its first product."""
+    if not getattr(producer, "takes_sink", False) or consumer is None:
+        return None
+    ok = getattr(consumer, "defers_norm", None)
+    return ResidualSink(res, norm) if ok is not None and ok(num_tokens) else None
 
 
 class PreNormResidual(Part):
@@ -15,11 +24,16 @@ class PreNormResidual(Part):
         self.mixer_norm = mixer_norm
         self.feed_forward_norm = feed_forward_norm
 
-    def forward(self, delta, res, ctx, cache):
+    def forward(self, delta, res, ctx, cache, next_block=None):
+        """``next_block``: the block that runs after this one, if it reads the stream through a norm
+        and a mixer as this one does (then the feed-forward may prepare that norm's output)."""
+        n = res.shape[0]
         x = self.mixer_norm(delta, res)
-        a = self.mixer.forward(x, ctx, cache)
+        sink = _sink_for(self.mixer, self.feed_forward, self.feed_forward_norm, res, n)
+        a = self.mixer.forward(x, ctx, cache, sink) if sink is not None else self.mixer.forward(x, ctx, cache)
         x = self.feed_forward_norm(a, res)
-        return self.feed_forward.forward(x, ctx)
+        sink = _sink_for(self.feed_forward, getattr(next_block, "mixer", None), getattr(next_block, "mixer_norm", None), res, n)
+        return self.feed_forward.forward(x, ctx, sink) if sink is not None else self.feed_forward.forward(x, ctx)
 
 
 register_part("block", "prenorm_residual", PreNormResidual)

@@ -34,13 +34,22 @@ class SwiGLU(FeedForward):
             self.w_gate_up = rt.place(torch.cat([g, u], 0))
         self.w_down = rt.place(tensors["down_proj.weight"])
 
-    def forward(self, x, ctx):
+    takes_sink = True
+
+    def defers_norm(self, num_tokens: int) -> bool:
+        return self.rt.defers_norm(num_tokens, self.w_gate_up)
+
+    def forward(self, x, ctx, sink=None):
         if self.interleaved:
             act = linear_kernels.linear_swiglu(x, self.w_gate_up, self.rt.dtype)
         else:
             gu = self.rt.linear(x, self.w_gate_up)
             act = self.rt.empty(x.shape[0], self.intermediate_size)
             ops.swiglu(gu, act)
+        if sink is not None:
+            done = self.rt.linear_into_stream(act, self.w_down, None, sink)
+            if done is not None:
+                return done
         return self.rt.linear(act, self.w_down)
 
 
