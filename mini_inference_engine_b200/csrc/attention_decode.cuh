@@ -42,7 +42,10 @@ decode_attention_kernel(const DecodeParams p) {
     // value (and the queries) afterwards.
     pdl_launch_dependents();
     const int row = blockIdx.z;
-    if (p.row_q_len[row] != 1) return;
+    if (p.row_q_len[row] != 1) {                                   // another kernel's row
+        pdl_wait();                                                // no block ends before the kernel in front has: later kernels rely on it
+        return;
+    }
     const int G = p.num_heads / p.num_kv_heads;
     const int kvh = blockIdx.y / p.chunks, chunk = blockIdx.y - kvh * p.chunks;
     const int g0 = chunk * 16, gn = min(16, G - g0);               // query heads of this block within the group

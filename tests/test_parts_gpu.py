@@ -151,6 +151,72 @@ def test_block_part(dt):
     close(got, want_delta, dt, "block output")
 
 
+def test_blocks_that_fold_their_norms_into_the_products():
+    """Few tokens in bfloat16 at sizes where the tensor-core product splits K: the mixer and the
+    feed-forward take the block's offer, add to the stream in their last product and prepare the next
+    norm; the norm then launches nothing and hands the prepared input on.  Two blocks in a row, the
+    second told about by the first, against the plain formulas; and the same blocks without the offer."""
+    from mini_inference_engine_b200.config import LayerSpec, PartSpec
+    from mini_inference_engine_b200.kernels import gemm_tc, ops
+    from mini_inference_engine_b200.models.decoder import _layer_parts
+    from mini_inference_engine_b200.parts import LayerCache
+    from mini_inference_engine_b200.parts.base import StreamUpdated
+    dt = torch.bfloat16
+    rt = rt_for(dt)
+    h, H, Hkv, D, I, T, eps = 512, 8, 2, 64, 1024, 5, 1e-5
+    norm = dict(size=h, eps=eps)
+    blocks, Ws = [], []
+    for b in range(2):
+        ls = LayerSpec("prenorm_residual",
+                       PartSpec("attention", dict(hidden_size=h, num_heads=H, num_kv_heads=Hkv, head_dim=D,
+                                                  position=PartSpec("rope", dict(head_dim=D, rotary_dim=D, theta=1e4, max_position=64))), "a."),
+                       PartSpec("swiglu", dict(hidden_size=h, intermediate_size=I), "f."),
+                       PartSpec("rmsnorm", norm, "n1."), PartSpec("rmsnorm", norm, "n2."))
+        block, named = _layer_parts(ls)
+        W = {}
+        for i, (prefix, part) in enumerate(named):
+            torch.manual_seed(100 * b + i)
+            tensors = {n: (torch.randn(sp.shape) * (0.04 if len(sp.shape) > 1 else 1.0)).to(dt) for n, sp in part.tensor_specs().items()}
+            part.bind(tensors, rt)
+            W.update({prefix + k: v.float() for k, v in tensors.items()})
+        blocks.append(block)
+        Ws.append(W)
+    assert blocks[0].mixer.defers_norm(T) and blocks[0].feed_forward.defers_norm(T)
+    res0, delta0 = torch.randn(T, h), torch.randn(T, h).to(dt)
+    cfg = dict(heads=H, kv_heads=Hkv, head_dim=D, theta=1e4, bias=False)
+    r = res0 + delta0.float()
+    for W in Ws:                                                  # the plain formulas, two layers
+        r = r + pl.attention_layer(pl.round_bf16(pl.rmsnorm(r, W["n1.weight"], eps)), W, "a.", cfg, torch.arange(T), pl.round_bf16)
+        last_delta = pl.feed_forward(pl.round_bf16(pl.rmsnorm(r, W["n2.weight"], eps)), W, "f.", pl.round_bf16)
+        r_before_ff = r
+        r = r + last_delta
+
+    def run(tell_next):
+        kv = torch.zeros(2, 2, 6, Hkv, 16, D, dtype=dt, device=DEV)
+        res = res0.to(DEV)
+        ctx = ctx_for([([0] * T, 0, [3, 4], [])], 16, None)
+        before = ops.launches
+        d = blocks[0].forward(delta0.to(DEV), res, ctx, LayerCache(group=0, k=kv[0, 0], v=kv[0, 1], page_size=16),
+                              **({"next_block": blocks[1]} if tell_next else {}))
+        mid = d
+        d = blocks[1].forward(d, res, ctx, LayerCache(group=0, k=kv[1, 0], v=kv[1, 1], page_size=16))
+        torch.cuda.synchronize()
+        gemm_tc.check_error()
+        return mid, d, res, ops.launches - before
+
+    mid, d, res, launches = run(True)
+    assert isinstance(mid, StreamUpdated) and mid.norm is blocks[1].mixer_norm and mid.deferred is not None
+    close(d, last_delta, dt, "output of the second block")       # the last block has nobody to prepare for
+    close(res, r_before_ff, dt, "stream after three folded sums")
+    mid2, d2, res2, launches2 = run(False)
+    assert isinstance(mid2, torch.Tensor)
+    close(d2, last_delta, dt, "output without telling the first block about the second")
+    close(res2, r_before_ff, dt, "stream without it")
+    # folded: norm, q|k|v, attention, out, gate/up, down + q|k|v, attention, out, gate/up, down; the
+    # untold first block ends with a plain product and the second starts with a norm kernel
+    assert launches == 11 and launches2 == 12
+
+
 def test_run_order_is_data_a_layer_twice_and_a_shared_cache(tmp_path):
     """A model whose run order names layer 0 twice (own cache each time) and lets layer 1 read the
     cache that the first run of layer 0 wrote.  Whole sequence == portion + single tokens."""
