@@ -17,8 +17,11 @@
 //
 // The reference does this with a library attention call per prompt portion
 // (inference_engine/model.py:146-158).  A block works through its key tiles one after the other
-// (S, softmax, PV); two blocks share an SM at head_dim 64 (256 TMEM columns and 80 KB of shared
-// memory each), so one block's softmax runs under the other's products.
+// (S, softmax, PV); two blocks share an SM at head_dim 64 (256 TMEM columns and 97 KB of shared
+// memory each), so one block's softmax runs under the other's products.  When a launch has more
+// query tiles than the GPU runs at a time, a block takes two tiles of a row one after the other,
+// the j-th from the end and the j-th from the start: under the causal mask every such pair has the
+// same number of key tiles, so the blocks end together instead of leaving a tail of long ones.
 //
 // Roles: warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane), warps 2..5 =
 // softmax and epilogue.  Barriers: q_full, kv_full[2] / kv_empty[2] (two key/value stages; kv_empty
@@ -41,6 +44,7 @@ struct FaParams {
     bf16* out;
     int* error;
     int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
+    int pair;                // 1: a block takes two query tiles of a row (see the kernel), 0: one
     float scale_log2e;
 };
 
@@ -102,23 +106,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     constexpr uint32_t TMEM_S = 0, TMEM_P = 128, TMEM_O = 192;  // column offsets: S 128 cols, P 64 cols (bf16 pairs), O D cols
     constexpr uint32_t TMEM_COLS = D == 64 ? 256 : 512;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full;
+    __shared__ __align__(8) uint64_t q_full[2], kv_full[2], kv_empty[2], s_full, p_full, o_full;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag, s_row, s_q0;
+    __shared__ int abort_flag, s_row, s_q0[2], s_nsub;
 
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* tiles = smem_dyn + (base - smem_u32(smem_dyn));
-    // layout: Q | K stage 0 | V stage 0 | K stage 1 | V stage 1
-    const uint32_t q_addr = base;
-    auto k_addr = [&](int s) { return base + Q_BYTES + (uint32_t)s * 2 * KV_BYTES; };
-    auto v_addr = [&](int s) { return base + Q_BYTES + (uint32_t)s * 2 * KV_BYTES + KV_BYTES; };
+    // layout: Q of the first query tile | Q of the second | K stage 0 | V stage 0 | K stage 1 | V stage 1
+    auto q_addr = [&](int u) { return base + (uint32_t)u * Q_BYTES; };
+    auto k_addr = [&](int s) { return base + 2 * Q_BYTES + (uint32_t)s * 2 * KV_BYTES; };
+    auto v_addr = [&](int s) { return base + 2 * Q_BYTES + (uint32_t)s * 2 * KV_BYTES + KV_BYTES; };
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        mbar_init(&q_full, 1);
+        mbar_init(&q_full[0], 1); mbar_init(&q_full[1], 1);
         mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
         mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
         mbar_init(&s_full, 1); mbar_init(&p_full, 4); mbar_init(&o_full, 1);
@@ -127,7 +131,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     }
     // key/value rows that no copy fills (beyond the context) must hold finite values: 0 * NaN is NaN
     for (uint32_t i = threadIdx.x * 16; i < 4 * KV_BYTES; i += FA_THREADS * 16)
-        *reinterpret_cast<uint4*>(tiles + Q_BYTES + i) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(tiles + 2 * Q_BYTES + i) = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the TMA unit must see the zeros before it overwrites them
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
@@ -136,16 +140,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     pdl_wait();                                                  // everything below reads what earlier kernels wrote
 
     if (threadIdx.x == 0) {
-        // tiles are numbered from the end of each row backwards: the longest key ranges start first
-        int tile = blockIdx.x, r = 0;
+        // A block takes two query tiles of a row, one after the other: the j-th from the end and the j-th
+        // from the start.  Under the causal mask their key ranges add up to the same length for every j,
+        // so all blocks of a row run equally long (the middle tile of an odd count stands alone).
+        // Pairing pays once there are more tiles than the GPU runs at a time (p.pair, the host's call):
+        // below that every tile has a block of its own and the longest one is the critical path.
+        int pair = blockIdx.x, r = 0, tiles_r = 0;
         for (; r < p.num_rows; ++r) {
             const int ql = p.row_q_len[r];
-            const int tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
-            if (tile < tiles_r) { tile = tiles_r - 1 - tile; break; }
-            tile -= tiles_r;
+            tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
+            const int blocks_r = p.pair ? (tiles_r + 1) / 2 : tiles_r;
+            if (pair < blocks_r) break;
+            pair -= blocks_r;
         }
         s_row = r < p.num_rows ? r : -1;
-        s_q0 = tile * FA_BM;
+        s_q0[0] = (tiles_r - 1 - pair) * FA_BM;                 // the longest key ranges start first
+        s_q0[1] = pair * FA_BM;
+        s_nsub = (p.pair && tiles_r - 1 - pair != pair) ? 2 : 1;
     }
     tc_fence_before();
     __syncthreads();
@@ -155,16 +166,27 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     const int row = s_row;
 
     if (row >= 0) {
-        const int q0 = s_q0;
         const int q_len = p.row_q_len[row], ctx = p.row_ctx_len[row], q_start = p.row_q_start[row];
         const int head = blockIdx.y;
         const int kvh = head / (p.num_heads / p.num_kv_heads);
-        const int pos0 = ctx - q_len + q0;                       // position of the tile's first query
-        const int nq = min(FA_BM, q_len - q0);
-        const int k_hi = pos0 + nq;                              // one past the last key any query here reads
-        const int k_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-        const int kbeg = k_lo & ~(FA_BN - 1);
-        const int ntiles = (k_hi - kbeg + FA_BN - 1) / FA_BN;
+        const int nsub = s_nsub;
+        // the geometry of query tile u: first query's position, rows, key range in tiles of FA_BN keys
+        struct Sub { int q0, pos0, nq, k_hi, k_lo, kbeg, ntiles; };
+        Sub sb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            Sub& g = sb[u];
+            g.q0 = s_q0[u < nsub ? u : 0];
+            g.pos0 = ctx - q_len + g.q0;                         // position of the tile's first query
+            g.nq = min(FA_BM, q_len - g.q0);
+            g.k_hi = g.pos0 + g.nq;                              // one past the last key any query here reads
+            g.k_lo = p.window > 0 ? max(0, g.pos0 - p.window + 1) : 0;
+            g.kbeg = g.k_lo & ~(FA_BN - 1);
+            g.ntiles = u < nsub ? (g.k_hi - g.kbeg + FA_BN - 1) / FA_BN : 0;
+        }
+        const int nA = sb[0].ntiles, G = nA + sb[1].ntiles;      // key tiles of the first query tile, and of both
+        // Key tiles are counted through both query tiles (g = 0 .. G-1): stages and barrier phases go on
+        // from the first query tile to the second without a break.
         const int rows_per_copy = min(p.page_size, FA_BN);       // one TMA copy = one page (or a 128-row piece of it)
 
         if (warp == 0) {
@@ -173,33 +195,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
             // freed stage and its refill.
             const int* table = p.block_tables + (int64_t)row * p.table_stride;
             if (lane == 0) {
-                mbar_expect_tx(&q_full, Q_BYTES);
+                for (int u = 0; u < nsub; ++u) {
+                    mbar_expect_tx(&q_full[u], Q_BYTES);
 #pragma unroll
-                for (int part = 0; part < PARTS; ++part)
-                    tma_load_2d(tiles + part * SUB_BYTES, &map_q, &q_full, head * D + part * 64, q_start + q0);
+                    for (int part = 0; part < PARTS; ++part)
+                        tma_load_2d(tiles + u * Q_BYTES + part * SUB_BYTES, &map_q, &q_full[u], head * D + part * 64, q_start + sb[u].q0);
+                }
             }
-            auto copies_of = [&](int t) {
-                const int key0 = kbeg + t * FA_BN;
-                return (min(key0 + FA_BN, k_hi) - key0 + rows_per_copy - 1) / rows_per_copy;
+            auto key0_of = [&](int g) { return g < nA ? sb[0].kbeg + g * FA_BN : sb[1].kbeg + (g - nA) * FA_BN; };
+            auto copies_of = [&](int g) {
+                const int key0 = key0_of(g), hi = g < nA ? sb[0].k_hi : sb[1].k_hi;
+                return (min(key0 + FA_BN, hi) - key0 + rows_per_copy - 1) / rows_per_copy;
             };
-            auto page_of = [&](int t) {                           // lane's page id in tile t (0 if it has no copy there)
-                const int key = kbeg + t * FA_BN + lane * rows_per_copy;
-                return (t < ntiles && lane < copies_of(t)) ? table[key >> p.page_shift] : 0;
+            auto page_of = [&](int g) {                           // lane's page id in key tile g (0 if it has no copy there)
+                if (g >= G || lane >= copies_of(g)) return 0;
+                return table[(key0_of(g) + lane * rows_per_copy) >> p.page_shift];
             };
             int page_next = page_of(0);
-            for (int t = 0; t < ntiles; ++t) {
-                const int s = t & 1, round = t >> 1;
+            for (int g = 0; g < G; ++g) {
+                const int s = g & 1, round = g >> 1;
                 const int page = page_next;
-                page_next = page_of(t + 1);
+                page_next = page_of(g + 1);
                 int ok = 1;
                 if (lane == 0) ok = mbar_wait(&kv_empty[s], (round & 1) ^ 1, abort_p) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                const int copies = copies_of(t);
+                const int copies = copies_of(g);
                 if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)copies * rows_per_copy * 128u * PARTS * 2u);
                 __syncwarp();
                 if (lane < copies) {
-                    const int key = kbeg + t * FA_BN + lane * rows_per_copy;
+                    const int key = key0_of(g) + lane * rows_per_copy;
                     const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
 #pragma unroll
                     for (int part = 0; part < PARTS; ++part) {
@@ -217,11 +242,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 // One thread issues every MMA, and between two of them it can do little: the descriptors
                 // of all operand slices are formed once, here, so that an MMA costs its own instruction.
                 constexpr int KS = D / 16, KV = FA_BN / 16;
-                uint64_t dq[KS], dk[2][KS], dv[2][KV];
+                uint64_t dq[2][KS], dk[2][KS], dv[2][KV];
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     const uint32_t off = (ks / 4) * SUB_BYTES + (ks % 4) * 32;
-                    dq[ks] = umma_desc_sw128(q_addr + off);
+                    dq[0][ks] = umma_desc_sw128(q_addr(0) + off);
+                    dq[1][ks] = umma_desc_sw128(q_addr(1) + off);
                     dk[0][ks] = umma_desc_sw128(k_addr(0) + off);
                     dk[1][ks] = umma_desc_sw128(k_addr(1) + off);
                 }
@@ -230,29 +256,33 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     dv[0][kk] = umma_desc_sw128_mn(v_addr(0) + kk * 2048, SUB_BYTES);
                     dv[1][kk] = umma_desc_sw128_mn(v_addr(1) + kk * 2048, SUB_BYTES);
                 }
-                auto issue_s = [&](int st) {
+                auto issue_s = [&](int g) {                        // scores of key tile g against its query tile
+                    const bool second = g >= nA, st = g & 1;
 #pragma unroll
                     for (int ks = 0; ks < KS; ++ks)
-                        umma_bf16(tmem_base + TMEM_S, dq[ks], st ? dk[1][ks] : dk[0][ks], idesc_s, ks > 0 ? 1u : 0u);
+                        umma_bf16(tmem_base + TMEM_S, second ? dq[1][ks] : dq[0][ks], st ? dk[1][ks] : dk[0][ks], idesc_s, ks > 0 ? 1u : 0u);
                     umma_commit(&s_full);
                 };
-                // Order per key tile: as soon as the softmax warps have taken S(t) (p_full), S(t+1) is issued
-                // ahead of P(t) V(t), so that the next scores are ready while the tensor pipe still works on
+                // Order per key tile: as soon as the softmax warps have taken S(g) (p_full), S(g+1) is issued
+                // ahead of P(g) V(g), so that the next scores are ready while the tensor pipe still works on
                 // this tile's values -- the softmax warps never wait for a product that they do not need yet.
                 // kv_empty (the commit behind P V) also tells them when P may be overwritten and O rescaled:
                 // a commit costs the issuing thread as much as two MMAs, so one serves both.
-                bool ok = mbar_wait(&q_full, 0, abort_p);
+                bool ok = mbar_wait(&q_full[0], 0, abort_p);
+                if (ok && nsub > 1) ok = mbar_wait(&q_full[1], 0, abort_p);
                 if (ok) ok = mbar_wait(&kv_full[0], 0, abort_p);
                 if (ok) { tc_fence_after(); issue_s(0); }
-                for (int t = 0; t < ntiles && ok; ++t) {
-                    const int s = t & 1;
-                    ok = mbar_wait(&p_full, t & 1, abort_p);       // P written, O rescaled, S free
+                for (int g = 0; g < G && ok; ++g) {
+                    const int s = g & 1;
+                    const int t = g < nA ? g : g - nA;             // key tile within its query tile
+                    const bool last_of_tile = g == nA - 1 || g == G - 1;
+                    ok = mbar_wait(&p_full, g & 1, abort_p);       // P written, O rescaled, S free
                     if (!ok) break;
                     tc_fence_after();
-                    bool next_issued = t + 1 >= ntiles;
-                    if (!next_issued && mbar_try_wait(&kv_full[s ^ 1], ((t + 1) >> 1) & 1)) {   // keys of the next tile are here
+                    bool next_issued = g + 1 >= G;
+                    if (!next_issued && mbar_try_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1)) {   // keys of the next tile are here
                         tc_fence_after();
-                        issue_s(s ^ 1);
+                        issue_s(g + 1);
                         next_issued = true;
                     }
 #pragma unroll
@@ -260,24 +290,28 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         umma_bf16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + kk * 8, s ? dv[1][kk] : dv[0][kk], idesc_o,
                                      (t > 0 || kk > 0) ? 1u : 0u);
                     umma_commit(&kv_empty[s]);                     // the stage may be refilled, P overwritten and O rescaled
+                    if (last_of_tile) umma_commit(&o_full);        // this query tile's output is complete
                     if (!next_issued) {                            // the keys were late: wait for them now
-                        ok = mbar_wait(&kv_full[s ^ 1], ((t + 1) >> 1) & 1, abort_p);
+                        ok = mbar_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1, abort_p);
                         if (!ok) break;
                         tc_fence_after();
-                        issue_s(s ^ 1);
+                        issue_s(g + 1);
                     }
                 }
-                if (ok) umma_commit(&o_full);
             }
         } else {
             const int q = warp & 3;
             const int r = q * 32 + lane;                           // this thread's query row within the tile
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            bool ok = true;
+            for (int u = 0; u < nsub && ok; ++u) {                 // one query tile after the other
+            const int q0 = sb[u].q0, pos0 = sb[u].pos0, nq = sb[u].nq, k_lo = sb[u].k_lo, kbeg = sb[u].kbeg, ntiles = sb[u].ntiles;
+            const int g0 = u ? nA : 0;                             // key tiles counted through both query tiles
             const int qpos = pos0 + r;
             float m_run = -INFINITY, l_run = 0.f;
-            bool ok = true;
             for (int t = 0; t < ntiles && ok; ++t) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&s_full, t & 1, abort_p));     // the warp goes on or gives up as one
+                const int g = g0 + t;
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full, g & 1, abort_p));     // the warp goes on or gives up as one
                 if (!ok) break;
                 tc_fence_after();
                 const int key0 = kbeg + t * FA_BN;
@@ -334,7 +368,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     for_each_chunk([&](int ch, const uint32_t* c) {
                         uint32_t packed[16];
                         // P(t-1) must have been read by its product before it is overwritten (normally long done)
-                        if (ch == 0 && t > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_p))) ok = false;
+                        if (ch == 0 && g > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_p))) ok = false;
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
@@ -387,7 +421,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 if (lane == 0) mbar_arrive(&p_full);              // one arrival per warp
             }
             // epilogue: O / l -> bfloat16 -> out[token, head, :]
-            if (ok) ok = mbar_wait(&o_full, 0, abort_p);
+            if (ok) ok = mbar_wait(&o_full, u & 1, abort_p);
             tc_fence_after();
             __syncwarp();
             if (__all_sync(0xffffffffu, ok)) {                      // warp-wide loads: every lane reads, rows inside the tile store
@@ -406,6 +440,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     *reinterpret_cast<uint4*>(op + c) = w0;
                     *reinterpret_cast<uint4*>(op + c + 8) = w1;
                 }
+                // the next query tile's first PV product overwrites O: it follows p_full, which this warp
+                // gives only after these loads
+                tc_fence_before();
+            }
             }
         }
     }
@@ -438,11 +476,16 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
 template <int D>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
                      cudaStream_t stream) {
-    const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 5 + 1024;     // Q + 2 x (K + V)
+    const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 6 + 1024;     // 2 x Q + 2 x (K + V)
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const dim3 grid((num_tokens + FA_BM - 1) / FA_BM + p.num_rows, p.num_heads);
-    return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, p);
+    // tiles <= tokens / 128 + rows; a block takes one tile, or a pair of them (at most (tiles + rows) / 2
+    // pairs) once the tiles of all heads are more than the GPU runs at a time
+    const int tiles = (num_tokens + FA_BM - 1) / FA_BM + p.num_rows;
+    FaParams pp = p;
+    pp.pair = (int64_t)tiles * p.num_heads > 148 * (D == 64 ? 2 : 1);
+    const dim3 grid(pp.pair ? (tiles + p.num_rows + 1) / 2 : tiles, p.num_heads);
+    return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, pp);
 }
 
 // q: the fused qkv activation [num_tokens, q_stride] bfloat16 (query head h at columns h*D ..), caches
@@ -469,7 +512,7 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
-    p.window = window; p.min_q_len = min_q_len;
+    p.window = window; p.min_q_len = min_q_len; p.pair = 0;
     p.scale_log2e = scale * 1.4426950408889634f;
     CUtensorMap mq, mk, mv;
     const int box_rows = page_size < FA_BN ? page_size : FA_BN;

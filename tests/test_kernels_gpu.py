@@ -575,6 +575,22 @@ def test_prefill_attention_tc_one_far_key(ops, far):
     close(out, want, torch.bfloat16, f"tcgen05 prefill far key {far}")
 
 
+@pytest.mark.parametrize("H,Hkv,D,rows,window", [
+    (32, 4, 64, [(2048, 2048)], None),                                   # 16 tiles: 8 pairs of 17 key tiles each
+    (32, 4, 64, [(700, 900), (1300, 1300), (129, 500), (1, 40), (257, 257)], None),   # 6, 11, 2, 1 and 3 tiles: odd counts, a lone middle tile
+    (32, 8, 64, [(1100, 1100), (900, 2000)], 300),                       # a window: the two tiles of a pair start at different keys
+    (16, 2, 128, [(1500, 1500), (1000, 1200)], None),                    # head size 128: one block per SM
+])
+def test_prefill_attention_tc_pairs_of_query_tiles(ops, H, Hkv, D, rows, window):
+    """With more query tiles than the GPU runs at a time a block takes two tiles of a row, one after
+    the other (the j-th from the end and the j-th from the start), and stages and barrier phases run on
+    from the first to the second.  Sizes chosen so that the launch pairs."""
+    tiles = sum((q + 127) // 128 for q, _ in rows) + len(rows)
+    assert tiles * H > 148 * (2 if D == 64 else 1)
+    out, want = _paged_case(ops, torch.bfloat16, H, Hkv, D, 16, rows, window=window, seed=H + D, kernel="prefill_tc")
+    close(out, want, torch.bfloat16, f"tcgen05 prefill in pairs, rows {rows} window {window}")
+
+
 def test_prefill_attention_tc_skips_single_token_rows(ops):
     out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(1, 100), (5, 50), (1, 300), (2, 7)], kernel="prefill_tc", min_q_len=2)
     assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
