@@ -41,7 +41,7 @@ def plan(M: int, N: int, K: int) -> dict:
         tiles = -(-N // 128)
     else:
         swapped = False
-        bn = 128
+        bn = 256 if N >= 256 else 128            # one thread issues an MMA every ~50 cycles: only 256 columns keep the tensor pipe busy
         tiles = -(-M // 128) * -(-N // bn)
     stage = 128 * 64 * 2 + bn * 64 * 2
     splits = 1
