@@ -249,9 +249,22 @@ def test_sampling_greedy_and_ties(ops):
     z = torch.zeros(3, device=DEV)
     ops.sample(lg, z, torch.zeros(3, dtype=torch.int64, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV), 0, out)
     assert out.tolist() == [999, 17, 0]
+    # a large vocabulary is cut into slices, one block each: ties across slices, winners in the first
+    # and the last slice, rows that are not 16-byte aligned (odd vocabulary)
+    for vocab in (32000, 32003, 4099):
+        lg = torch.zeros(5, vocab, device=DEV)
+        lg[0, vocab - 1] = 1.0
+        lg[1, [4001, vocab - 50, vocab - 2]] = 2.0             # all inside the smallest vocabulary here
+        lg[2] = -torch.arange(float(vocab))
+        lg[3, vocab // 2 + 1] = 0.5
+        lg[4] = torch.arange(float(vocab)) % 7                  # the first 6 is at index 6
+        out = torch.empty(5, dtype=torch.int32, device=DEV)
+        ops.sample(lg, torch.zeros(5, device=DEV), torch.zeros(5, dtype=torch.int64, device=DEV),
+                   torch.zeros(5, dtype=torch.int32, device=DEV), 0, out)
+        assert out.tolist() == [vocab - 1, 4001, 0, vocab // 2 + 1, 6], vocab
 
 
-@pytest.mark.parametrize("vocab", [384, 5000, 32000])
+@pytest.mark.parametrize("vocab", [384, 5000, 32000, 32003])
 def test_sampling_temperature_matches_plain(ops, vocab):
     torch.manual_seed(vocab)
     rows = 6
