@@ -305,145 +305,145 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             bool ok = true;
             for (int u = 0; u < nsub && ok; ++u) {                 // one query tile after the other
-            const int q0 = sb[u].q0, pos0 = sb[u].pos0, nq = sb[u].nq, k_lo = sb[u].k_lo, kbeg = sb[u].kbeg, ntiles = sb[u].ntiles;
-            const int g0 = u ? nA : 0;                             // key tiles counted through both query tiles
-            const int qpos = pos0 + r;
-            float m_run = -INFINITY, l_run = 0.f;
-            for (int t = 0; t < ntiles && ok; ++t) {
-                const int g = g0 + t;
-                ok = __all_sync(0xffffffffu, mbar_wait(&s_full, g & 1, abort_p));     // the warp goes on or gives up as one
-                if (!ok) break;
-                tc_fence_after();
-                const int key0 = kbeg + t * FA_BN;
-                // masks are needed only where the tile touches the diagonal, the window's edge or the range's start
-                const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
-                // The row of S comes out of TMEM in four chunks of 32 columns; the load of the next chunk is
-                // in flight while the current one is worked on.
-                auto for_each_chunk = [&](auto&& body) {
-                    uint32_t ca[32], cb[32];
-                    tmem_ld32_async(lane_addr + TMEM_S, ca);
-                    tmem_ld_wait(ca);
-                    tmem_ld32_async(lane_addr + TMEM_S + 32, cb);
-                    body(0, ca);
-                    tmem_ld_wait(cb);
-                    tmem_ld32_async(lane_addr + TMEM_S + 64, ca);
-                    body(1, cb);
-                    tmem_ld_wait(ca);
-                    tmem_ld32_async(lane_addr + TMEM_S + 96, cb);
-                    body(2, ca);
-                    tmem_ld_wait(cb);
-                    body(3, cb);
-                };
-                auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
-                // Reference point of the exponent.  Reading S once per tile is what matters here (TMEM
-                // loads are the slowest part of the step), so the running max is not recomputed up front:
-                // P is formed against the running max as it stands, the row's true max is found on the
-                // way, and only if some entry would exceed 2^8 is the tile redone against the new max
-                // (then O and l are rescaled).  The first tile has no running max and takes a max pass.
-                // The two loops below exist in a masked and an unmasked version, chosen once per tile: a
-                // test per element would double the instructions of the common, unmasked tiles.
-                auto row_max = [&](auto mask_tag) {
-                    constexpr bool MASK = decltype(mask_tag)::value;
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    for_each_chunk([&](int ch, const uint32_t* c) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float x = __uint_as_float(c[i]);
-                            if (MASK && masked(key0 + ch * 32 + i)) x = -INFINITY;
-                            mx4[i & 3] = fmaxf(mx4[i & 3], x);
-                        }
-                    });
-                    return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                };
-                if (t == 0) {
-                    const float mx = need_mask ? row_max(std::true_type{}) : row_max(std::false_type{});
-                    m_run = mx * p.scale_log2e;                    // the scale is positive: max and scaling commute
-                }
-                float alpha = 1.f, sum = 0.f;
-                auto p_pass = [&](auto mask_tag, float neg_m, float& xmax_out) {
-                    constexpr bool MASK = decltype(mask_tag)::value;
-                    // four independent sums and maxima: one warp per scheduler has nothing else to hide
-                    // the latency of a dependent chain behind
-                    float xm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, sm[4] = {0.f, 0.f, 0.f, 0.f};
-                    for_each_chunk([&](int ch, const uint32_t* c) {
-                        uint32_t packed[16];
-                        // P(t-1) must have been read by its product before it is overwritten (normally long done)
-                        if (ch == 0 && g > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_p))) ok = false;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
-                            float x1 = fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
-                            if (MASK) {
-                                if (masked(key0 + ch * 32 + i)) x0 = -INFINITY;
-                                if (masked(key0 + ch * 32 + i + 1)) x1 = -INFINITY;
+                const int q0 = sb[u].q0, pos0 = sb[u].pos0, nq = sb[u].nq, k_lo = sb[u].k_lo, kbeg = sb[u].kbeg, ntiles = sb[u].ntiles;
+                const int g0 = u ? nA : 0;                             // key tiles counted through both query tiles
+                const int qpos = pos0 + r;
+                float m_run = -INFINITY, l_run = 0.f;
+                for (int t = 0; t < ntiles && ok; ++t) {
+                    const int g = g0 + t;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&s_full, g & 1, abort_p));     // the warp goes on or gives up as one
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int key0 = kbeg + t * FA_BN;
+                    // masks are needed only where the tile touches the diagonal, the window's edge or the range's start
+                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
+                    // The row of S comes out of TMEM in four chunks of 32 columns; the load of the next chunk is
+                    // in flight while the current one is worked on.
+                    auto for_each_chunk = [&](auto&& body) {
+                        uint32_t ca[32], cb[32];
+                        tmem_ld32_async(lane_addr + TMEM_S, ca);
+                        tmem_ld_wait(ca);
+                        tmem_ld32_async(lane_addr + TMEM_S + 32, cb);
+                        body(0, ca);
+                        tmem_ld_wait(cb);
+                        tmem_ld32_async(lane_addr + TMEM_S + 64, ca);
+                        body(1, cb);
+                        tmem_ld_wait(ca);
+                        tmem_ld32_async(lane_addr + TMEM_S + 96, cb);
+                        body(2, ca);
+                        tmem_ld_wait(cb);
+                        body(3, cb);
+                    };
+                    auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
+                    // Reference point of the exponent.  Reading S once per tile is what matters here (TMEM
+                    // loads are the slowest part of the step), so the running max is not recomputed up front:
+                    // P is formed against the running max as it stands, the row's true max is found on the
+                    // way, and only if some entry would exceed 2^8 is the tile redone against the new max
+                    // (then O and l are rescaled).  The first tile has no running max and takes a max pass.
+                    // The two loops below exist in a masked and an unmasked version, chosen once per tile: a
+                    // test per element would double the instructions of the common, unmasked tiles.
+                    auto row_max = [&](auto mask_tag) {
+                        constexpr bool MASK = decltype(mask_tag)::value;
+                        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                        for_each_chunk([&](int ch, const uint32_t* c) {
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                float x = __uint_as_float(c[i]);
+                                if (MASK && masked(key0 + ch * 32 + i)) x = -INFINITY;
+                                mx4[i & 3] = fmaxf(mx4[i & 3], x);
                             }
-                            xm[(i >> 1) & 3] = fmaxf(xm[(i >> 1) & 3], fmaxf(x0, x1));
-                            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                            sm[(i >> 1) & 3] += p0 + p1;
-                            packed[i >> 1] = pack2_bf16(p0, p1);
-                        }
-                        tmem_st16(lane_addr + TMEM_P + ch * 16, packed);
-                    });
-                    xmax_out = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
-                    return (sm[0] + sm[1]) + (sm[2] + sm[3]);
-                };
-                for (int attempt = 0; attempt < 2; ++attempt) {
-                    const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-                    float xmax;
-                    sum = need_mask ? p_pass(std::true_type{}, neg_m, xmax) : p_pass(std::false_type{}, neg_m, xmax);
-                    // the running max moves only when it has to (warp-wide decision: the loads are warp-wide)
-                    const bool moved = xmax > 8.0f || (m_run == -INFINITY && xmax > -INFINITY);
-                    if (attempt == 1 || !__any_sync(0xffffffffu, moved)) break;
-                    if (moved) {
-                        const float m_new = (m_run == -INFINITY ? 0.f : m_run) + xmax;
-                        alpha = m_run == -INFINITY ? 1.f : ex2_approx(m_run - m_new);
-                        m_run = m_new;
+                        });
+                        return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                    };
+                    if (t == 0) {
+                        const float mx = need_mask ? row_max(std::true_type{}) : row_max(std::false_type{});
+                        m_run = mx * p.scale_log2e;                    // the scale is positive: max and scaling commute
                     }
+                    float alpha = 1.f, sum = 0.f;
+                    auto p_pass = [&](auto mask_tag, float neg_m, float& xmax_out) {
+                        constexpr bool MASK = decltype(mask_tag)::value;
+                        // four independent sums and maxima: one warp per scheduler has nothing else to hide
+                        // the latency of a dependent chain behind
+                        float xm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, sm[4] = {0.f, 0.f, 0.f, 0.f};
+                        for_each_chunk([&](int ch, const uint32_t* c) {
+                            uint32_t packed[16];
+                            // P(t-1) must have been read by its product before it is overwritten (normally long done)
+                            if (ch == 0 && g > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_p))) ok = false;
+    #pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
+                                float x1 = fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
+                                if (MASK) {
+                                    if (masked(key0 + ch * 32 + i)) x0 = -INFINITY;
+                                    if (masked(key0 + ch * 32 + i + 1)) x1 = -INFINITY;
+                                }
+                                xm[(i >> 1) & 3] = fmaxf(xm[(i >> 1) & 3], fmaxf(x0, x1));
+                                const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                                sm[(i >> 1) & 3] += p0 + p1;
+                                packed[i >> 1] = pack2_bf16(p0, p1);
+                            }
+                            tmem_st16(lane_addr + TMEM_P + ch * 16, packed);
+                        });
+                        xmax_out = fmaxf(fmaxf(xm[0], xm[1]), fmaxf(xm[2], xm[3]));
+                        return (sm[0] + sm[1]) + (sm[2] + sm[3]);
+                    };
+                    for (int attempt = 0; attempt < 2; ++attempt) {
+                        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+                        float xmax;
+                        sum = need_mask ? p_pass(std::true_type{}, neg_m, xmax) : p_pass(std::false_type{}, neg_m, xmax);
+                        // the running max moves only when it has to (warp-wide decision: the loads are warp-wide)
+                        const bool moved = xmax > 8.0f || (m_run == -INFINITY && xmax > -INFINITY);
+                        if (attempt == 1 || !__any_sync(0xffffffffu, moved)) break;
+                        if (moved) {
+                            const float m_new = (m_run == -INFINITY ? 0.f : m_run) + xmax;
+                            alpha = m_run == -INFINITY ? 1.f : ex2_approx(m_run - m_new);
+                            m_run = m_new;
+                        }
+                    }
+                    l_run = l_run * alpha + sum;
+                    // rescale this row of O (the PV product of the tile before has finished: s_full came after it)
+                    // (tcgen05.ld / st are warp-wide instructions: the whole warp rescales if any of its rows moved)
+                    if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+    #pragma unroll 1
+                        for (int c = 0; c < D; c += 16) {
+                            float v[16];
+                            tmem_ld16(lane_addr + TMEM_O + c, v);
+                            uint32_t w[16];
+    #pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i] * alpha);
+                            tmem_st8(lane_addr + TMEM_O + c, w);
+                            tmem_st8(lane_addr + TMEM_O + c + 8, w + 8);
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_full);              // one arrival per warp
                 }
-                l_run = l_run * alpha + sum;
-                // rescale this row of O (the PV product of the tile before has finished: s_full came after it)
-                // (tcgen05.ld / st are warp-wide instructions: the whole warp rescales if any of its rows moved)
-                if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
+                // epilogue: O / l -> bfloat16 -> out[token, head, :]
+                if (ok) ok = mbar_wait(&o_full, u & 1, abort_p);
+                tc_fence_after();
+                __syncwarp();
+                if (__all_sync(0xffffffffu, ok)) {                      // warp-wide loads: every lane reads, rows inside the tile store
+                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                    bf16* op = p.out + ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
+    #pragma unroll 1
                     for (int c = 0; c < D; c += 16) {
                         float v[16];
                         tmem_ld16(lane_addr + TMEM_O + c, v);
-                        uint32_t w[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i] * alpha);
-                        tmem_st8(lane_addr + TMEM_O + c, w);
-                        tmem_st8(lane_addr + TMEM_O + c + 8, w + 8);
+                        if (r >= nq) continue;
+                        uint4 w0, w1;
+                        w0.x = pack2_bf16(v[0] * inv, v[1] * inv); w0.y = pack2_bf16(v[2] * inv, v[3] * inv);
+                        w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
+                        w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
+                        w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
+                        *reinterpret_cast<uint4*>(op + c) = w0;
+                        *reinterpret_cast<uint4*>(op + c + 8) = w1;
                     }
+                    // the next query tile's first PV product overwrites O: it follows p_full, which this warp
+                    // gives only after these loads
+                    tc_fence_before();
                 }
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&p_full);              // one arrival per warp
-            }
-            // epilogue: O / l -> bfloat16 -> out[token, head, :]
-            if (ok) ok = mbar_wait(&o_full, u & 1, abort_p);
-            tc_fence_after();
-            __syncwarp();
-            if (__all_sync(0xffffffffu, ok)) {                      // warp-wide loads: every lane reads, rows inside the tile store
-                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-                bf16* op = p.out + ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
-#pragma unroll 1
-                for (int c = 0; c < D; c += 16) {
-                    float v[16];
-                    tmem_ld16(lane_addr + TMEM_O + c, v);
-                    if (r >= nq) continue;
-                    uint4 w0, w1;
-                    w0.x = pack2_bf16(v[0] * inv, v[1] * inv); w0.y = pack2_bf16(v[2] * inv, v[3] * inv);
-                    w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
-                    w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
-                    w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
-                    *reinterpret_cast<uint4*>(op + c) = w0;
-                    *reinterpret_cast<uint4*>(op + c + 8) = w1;
-                }
-                // the next query tile's first PV product overwrites O: it follows p_full, which this warp
-                // gives only after these loads
-                tc_fence_before();
-            }
             }
         }
     }
