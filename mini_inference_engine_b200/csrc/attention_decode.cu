@@ -31,14 +31,19 @@
 // Scratch (optional; without it splits must be 1, 2, 4 or 8): part_o float32 [rows * heads * splits * head_dim], part_lse
 // float32 [rows * heads * splits], counters int32 [rows * kv_heads * chunks], the counters zero
 // before the first launch (the kernel leaves them zero).  `stages`: key/value tiles in flight per
-// block (2, 3 or 4; 0 = 4).
+// block (2, 3 or 4; 0 = 4).  `num_pages`: pages in each cache (rows of the TMA tensor map); 0 keeps the
+// cp.async copies.
 extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_tables, int table_stride, const int* row_q_start,
                                     const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                     int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                     int window, int splits, float* part_o, float* part_lse, int* counters,
-                                    int stages, cudaStream_t stream) {
+                                    int stages, int64_t num_pages, cudaStream_t stream) {
     return decode_attention_launch(q, q_stride, k_cache, v_cache, block_tables, table_stride, row_q_start, row_q_len,
                                    row_ctx_len, num_rows, out, num_heads, num_kv_heads, head_dim, page_size, scale,
-                                   window, splits, part_o, part_lse, counters, stream, stages);
+                                   window, splits, part_o, part_lse, counters, stream, stages, num_pages);
 }
+
+// Non-zero when a block of any launch so far gave up a bounded wait (TMA copies that did not arrive).
+extern "C" int mie_decode_attention_error(void) { return g_error_host ? *g_error_host : 0; }
+extern "C" void mie_decode_attention_clear_error(void) { if (g_error_host) *g_error_host = 0; }

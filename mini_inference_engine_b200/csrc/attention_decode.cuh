@@ -3,6 +3,7 @@
 // caller's; attention_decode_static.cu: a fixed array inside the library).
 #pragma once
 #include "mma_common.cuh"
+#include "tcgen05_common.cuh"      // mbarrier, TMA copies, bounded waits, the tensor-map encoder
 
 #define DEC_WARPS 4
 #define DEC_TILE 64
@@ -20,17 +21,40 @@ struct DecodeParams {
     int stages;              // tiles in flight per block (2, 3 or 4)
     int cluster;             // 1: the splits of a (row, kv head, chunk) are a thread-block cluster and merge through shared memory
     float scale_log2e;
+    int* error;              // host-visible error word (TMA path: a bounded wait that ran out)
 };
 
+// Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
+// 128-byte swizzle: rows of 64 elements (128 bytes), 64 rows (8 KB) per 64-column part of the head,
+// the piece index XORed with the row's place in its group of eight.
+__device__ __forceinline__ uint32_t swz_tile_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * 8192 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
 
-template <int D, int NSTAGE>
+
+// TMA = true (head sizes 64 and 128, pages of at least 8 positions): keys and values arrive a page per
+// copy (cp.async.bulk.tensor through the block table, 128-byte swizzle, an mbarrier per stage) instead of
+// 16 bytes per thread per cp.async: a thousand address computations a tile less, and the copies of a
+// tile are in flight from one instruction each.  Measured on B200 (32 q / 4 kv heads of 64): with more
+// blocks than fit beside one another it is the faster way (128 requests x 512 keys 20.6 -> 14.9 us,
+// 256 x 512 34.4 -> 29.2 us, 256 x 2048 101 -> 96 us = 5.6 TB/s); where a block walks a long part
+// alone it is not (64 x 2048: 40.0 -> 42.9 us), so the caller chooses (ops.decode_uses_tma).
+template <int D, int NSTAGE, bool TMA>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-decode_attention_kernel(const DecodeParams p) {
+decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const DecodeParams p) {
     constexpr int DP = D + 8;                    // padded row: ldmatrix rows fall into different banks
     constexpr int KSTEPS = D / 16, NBLK = D / 8;
+    constexpr int PARTS = (D + 63) / 64;                           // 64-column parts of a head (TMA layout)
+    constexpr uint32_t KV_TILE_BYTES = PARTS * 8192;               // one tile of keys (or values) as TMA lays it out
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                 // [NSTAGE][DEC_TILE][DP]
     bf16* v_s = k_s + NSTAGE * DEC_TILE * DP;                      // [NSTAGE][DEC_TILE][DP]
+    // TMA layout: swizzled tiles on 1024-byte lines: stage s = keys | values, 2 * KV_TILE_BYTES each
+    const uint32_t tma_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* tma_tiles = smem_raw + (tma_base - smem_u32(smem_raw));
+    __shared__ __align__(8) uint64_t full_bar[4];
+    __shared__ int abort_flag;
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ __align__(16) float c_lse[16];
     __shared__ int s_pages[DEC_PAGE_SLOTS];                        // this block's page ids, fetched once
@@ -69,6 +93,21 @@ decode_attention_kernel(const DecodeParams p) {
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+    volatile int* abort_p = &abort_flag;
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            abort_flag = 0;
+            for (int s = 0; s < NSTAGE; ++s) mbar_init(&full_bar[s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        // A copy brings whole pages; rows of a tile that no page of this part covers keep what the shared
+        // memory held.  Their scores are masked, but 0 * NaN is NaN: they must be finite.
+        if ((kend - kbeg) & (DEC_TILE - 1))
+            for (uint32_t i = threadIdx.x * 16; i < (uint32_t)NSTAGE * 2 * KV_TILE_BYTES; i += DEC_WARPS * 32 * 16)
+                *reinterpret_cast<uint4*>(tma_tiles + i) = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // barriers and zeros before the TMA unit touches them
+    }
+
     // The page ids of this block's part go to shared memory first: a lookup in global memory inside the
     // tile loop would put a memory round trip in front of every tile's copies.
     const int* table = p.block_tables + (int64_t)row * p.table_stride;
@@ -77,8 +116,29 @@ decode_attention_kernel(const DecodeParams p) {
     for (int i = threadIdx.x; i < min(n_pages, DEC_PAGE_SLOTS); i += DEC_WARPS * 32) s_pages[i] = table[first_page + i];
     __syncthreads();
     constexpr int CHUNKS_PER_ROW = D / 8;                          // 16-byte pieces per key
+    const int rows_per_copy = min(p.page_size, DEC_TILE);          // TMA: one copy = one page (or a 64-row piece of it)
     auto load_tile = [&](int t, int stage) {
         const int k0 = kbeg + t * DEC_TILE;
+        if (TMA) {
+            if (warp == 0) {                                       // lane c copies page c of the tile, keys and values
+                const int copies = (min(DEC_TILE, kend - k0) + rows_per_copy - 1) / rows_per_copy;
+                if (lane == 0) mbar_expect_tx(&full_bar[stage], (uint32_t)copies * rows_per_copy * 128u * PARTS * 2u);
+                __syncwarp();
+                if (lane < copies) {
+                    const int key = k0 + lane * rows_per_copy;
+                    const int pi = (key >> p.page_shift) - first_page;
+                    const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                    const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
+                    unsigned char* kd = tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES + (size_t)lane * rows_per_copy * 128;
+#pragma unroll
+                    for (int part = 0; part < PARTS; ++part) {
+                        tma_load_2d(kd + part * 8192, &map_k, &full_bar[stage], part * 64, src_row);
+                        tma_load_2d(kd + KV_TILE_BYTES + part * 8192, &map_v, &full_bar[stage], part * 64, src_row);
+                    }
+                }
+            }
+            return;
+        }
         bf16* kd = k_s + stage * DEC_TILE * DP;
         bf16* vd = v_s + stage * DEC_TILE * DP;
         for (int idx = threadIdx.x; idx < DEC_TILE * CHUNKS_PER_ROW; idx += DEC_WARPS * 32) {
@@ -121,9 +181,14 @@ decode_attention_kernel(const DecodeParams p) {
     for (int t = 0; t < ntiles; ++t) {
         const int stage = t % NSTAGE;
         if (t + NSTAGE - 1 < ntiles) load_tile(t + NSTAGE - 1, (t + NSTAGE - 1) % NSTAGE);
-        cp_async_commit();
-        cp_async_wait<NSTAGE - 1>();                               // tile t has landed; NSTAGE - 1 younger ones may be in flight
-        __syncthreads();
+        if (TMA) {
+            // bounded; every thread sees the bytes itself, and the block goes on or gives up as one
+            if (!__syncthreads_and(mbar_wait(&full_bar[stage], (t / NSTAGE) & 1, abort_p))) break;
+        } else {
+            cp_async_commit();
+            cp_async_wait<NSTAGE - 1>();                           // tile t has landed; NSTAGE - 1 younger ones may be in flight
+            __syncthreads();
+        }
         if (t < NSTAGE - 1 && newest >= kbeg + t * DEC_TILE && newest < min(kend, kbeg + (t + 1) * DEC_TILE)) {
             // this tile was copied before the wait: its newest row may be stale, fetch it again (L2, not L1)
             if (threadIdx.x < 2 * CHUNKS_PER_ROW) {
@@ -133,12 +198,14 @@ decode_attention_kernel(const DecodeParams p) {
                 const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (newest & (p.page_size - 1))) * D + c;
                 const uint4 v = __ldcg(reinterpret_cast<const uint4*>((which ? p.v_cache : p.k_cache) + src));
-                *reinterpret_cast<uint4*>((which ? v_s : k_s) + stage * DEC_TILE * DP + r * DP + c) = v;
+                if (TMA) *reinterpret_cast<uint4*>(tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES + which * KV_TILE_BYTES + swz_tile_off(r, c / 8)) = v;
+                else *reinterpret_cast<uint4*>((which ? v_s : k_s) + stage * DEC_TILE * DP + r * DP + c) = v;
             }
             __syncthreads();
         }
         const bf16* kt = k_s + stage * DEC_TILE * DP + warp * 16 * DP;
         const bf16* vt = v_s + stage * DEC_TILE * DP + warp * 16 * DP;
+        const unsigned char* kt_tma = tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES;   // keys of the stage; values KV_TILE_BYTES behind
         const int key0 = kbeg + t * DEC_TILE + warp * 16;
         if (key0 < kend) {                                          // warp-uniform
             float s[2][4];
@@ -147,7 +214,9 @@ decode_attention_kernel(const DecodeParams p) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, kt + ((lane & 7) + (lane >> 4) * 8) * DP + ks * 16 + ((lane >> 3) & 1) * 8);
+                if (TMA) ldmatrix_x4(b0, b1, b2, b3, reinterpret_cast<const bf16*>(
+                             kt_tma + swz_tile_off(warp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1))));
+                else ldmatrix_x4(b0, b1, b2, b3, kt + ((lane & 7) + (lane >> 4) * 8) * DP + ks * 16 + ((lane >> 3) & 1) * 8);
                 mma_bf16(s[0], qf[ks], b0, b1);
                 mma_bf16(s[1], qf[ks], b2, b3);
             }
@@ -207,7 +276,9 @@ decode_attention_kernel(const DecodeParams p) {
 #pragma unroll
             for (int n2 = 0; n2 < NBLK / 2; ++n2) {
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4_trans(b0, b1, b2, b3, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + n2 * 16 + (lane >> 4) * 8);
+                if (TMA) ldmatrix_x4_trans(b0, b1, b2, b3, reinterpret_cast<const bf16*>(
+                             kt_tma + KV_TILE_BYTES + swz_tile_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n2 * 2 + (lane >> 4))));
+                else ldmatrix_x4_trans(b0, b1, b2, b3, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + n2 * 16 + (lane >> 4) * 8);
                 mma_bf16(o[2 * n2], pf, b0, b1);
                 mma_bf16(o[2 * n2 + 1], pf, b2, b3);
             }
@@ -216,6 +287,11 @@ decode_attention_kernel(const DecodeParams p) {
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (TMA && abort_flag) {                                       // a wait ran out: say so, let copies in flight land
+        if (threadIdx.x == 0) atomicExch(p.error, 1);
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        __syncthreads();
+    }
 
     // merge the four warps: each leaves (m, l, O) in shared memory (the tile buffers are free now)
     float* o_s = reinterpret_cast<float*>(smem_raw);               // [DEC_WARPS][16][D]
@@ -331,26 +407,50 @@ decode_attention_kernel(const DecodeParams p) {
     }
 }
 
-template <int D, int NSTAGE>
-static int launch_decode_stages(const DecodeParams& p, int num_rows, cudaStream_t stream) {
+// The caches as a 2-D tensor map for the TMA path: rows = (page, kv head, slot), columns = head_dim,
+// boxes of {64 columns, box_rows} with the 128-byte swizzle.
+struct DecodeMaps { CUtensorMap k, v; bool use; };
+
+static int make_decode_map(CUtensorMap* map, const void* ptr, uint64_t rows, int head_dim, int box_rows) {
+    cuuint64_t gdim[2] = {(cuuint64_t)head_dim, rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)head_dim * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int D, int NSTAGE, bool TMA>
+static int launch_decode_stages(const DecodeParams& p, const DecodeMaps& maps, int num_rows, cudaStream_t stream) {
     // at least the four-warp merge buffer (4 x 16 x D float32) plus the block's output (16 x D) must fit
-    size_t smem = (size_t)NSTAGE * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
+    size_t smem = TMA ? (size_t)NSTAGE * 2 * ((D + 63) / 64) * 8192 + 1024 : (size_t)NSTAGE * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
     const size_t merge = (size_t)(DEC_WARPS + 1) * 16 * D * sizeof(float);
     if (smem < merge) smem = merge;
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, NSTAGE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
     const dim3 cluster(p.cluster ? p.splits : 1, 1, 1);
-    return launch_kernel_cluster(decode_attention_kernel<D, NSTAGE>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster, p);
+    return launch_kernel_cluster(decode_attention_kernel<D, NSTAGE, TMA>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster,
+                                 maps.k, maps.v, p);
 }
 
 // Tiles in flight per block.  Few tiles per block (short contexts, many splits): two stages, so that
 // more blocks share an SM and hide one another's latencies.  Many tiles per block: a deeper ring.
+template <int D, bool TMA>
+static int launch_decode_tma(const DecodeParams& p, const DecodeMaps& maps, int num_rows, cudaStream_t stream) {
+    if (p.stages <= 2) return launch_decode_stages<D, 2, TMA>(p, maps, num_rows, stream);
+    if (p.stages == 3 || D > 64) return launch_decode_stages<D, 3, TMA>(p, maps, num_rows, stream);
+    return launch_decode_stages<D, 4, TMA>(p, maps, num_rows, stream);
+}
+
 template <int D>
-static int launch_decode(const DecodeParams& p, int num_rows, cudaStream_t stream) {
-    if (p.stages <= 2) return launch_decode_stages<D, 2>(p, num_rows, stream);
-    if (p.stages == 3 || D > 64) return launch_decode_stages<D, 3>(p, num_rows, stream);
-    return launch_decode_stages<D, 4>(p, num_rows, stream);
+static int launch_decode(const DecodeParams& p, const DecodeMaps& maps, int num_rows, cudaStream_t stream) {
+    if constexpr (D == 64 || D == 128) {
+        if (maps.use) return launch_decode_tma<D, true>(p, maps, num_rows, stream);
+    }
+    return launch_decode_tma<D, false>(p, maps, num_rows, stream);
 }
 
 
@@ -362,7 +462,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                    int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
-                                   cudaStream_t stream, int stages = 0) {
+                                   cudaStream_t stream, int stages = 0, int64_t num_pages = 0) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -385,15 +485,30 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;
+    // TMA copies (see the kernel): head sizes 64 and 128, pages of 8 positions or more, a caller that says
+    // how many pages the caches hold (num_pages; the entry point that must not allocate passes 0)
+    DecodeMaps maps;
+    maps.use = num_pages > 0 && (head_dim == 64 || head_dim == 128) && page_size >= 8 &&
+               !((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15);
+    p.error = nullptr;
+    if (maps.use) {
+        int rc = tc_setup();
+        if (rc) return rc;
+        const int box_rows = page_size < DEC_TILE ? page_size : DEC_TILE;
+        const uint64_t rows = (uint64_t)num_pages * num_kv_heads * page_size;
+        if ((rc = make_decode_map(&maps.k, k_cache, rows, head_dim, box_rows))) return rc;
+        if ((rc = make_decode_map(&maps.v, v_cache, rows, head_dim, box_rows))) return rc;
+        p.error = g_error_dev;
+    }
     switch (head_dim) {
-        case 16: return launch_decode<16>(p, num_rows, stream);
-        case 32: return launch_decode<32>(p, num_rows, stream);
-        case 48: return launch_decode<48>(p, num_rows, stream);
-        case 64: return launch_decode<64>(p, num_rows, stream);
-        case 80: return launch_decode<80>(p, num_rows, stream);
-        case 96: return launch_decode<96>(p, num_rows, stream);
-        case 112: return launch_decode<112>(p, num_rows, stream);
-        case 128: return launch_decode<128>(p, num_rows, stream);
+        case 16: return launch_decode<16>(p, maps, num_rows, stream);
+        case 32: return launch_decode<32>(p, maps, num_rows, stream);
+        case 48: return launch_decode<48>(p, maps, num_rows, stream);
+        case 64: return launch_decode<64>(p, maps, num_rows, stream);
+        case 80: return launch_decode<80>(p, maps, num_rows, stream);
+        case 96: return launch_decode<96>(p, maps, num_rows, stream);
+        case 112: return launch_decode<112>(p, maps, num_rows, stream);
+        case 128: return launch_decode<128>(p, maps, num_rows, stream);
     }
     return MIE_ERR_BAD_ARG;
 }

@@ -117,7 +117,7 @@ def cmd_decode_attention(args):
         out = torch.empty(B, H, D, device=DEV, dtype=torch.bfloat16)
         fn = lambda i: ops.decode_attention(qkv, stride, k, v, bt, rows, ones, ctx, out, H, Hkv, D, args.page,   # noqa: E731
                                             1 / math.sqrt(D), max_ctx=args.max_context or args.context, splits=args.splits,
-                                            stages=args.stages)
+                                            stages=args.stages, tma={'auto': None, 'on': True, 'off': False}[args.tma])
         if args.once:
             run_plain(fn, 3)
             continue
@@ -204,6 +204,7 @@ def main(argv=None):
     d.add_argument("--splits", type=int, default=None)
     d.add_argument("--stages", type=int, default=None)
     d.add_argument("--page", type=int, default=16)
+    d.add_argument("--tma", choices=["auto", "on", "off"], default="auto", help="key/value copies by TMA (default: the wrapper's choice)")
     d.set_defaults(fn=cmd_decode_attention)
     p = sub.add_parser("prefill-attention")
     p.add_argument("--tokens", type=int, nargs="+", default=[512, 2048, 8192])

@@ -220,7 +220,7 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
 
 def check_tc_errors() -> None:
     """Raises if a block of a tensor-core kernel gave up a bounded wait (call after a synchronise)."""
-    for name, fn in (("attention_prefill_tc", "mie_prefill_attention_tc"),):
+    for name, fn in (("attention_prefill_tc", "mie_prefill_attention_tc"), ("attention_decode", "mie_decode_attention")):
         lib = build._libs.get(name)
         if lib is not None and getattr(lib, fn + "_error")():
             getattr(lib, fn + "_clear_error")()
@@ -255,7 +255,7 @@ def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
     return splits
 
 
-def decode_stages(blocks: int, max_ctx: int, splits: int) -> int:
+def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False) -> int:
     """Tiles of 64 keys in flight per block.  Shared memory that attention does not take stays free
     for the prologue of the kernel after it (the output projection fills its ring with weights while
     attention still runs): measured on B200 in the whole decode step at batch 8, 512 keys, three
@@ -266,14 +266,26 @@ def decode_stages(blocks: int, max_ctx: int, splits: int) -> int:
     46 us)."""
     tiles = -(-(-(-max(1, max_ctx) // splits)) // 64)
     if blocks > 3 * NUM_SMS:
-        return 2
+        return 3 if tma else 2            # TMA tiles are unpadded: three stages still put four blocks on an SM (256 x 512: 29.2 us, two stages 30.7)
     return 3 if tiles <= 4 else 4
+
+
+def decode_uses_tma(blocks: int) -> bool:
+    """Whether the decode kernel fetches keys and values a page per TMA copy instead of 16 bytes per
+    cp.async.  Measured on B200 (32 q / 4 kv heads of 64): it pays where there are more blocks than
+    fit beside one another (128 requests x 512 keys: 14.9 us against 20.6 us; 256 x 512: 29.2 against
+    34.4 us) and costs a little where each block walks a long part alone (64 x 2048: 42.9 against
+    40.0 us; 8 x 512: 7.5 against 7.1 us) -- the copies were never the bound there, the softmax
+    bookkeeping per 16 keys is.  Cache slots beyond a request's context are copied along with their
+    page and must hold finite values (the cache storage starts as zeros)."""
+    return blocks > 3 * NUM_SMS
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
-                     splits: int | None = None, merge: str = "cluster", stages: int | None = None) -> torch.Tensor:
+                     splits: int | None = None, merge: str = "cluster", stages: int | None = None,
+                     tma: bool | None = None) -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
     blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
     "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
@@ -289,8 +301,11 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
     chunks = -(-(num_heads // num_kv_heads) // 16)
     if splits is None:
         splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
+    if tma is None:
+        tma = decode_uses_tma(rows * num_kv_heads * chunks * splits)
+    tma = bool(tma) and head_dim in (64, 128) and page_size >= 8
     if stages is None:
-        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits)
+        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma)
     part_o = part_lse = counters = None
     if merge == "cluster" and splits not in (1, 2, 4, 8):
         merge = "scratch"
@@ -303,7 +318,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                     _ptr(row_ctx_len), rows, _ptr(out), num_heads, num_kv_heads, head_dim,
                                     page_size, ctypes.c_float(scale), int(window or 0), int(splits),
-                                    _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0), _stream()),
+                                    _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0),
+                                    ctypes.c_int64(k_cache.shape[0] if tma else 0), _stream()),
            "decode_attention")
     return out
 

@@ -328,10 +328,22 @@ def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=
     q_len = torch.tensor(q_lens, dtype=torch.int32)
     ctx_len = torch.tensor(ctxs, dtype=torch.int32)
     q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+    args = (q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV),
+            q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV))
     out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
-    ops.decode_attention(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV),
-                         q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV), out, H, Hkv, D, page, scale, window,
-                         max_ctx=max_ctx or max(ctxs), splits=splits, merge=merge)
+    ops.decode_attention(*args, out, H, Hkv, D, page, scale, window, max_ctx=max_ctx or max(ctxs), splits=splits, merge=merge,
+                         tma=False)
+    if D in (64, 128) and page >= 8:
+        # the same case with keys and values fetched a page per TMA copy (the wrapper picks that way only
+        # for many blocks): both ways must give the answer, skipped rows untouched in both
+        out_tma = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
+        ops.decode_attention(*args, out_tma, H, Hkv, D, page, scale, window, max_ctx=max_ctx or max(ctxs), splits=splits,
+                             merge=merge, tma=True)
+        torch.cuda.synchronize()
+        ops.check_tc_errors()
+        live = torch.repeat_interleave(q_len == 1, q_len).to(DEV)
+        close(out_tma[live], torch.cat(want, 0)[live.cpu()], dt, f"decode attention by TMA, H{H} Hkv{Hkv} D{D} page{page} ctx {ctxs[:6]}")
+        assert (out_tma[~live] == 77.0).all()
     return out, torch.cat(want, 0), q_start.tolist()
 
 
@@ -363,7 +375,8 @@ def test_decode_attention_head_shapes(ops, H, Hkv, D, page):
         close(out, want, torch.bfloat16, f"decode H{H} Hkv{Hkv} D{D} page{page} splits {splits}")
 
 
-def test_decode_attention_reads_the_key_written_just_before_it(ops):
+@pytest.mark.parametrize("tma", [False, True])
+def test_decode_attention_reads_the_key_written_just_before_it(ops, tma):
     """The decode kernel starts copying cached keys before the kernel in front of it has finished
     (programmatic dependent launch); the newest token's key and value, which that kernel writes, must
     still be the ones it uses.  Contexts grow token by token, write and attention back to back with no
@@ -396,7 +409,7 @@ def test_decode_attention_reads_the_key_written_just_before_it(ops):
         ops.rope_cache_write(qkv, pos, slots, cos, sin, k_cache, v_cache, H, Hkv, D, 0, page)
         out = torch.empty(rows, H * D, dtype=torch.bfloat16, device=DEV)
         ops.decode_attention(qkv, qkv.shape[1], k_cache, v_cache, tables, q_start, q_len, ctx_len, out, H, Hkv, D, page,
-                             1.0 / math.sqrt(D), max_ctx=start + steps)
+                             1.0 / math.sqrt(D), max_ctx=start + steps, tma=tma)
         outs.append(out)
     torch.cuda.synchronize()
     for i, (out, want) in enumerate(zip(outs, wants)):
