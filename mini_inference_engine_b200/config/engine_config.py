@@ -2,7 +2,8 @@
 inference_engine/config.py:45-56; the two Triton switches have no counterpart here
 (every GPU op is this package's own CUDA), and ``num_blocks`` and ``seed`` are added:
 tests need tiny page pools (the reference can only shrink its pool through the memory
-fraction, tests/test_correctness.py:46), and seeded sampling needs a seed."""
+fraction, tests/test_correctness.py:46), and seeded sampling needs a seed; ``overlap_steps`` and
+``graph_prompt_portions`` switch two things that the reference does not have."""
 from __future__ import annotations
 
 from dataclasses import dataclass, fields
@@ -21,6 +22,7 @@ class EngineConfig:
     num_blocks: int | None = None           # explicit pool size in pages (page 0 included); None = from memory
     seed: int = 0                           # sampling seed
     overlap_steps: bool = True              # launch step N+1 before reading step N's tokens (they are fed back on the device)
+    graph_prompt_portions: int = 4          # graphs kept for steps that are one prompt portion of a length seen before (0 = none)
 
     def __post_init__(self):
         if self.block_size < 16 or self.block_size & (self.block_size - 1) or self.block_size > 128:

@@ -119,6 +119,10 @@ class LLMEngine:
         self.graph_sizes: list = []
         self.num_steps = 0
         self.num_graph_steps = 0
+        self.num_portion_graph_steps = 0
+        self._portion_graphs: dict = {}          # (tokens, wanted logits) -> captured step of one prompt portion
+        self._portion_seen: dict = {}
+        self._graph_pool = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         if self.cfg.use_cuda_graphs:
@@ -171,10 +175,57 @@ class LLMEngine:
             pool = g.pool()
             self.graphs[bs] = _DecodeGraph(g, layout, static, tokens, ops.launches - before)
         torch.cuda.synchronize()
+        self._graph_pool = pool
         self.graph_sizes = sizes
         if self.verbose:
             print(f"[mini_inference_engine_b200] captured {len(sizes)} decode graphs (batch <= {sizes[-1]}) "
                   f"in {time.perf_counter() - t0:.1f} s")
+
+    # ------------------------------------------------------------------ CUDA graphs of prompt portions
+    PORTION_GRAPH_MIN_TOKENS = 128
+
+    @torch.inference_mode()
+    def _portion_graph(self, rows, extras, wanted: int):
+        """The captured step for a batch that is one portion of one prompt, if a step of the same
+        shape (tokens, wanted logits) has run before; else None, and the shape is remembered.
+        Long prompts are cut into portions of the token budget, so their steps repeat in shape:
+        launching some 160 kernels one by one costs the host about 3 ms a step, more than a short
+        portion takes on the device.  What differs between replays -- tokens, positions, block table,
+        sampling inputs -- lives in the graph's static input buffer; the context bound that kernels
+        plan by is the model's longest.  At most ``graph_prompt_portions`` graphs are kept (the least
+        recently used one goes).  The reference launches such steps eagerly."""
+        n = len(rows[0].tokens)
+        key = (n, wanted)
+        g = self._portion_graphs.get(key)
+        if g is not None:
+            self._portion_graphs[key] = self._portion_graphs.pop(key)        # most recently used last
+            return g
+        if not self._portion_seen.get(key):
+            if len(self._portion_seen) > 64:
+                self._portion_seen.clear()
+            self._portion_seen[key] = 1
+            return None
+        b = self.runner.builder
+        buf, layout = b.pack(rows, table_width=self.max_blocks_per_seq, extras=extras)
+        layout["max_ctx_len"] = self.cfg.max_model_len
+        static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
+        ctx = b.to_device(buf, layout, into=static)
+        ctx.token_feedback = self._sampled
+        tokens = self._sampled[:wanted]
+        # no warm-up run: a step of this shape has run before (kernels built, buffers sized), and running
+        # this one twice would write the request's cache twice -- harmless, but not free
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            self._forward_and_sample(ctx, tokens)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        g = _DecodeGraph(graph, layout, static, tokens, ops.launches - before)
+        while len(self._portion_graphs) >= max(1, self.cfg.graph_prompt_portions):
+            self._portion_graphs.pop(next(iter(self._portion_graphs)))
+        self._portion_graphs[key] = g
+        return g
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt, params: SamplingParams | None = None) -> Sequence:
@@ -259,6 +310,10 @@ class LLMEngine:
         with _nvtx_range("forward"):
             b = self.runner.builder
             k = len(sample_seqs)
+            pg = None
+            if (not use_graph and self.cfg.use_cuda_graphs and self.cfg.graph_prompt_portions > 0 and len(rows) == 1
+                    and len(rows[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and seeds <= {self.cfg.seed}):
+                pg = self._portion_graph(rows, extras, k)
             if use_graph:
                 bs = next(s for s in self.graph_sizes if s >= len(batch))
                 g = self.graphs[bs]
@@ -268,6 +323,13 @@ class LLMEngine:
                 b.to_device(buf, g.layout, into=g.buffer)
                 g.graph.replay()
                 self.num_graph_steps += 1
+                self.h2d_bytes += buf.nbytes
+            elif pg is not None:                           # one portion of one prompt, of a shape seen before
+                buf, layout = b.pack(rows, table_width=self.max_blocks_per_seq, extras=extras)
+                assert layout["size"] == pg.layout["size"]
+                b.to_device(buf, pg.layout, into=pg.buffer)
+                pg.graph.replay()
+                self.num_portion_graph_steps += 1
                 self.h2d_bytes += buf.nbytes
             else:
                 buf, layout = b.pack(rows, extras=extras)

@@ -204,3 +204,33 @@ def test_overlapped_steps_give_the_same_tokens_and_stop_at_eos(overlap, model_fo
     assert all(s.finish_time is not None and s.first_token_time is not None for s in seqs)
     eng.cache.check()
     assert eng.cache.num_free() == eng.cache.pools[0].num_usable and not eng.has_work()
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_long_prompts_in_portions_replayed_from_graphs(dtype_name, model_folders):
+    """Prompts longer than the token budget go in portions of the budget; a step that is one such
+    portion is captured the second time its shape occurs and replayed from then on (tokens, positions
+    and block table differ between replays, the shape does not).  The tokens must be the plain
+    implementation's, and the same as without those graphs."""
+    dtype, rnd = DTYPES[dtype_name]
+    folder = model_folders["tiny_c"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    limit, budget = cfg["max_pos"], 32
+    n = min(limit - 8, 6 * budget + 21)
+    rng = random.Random(3)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)], [rng.randrange(cfg["vocab"]) for _ in range(n - 5)]]
+    from mini_inference_engine_b200 import SamplingParams
+    outs = {}
+    for keep in (4, 0):
+        eng = engine_for(folder, dtype, max_num_batched_tokens=budget, max_model_len=limit, graph_prompt_portions=keep)
+        eng.PORTION_GRAPH_MIN_TOKENS = 16                  # the tiny model's positions end long before the usual 128
+        res = []
+        for p in prompts:                                  # one after the other: every prompt step is one portion of one prompt
+            res += eng.generate([p], SamplingParams(max_tokens=6, ignore_eos=True))
+        outs[keep] = [o.output_ids for o in res]
+        full = n // budget + (n - 5) // budget             # steps of exactly `budget` tokens that want no logits
+        assert eng.num_portion_graph_steps == (full - 1 if keep else 0), (eng.num_portion_graph_steps, full)
+        assert eng.cache.num_free() == eng.cache.pools[0].num_usable
+    assert outs[4] == outs[0]
+    for p, ids in zip(prompts, outs[4]):
+        assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
