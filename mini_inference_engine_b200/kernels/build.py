@@ -165,6 +165,14 @@ def load(name: str) -> ctypes.CDLL:
         return lib
 
 
+def prepare(names, verbose: bool = True) -> None:
+    """Compiles those of ``names`` that are not built yet, side by side: a model that needs nine
+    libraries waits for the slowest of them at its first load, not for their sum."""
+    missing = [n for n in sorted(set(names)) if n not in _libs and not os.path.isfile(library_path(n))]
+    if len(missing) > 1:
+        build_all(verbose, missing)
+
+
 def build_all(verbose: bool = True, sources=SOURCES) -> list[str]:
     """Compiles every source (in parallel processes of nvcc) and returns the library paths."""
     errors: list = []

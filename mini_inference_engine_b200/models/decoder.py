@@ -82,6 +82,13 @@ class DecoderModel:
         if tied:
             sk.head.bind({}, rt, shared=sk.embedding.weight)
         self.embedding, self.final_norm, self.head, self.blocks = sk.embedding, sk.final_norm, sk.head, sk.blocks
+        if rt.device.type == "cuda":
+            # what this model launches is known now: compile what is still missing side by side
+            from ..kernels import build
+            names = set()
+            for _, part in sk.named:
+                names |= part.kernel_sources()
+            build.prepare(names)
         self.run_order = spec.run_order
         # a block that can be told which block runs after it (to prepare that block's first norm)
         self._takes_next = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]

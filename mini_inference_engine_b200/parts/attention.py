@@ -61,6 +61,15 @@ class Attention(Mixer):
 
     takes_sink = True
 
+    def kernel_sources(self):
+        import torch as _torch
+        names = self.rt.product_sources(self.w_qkv, self.w_o) | self.position.kernel_sources()
+        if self.rt.dtype == _torch.float32 or self.head_dim > 128:
+            names.add("attention_simt")
+        if self.rt.dtype != _torch.float32 and self.head_dim <= 128:
+            names |= {"attention_decode", "attention_prefill_tc" if self.head_dim in (64, 128) else "attention_prefill"}
+        return names
+
     def defers_norm(self, num_tokens: int) -> bool:
         return self.rt.defers_norm(num_tokens, self.w_qkv)
 

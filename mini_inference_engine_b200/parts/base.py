@@ -154,6 +154,12 @@ class Runtime:
         from ..kernels import linear as _linear
         return _linear.linear(x, w, bias, out_dtype or self.dtype)
 
+    def product_sources(self, *weights) -> set:
+        """The kernel sources behind ``linear`` for these weights."""
+        if self.dtype == torch.float32 or any(w is not None and w.dtype == torch.float32 for w in weights):
+            return {"gemm_simt"} if self.dtype == torch.float32 else {"gemm_simt", "gemm_tcgen05"}
+        return {"gemm_tcgen05"}
+
     def defers_norm(self, num_tokens: int, w: torch.Tensor) -> bool:
         """Whether the product with ``w`` can take the norm in front of it as a factor on its sums
         (its input then comes as a DeferredNorm from ``linear_into_stream``)."""
@@ -176,6 +182,11 @@ class Runtime:
 class Part:
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
+
+    def kernel_sources(self) -> set:
+        """Names of the kernel sources (csrc/<name>.cu) this part launches once bound; the model
+        compiles the ones still missing side by side when it is built."""
+        return set()
 
     def bind(self, tensors: dict, rt: Runtime) -> None:
         self.rt = rt

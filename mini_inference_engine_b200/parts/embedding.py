@@ -21,6 +21,9 @@ class Embedding(Part):
         self.rt = rt
         self.weight = rt.place(tensors["weight"])
 
+    def kernel_sources(self):
+        return {"embedding"}
+
     def forward(self, ctx):
         res = self.rt.empty(ctx.num_tokens, self.hidden_size, dtype=torch.float32)
         return ops.embedding(self.weight, ctx.token_ids, res, ctx.token_feedback)
@@ -40,6 +43,9 @@ class LinearHead(Part):
     def bind(self, tensors, rt, shared=None):
         self.rt = rt
         self.weight = shared if shared is not None else rt.place(tensors["weight"])
+
+    def kernel_sources(self):
+        return self.rt.product_sources(self.weight)
 
     def forward(self, x):
         return self.rt.linear(x, self.weight, None, out_dtype=torch.float32)

@@ -36,6 +36,9 @@ class SwiGLU(FeedForward):
 
     takes_sink = True
 
+    def kernel_sources(self):
+        return {"activation"} | self.rt.product_sources(self.w_gate_up, self.w_down)
+
     def defers_norm(self, num_tokens: int) -> bool:
         return self.rt.defers_norm(num_tokens, self.w_gate_up)
 

@@ -20,6 +20,9 @@ class RMSNorm(Part):
         self.rt = rt
         self.weight = rt.place(tensors["weight"])
 
+    def kernel_sources(self):
+        return {"norm"}
+
     def deferred_args(self):
         """Weight and eps, for a product that folds this norm into its neighbours' epilogues."""
         return self.weight, self.eps

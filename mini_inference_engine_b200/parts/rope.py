@@ -28,6 +28,9 @@ class Rope(Part):
         self.theta = float(theta)
         self.max_position = max_position
 
+    def kernel_sources(self):
+        return {"rope_cache"}
+
     def inv_freq(self) -> torch.Tensor:
         j = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).float()
         return 1.0 / (self.theta ** (j / self.rotary_dim))
