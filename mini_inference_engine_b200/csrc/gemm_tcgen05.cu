@@ -78,7 +78,7 @@ struct TcParams {
     const int* positions; const int* slots;
     const float* cos_t; const float* sin_t;          // [max_pos, rotary_dim / 2]
     bf16* k_cache; bf16* v_cache;                    // [pages, kv_heads, page_size, head_dim]
-    int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
+    int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, page_shift, max_pos, write_cache;
     uint32_t rope_smem_offset;                       // where the rotation's tables start inside dynamic shared memory
     uint32_t recv_smem_offset;                       // with `push`: where the slots for the peers' partial rows start
     int push;                                        // split-K by sending partial rows to their owners (SWAPPED, when the slots fit)
@@ -121,7 +121,9 @@ __device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, i
 
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// silu(g) * u with the fast exponential and division (a few ulp; the result is rounded to bfloat16 or
+// added to float32 sums of bfloat16 products)
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 template <int BN, bool SWAPPED, bool OUT_F32>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -292,8 +294,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             // where row r of the partial tile goes: the owner's slot for this sender (see the sum below)
             uint32_t send_to = 0;
             if (push) {
-                const int S = p.splits, rows_per = TC_BM / S;
-                const int owner = p.rope ? r % S : r / rows_per, li = p.rope ? r / S : r % rows_per;
+                const int S = p.splits, rows_per = TC_BM / S;              // powers of two: masks and shifts
+                const int s_shift = 31 - __clz(S), rows_shift = 31 - __clz(rows_per);
+                const int owner = p.rope ? r & (S - 1) : r >> rows_shift, li = p.rope ? r >> s_shift : r & (rows_per - 1);
                 send_to = cluster_addr(tiles_base + p.recv_smem_offset, owner) + (uint32_t)((split * rows_per + li) * RED_LD) * 4u;
             }
 #pragma unroll 1
@@ -371,6 +374,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         cluster_sync_all();
         const int S = p.splits;
         const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
+        const int rows_shift = 31 - __clz(rows_per);         // rows_per is a power of two: shifts, no divisions, on this last stretch
         const int r_lo = split * rows_per;
         if (warp >= 2 && !aborted) {
             const int tid = threadIdx.x - 64;                // 0..127
@@ -382,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             // one thread: one row of the tile, four consecutive columns, summed over the blocks in rank order
             for (int idx = tid; idx < rows_per * (BN / 4); idx += 128) {
                 int rr, c, li = 0;
-                if (SWAPPED) { li = idx % rows_per; c = (idx / rows_per) * 4; rr = cyclic ? li * S + split : r_lo + li; }   // neighbours: consecutive features
+                if (SWAPPED) { li = idx & (rows_per - 1); c = (idx >> rows_shift) * 4; rr = cyclic ? li * S + split : r_lo + li; }   // neighbours: consecutive features
                 else { rr = r_lo + idx / (BN / 4); c = (idx % (BN / 4)) * 4; }             // neighbours: consecutive columns
                 const uint32_t off = (uint32_t)(rr * RED_LD + c) * 4u;
                 float4 part[8];
@@ -416,13 +420,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                     const int n = a0 + rr;
                     if (n < p.N) {
                         const int D = p.head_dim, half = p.rotary_dim >> 1;
-                        const int hd = n / D, d = n - hd * D;                 // head (over q, k, v together) and place in it
+                        const int hd = n >> (31 - __clz(D)), d = n & (D - 1); // head (over q, k, v together) and place in it; D divides 128
                         const bool rotated = hd < p.num_heads + p.num_kv_heads && d < p.rotary_dim;
                         float pacc[4] = {0.f, 0.f, 0.f, 0.f};
                         int np = n;
                         if (rotated) {                                       // the partner row: half a rotation apart, same tile
                             np = d < half ? n + half : n - half;
-                            const int pli = li + (np - n) / S;               // the partner's place in this block's slots
+                            const int pli = li + ((np - n) >> (31 - __clz(S)));   // the partner's place in this block's slots (half is a multiple of S)
                             float4 pp[8];
 #pragma unroll
                             for (int s2 = 0; s2 < 8; ++s2)
@@ -452,7 +456,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                                 store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                             } else if (p.write_cache) {
                                 const int slot = rope_slot[c + j];
-                                const int page = slot / p.page_size, off = slot - page * p.page_size;
+                                const int page = slot >> p.page_shift, off = slot & (p.page_size - 1);
                                 const bool is_k = hd < p.num_heads + p.num_kv_heads;
                                 const int kvh = hd - p.num_heads - (is_k ? 0 : p.num_kv_heads);
                                 const int64_t dst = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + off) * D + d;
@@ -490,13 +494,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         }
                     }
                     if (p.sq_out) {
-                        const int width = rows_per < 32 ? rows_per : 32;
+                        const int width = rows_per < 32 ? rows_per : 32;         // 16 or 32
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            for (int o = width >> 1; o > 0; o >>= 1) sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], o);
+                        for (int o = 1; o <= 8; o <<= 1) {                       // four independent trees, step by step
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], o);
+                        }
+                        if (width == 32) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], 16);
+                        }
                         if ((li & (width - 1)) == 0) {
                             const int groups = TC_BM / width;                     // slots per 128-row tile = max(S, 4)
-                            const int slot = blockIdx.x * groups + (split * rows_per + li) / width;
+                            const int slot = blockIdx.x * groups + ((split * rows_per + li) >> (width == 32 ? 5 : 4));
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
                                 if (b0 + c + j < p.sq_stride) p.sq_out[(int64_t)slot * p.sq_stride + b0 + c + j] = sq[j];
@@ -671,6 +681,9 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
         p.k_cache = (bf16*)rope->k_cache; p.v_cache = (bf16*)rope->v_cache;
         p.num_heads = rope->num_heads; p.num_kv_heads = rope->num_kv_heads; p.head_dim = rope->head_dim;
         p.rotary_dim = rope->rotary_dim; p.page_size = rope->page_size; p.max_pos = rope->max_pos;
+        if (rope->page_size < 1 || (rope->page_size & (rope->page_size - 1))) return MIE_ERR_BAD_ARG;
+        p.page_shift = 0;
+        while ((1 << p.page_shift) < rope->page_size) ++p.page_shift;
         p.write_cache = rope->write_cache;
     }
     p.k_tiles = (K + TC_BK - 1) / TC_BK;
