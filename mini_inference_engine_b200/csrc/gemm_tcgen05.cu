@@ -195,14 +195,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             grid_dep_wait();                                  // the activations are the previous kernel's output
             for (int it = 0; it < ahead; ++it)
                 tma_load_2d(tiles + (size_t)it * STAGE_BYTES + x_off, map_x, &full_bar[it], (kt0 + it) * TC_BK, x0);
+            // slot and round by counting: a division by the (run-time) ring depth costs this one thread more
+            // than the MMAs of a k-tile cost to issue
+            int s = ahead == p.stages ? 0 : ahead, round = ahead == p.stages ? 1 : 0;
             for (int it = ahead; it < n_kt; ++it) {
-                const int s = it % p.stages, round = it / p.stages;
                 if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p)) break;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 unsigned char* slot = tiles + (size_t)s * STAGE_BYTES;
                 const int k = (kt0 + it) * TC_BK;
                 tma_load_2d(slot + w_off, map_w, &full_bar[s], k, w0);
                 tma_load_2d(slot + x_off, map_x, &full_bar[s], k, x0);
+                if (++s == p.stages) { s = 0; ++round; }
             }
         }
         __syncwarp();
@@ -211,18 +214,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
             bool ok = true;
+            int s = 0, round = 0;
+            const uint64_t desc_a0 = umma_desc_sw128(tiles_base), desc_b0 = umma_desc_sw128(tiles_base + A_BYTES);
             for (int it = 0; it < n_kt && ok; ++it) {
-                const int s = it % p.stages, round = it / p.stages;
                 ok = mbar_wait(&full_bar[s], round & 1, abort_p);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = tiles_base + (uint32_t)s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+                // the descriptors of a slot's slices differ from the first slot's only in the address field
+                // (units of 16 bytes, 14 bits: shared memory ends below 2^18 bytes, so the sum cannot carry)
+                const uint64_t step = (uint64_t)((uint32_t)s * STAGE_BYTES >> 4);
 #pragma unroll
                 for (int j = 0; j < TC_BK / 16; ++j) {       // 16 elements = 32 bytes of K per MMA, inside the swizzle row
-                    umma_bf16(tmem_base, umma_desc_sw128(a_addr + j * 32), umma_desc_sw128(b_addr + j * 32), idesc,
+                    umma_bf16(tmem_base, desc_a0 + step + (uint64_t)(j * 2), desc_b0 + step + (uint64_t)(j * 2), idesc,
                               (it > 0 || j > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);                  // frees the slot once these MMAs have read it
+                if (++s == p.stages) { s = 0; ++round; }
             }
             if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
         }
