@@ -27,6 +27,14 @@ struct DecodeParams {
 // Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
 // 128-byte swizzle: rows of 64 elements (128 bytes), 64 rows (8 KB) per 64-column part of the head,
 // the piece index XORed with the row's place in its group of eight.
+// 2^x by the hardware approximation (two ulp; -inf gives 0): the library call costs several
+// instructions where one does, in loops that issue instructions most of the time.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t swz_tile_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * 8192 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
@@ -244,7 +252,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const float mn = fmaxf(m[h], mx[h]);
-                alpha[h] = mn == -INFINITY ? 1.f : exp2f(m[h] - mn);
+                alpha[h] = mn == -INFINITY ? 1.f : fast_exp2(m[h] - mn);
                 m[h] = mn;
             }
             unsigned pf[4];
@@ -255,7 +263,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float mm = m[i >> 1];
-                        pv[n][i] = mm == -INFINITY ? 0.f : exp2f(s[n][i] - mm);
+                        pv[n][i] = mm == -INFINITY ? 0.f : fast_exp2(s[n][i] - mm);
                         sum[i >> 1] += pv[n][i];
                     }
                 pf[0] = pack_bf16(pv[0][0], pv[0][1]);
@@ -299,39 +307,53 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
     for (int n = 0; n < NBLK; ++n) {
         const int c = n * 8 + tq * 2;
-        o_s[(warp * 16 + quad) * D + c] = o[n][0];
-        o_s[(warp * 16 + quad) * D + c + 1] = o[n][1];
-        o_s[(warp * 16 + quad + 8) * D + c] = o[n][2];
-        o_s[(warp * 16 + quad + 8) * D + c + 1] = o[n][3];
+        *reinterpret_cast<float2*>(o_s + (warp * 16 + quad) * D + c) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(o_s + (warp * 16 + quad + 8) * D + c) = make_float2(o[n][2], o[n][3]);
     }
     __syncthreads();
     const int unit = (row * p.num_kv_heads + kvh) * p.chunks + chunk;
     float* c_o = o_s + DEC_WARPS * 16 * D;                         // [16][D]: this block's normalised output (cluster merge)
-    for (int idx = threadIdx.x; idx < gn * D; idx += DEC_WARPS * 32) {
-        const int g = idx / D, d = idx - g * D;
+    // The weight of warp w's partial output for head g, 2^(m_w - max) / sum, is the same for all D
+    // dimensions: 16 x DEC_WARPS threads work it out once, the element loop below is four multiply-adds.
+    __shared__ float f_s[DEC_WARPS][16];
+    if (threadIdx.x < 16) {
+        const int g = threadIdx.x;
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, m_s[w][g]);
-        float acc = 0.f, ll = 0.f;
-        if (mm > -INFINITY) {
+        float f[DEC_WARPS], ll = 0.f;
 #pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) {
-                const float f = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - mm);
-                acc += f * o_s[(w * 16 + g) * D + d];
-                ll += f * l_s[w][g];
-            }
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            f[w] = (mm == -INFINITY || m_s[w][g] == -INFINITY) ? 0.f : fast_exp2(m_s[w][g] - mm);
+            ll += f[w] * l_s[w][g];
         }
-        const float val = ll > 0.f ? acc / ll : 0.f;
+        const float inv = ll > 0.f ? __frcp_rn(ll) : 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) f_s[w][g] = f[w] * inv;
+        c_lse[g] = ll > 0.f ? mm + __log2f(ll) : -INFINITY;           // base-2 log-sum-exp of this block's part
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gn * (D / 4); idx += DEC_WARPS * 32) {      // one thread: one head, four dimensions
+        const int g = idx / (D / 4), d = (idx - g * (D / 4)) * 4;
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = f_s[w][g];
+            const float4 v = *reinterpret_cast<const float4*>(o_s + (w * 16 + g) * D + d);
+            val.x += f * v.x; val.y += f * v.y; val.z += f * v.z; val.w += f * v.w;
+        }
         const int head = kvh * G + g0 + g;
         if (p.splits == 1) {
-            p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(val);
+            uint2 packed;
+            packed.x = pack_bf16(val.x, val.y);
+            packed.y = pack_bf16(val.z, val.w);
+            *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d) = packed;
         } else if (p.cluster) {
-            c_o[g * D + d] = val;
-            if (d == 0) c_lse[g] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+            *reinterpret_cast<float4*>(c_o + g * D + d) = val;
         } else {
             const int64_t slot = ((int64_t)row * p.num_heads + head) * p.splits + split;
-            p.part_o[slot * D + d] = val;
-            if (d == 0) p.part_lse[slot] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+            *reinterpret_cast<float4*>(p.part_o + slot * D + d) = val;
+            if (d == 0) p.part_lse[slot] = c_lse[g];
         }
     }
     if (p.splits == 1) return;
@@ -362,12 +384,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
             for (int s2 = 0; s2 < 8; ++s2) {
                 if (s2 < S) {
-                    const float w = lse[s2] == -INFINITY ? 0.f : exp2f(lse[s2] - mm);
+                    const float w = lse[s2] == -INFINITY ? 0.f : fast_exp2(lse[s2] - mm);
                     acc[0] += w * part[s2].x; acc[1] += w * part[s2].y; acc[2] += w * part[s2].z; acc[3] += w * part[s2].w;
                     wsum += w;
                 }
             }
-            const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+            const float inv = wsum > 0.f ? __frcp_rn(wsum) : 0.f;
             const int head = kvh * G + g0 + g;
             uint2 packed;
             packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
@@ -399,7 +421,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         for (int s2 = 0; s2 < p.splits; ++s2) {
             const float lse = __ldcg(p.part_lse + base + s2);
             if (lse == -INFINITY) continue;
-            const float w = exp2f(lse - mm);
+            const float w = fast_exp2(lse - mm);
             acc += w * __ldcg(p.part_o + (base + s2) * D + d);
             wsum += w;
         }
