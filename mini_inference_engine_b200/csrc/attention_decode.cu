@@ -18,10 +18,11 @@
 //   in the reference (decode_attention.py:69).
 //
 // Merging the splits, two ways.  (1) 2, 4 or 8 splits and no scratch given: the splits of a
-// (row, kv head, chunk) are launched as one thread-block cluster; each block leaves its normalised
-// output and base-2 log-sum-exp in shared memory, the cluster synchronises, and every block merges
-// its share of the outputs straight out of the others' shared memory (weights 2^(lse_s - max)).
-// No global round trip, no atomics.  (2) Any number of splits with scratch memory: each block writes
+// (row, kv head, chunk) are launched as one thread-block cluster; every block sends its normalised
+// partial outputs to the blocks that own them (each owns a share of the (head, dimension) items) and
+// its base-2 log-sum-exps to all of them, straight into their shared memory; after one cluster barrier
+// each owner merges what it received (weights 2^(lse_s - max), in rank order).  No global round trip,
+// no atomics.  (2) Any number of splits with scratch memory: each block writes
 // its partial output and log-sum-exp to the scratch and bumps a counter of its unit; the block that
 // sees the count complete merges all partials and resets the counter, so the scratch needs no
 // clearing between launches.  Rows with q_len != 1 are left to the prefill

@@ -63,6 +63,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     unsigned char* tma_tiles = smem_raw + (tma_base - smem_u32(smem_raw));
     __shared__ __align__(8) uint64_t full_bar[4];
     __shared__ int abort_flag;
+    // cluster merge: what the other splits send this block (its share of the outputs, and every split's
+    // log-sum-exp), one slot per sender
+    __shared__ __align__(16) float4 recv_o[16 * (D / 4) + 8];
+    __shared__ float recv_lse[8][16];
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ __align__(16) float c_lse[16];
     __shared__ int s_pages[DEC_PAGE_SLOTS];                        // this block's page ids, fetched once
@@ -78,6 +82,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         pdl_wait();                                                // no block ends before the kernel in front has: later kernels rely on it
         return;
     }
+    if (p.cluster) cluster_arrive_relaxed();                       // see the merge: a block is written to only once it runs
     const int G = p.num_heads / p.num_kv_heads;
     const int kvh = blockIdx.y / p.chunks, chunk = blockIdx.y - kvh * p.chunks;
     const int g0 = chunk * 16, gn = min(16, G - g0);               // query heads of this block within the group
@@ -312,7 +317,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     __syncthreads();
     const int unit = (row * p.num_kv_heads + kvh) * p.chunks + chunk;
-    float* c_o = o_s + DEC_WARPS * 16 * D;                         // [16][D]: this block's normalised output (cluster merge)
     // The weight of warp w's partial output for head g, 2^(m_w - max) / sum, is the same for all D
     // dimensions: 16 x DEC_WARPS threads work it out once, the element loop below is four multiply-adds.
     __shared__ float f_s[DEC_WARPS][16];
@@ -332,6 +336,21 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         for (int w = 0; w < DEC_WARPS; ++w) f_s[w][g] = f[w] * inv;
         c_lse[g] = ll > 0.f ? mm + __log2f(ll) : -INFINITY;           // base-2 log-sum-exp of this block's part
     }
+    // Merging the splits inside a cluster: (head, four dimensions) items go round the blocks, item i to
+    // block i % S.  Every block sends its normalised partial of an item straight to the item's owner
+    // (st.shared::cluster, a slot per sender) and its log-sum-exps to everybody; one cluster barrier; the
+    // owner weighs the S partials by 2^(lse_s - max) out of its own shared memory and writes the result.
+    const int S = p.splits, items_per_owner = (16 * (D / 4) + S - 1) / S;
+    const uint32_t recv_o_addr = (uint32_t)__cvta_generic_to_shared(recv_o);
+    if (p.cluster) {
+        cluster_wait();                                            // every block of the cluster runs
+        if (threadIdx.x < 16) {
+            const float v = c_lse[threadIdx.x];
+            const uint32_t at = (uint32_t)__cvta_generic_to_shared(&recv_lse[split][threadIdx.x]);
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) st_cluster_f32(cluster_addr(at, s2), v);
+        }
+    }
     __syncthreads();
     for (int idx = threadIdx.x; idx < gn * (D / 4); idx += DEC_WARPS * 32) {      // one thread: one head, four dimensions
         const int g = idx / (D / 4), d = (idx - g * (D / 4)) * 4;
@@ -349,7 +368,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             packed.y = pack_bf16(val.z, val.w);
             *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d) = packed;
         } else if (p.cluster) {
-            *reinterpret_cast<float4*>(c_o + g * D + d) = val;
+            const int owner = idx & (S - 1), li = idx >> (31 - __clz(S));            // S is 2, 4 or 8
+            st_cluster_f32x4(cluster_addr(recv_o_addr, owner) + (uint32_t)(split * items_per_owner + li) * 16u, val.x, val.y, val.z, val.w);
         } else {
             const int64_t slot = ((int64_t)row * p.num_heads + head) * p.splits + split;
             *reinterpret_cast<float4*>(p.part_o + slot * D + d) = val;
@@ -359,33 +379,22 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (p.splits == 1) return;
 
     if (p.cluster) {
-        // The splits are the blocks of one cluster: every block merges its share of the outputs
-        // straight out of the others' shared memory, weights 2^(lse_s - max), in rank order.
-        cluster_sync_all();
-        const int S = p.splits;                                    // 2, 4 or 8
-        const int rank = (int)cluster_rank();
-        const uint32_t o_base = (uint32_t)__cvta_generic_to_shared(c_o), l_base = (uint32_t)__cvta_generic_to_shared(c_lse);
-        // one thread: one head, four consecutive dimensions
-        for (int quad_id = threadIdx.x * S + rank; quad_id < gn * (D / 4); quad_id += DEC_WARPS * 32 * S) {
-            const int g = quad_id / (D / 4), d4 = (quad_id - g * (D / 4)) * 4;
-            float lse[8];
-            float4 part[8];
-#pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2) {
-                if (s2 < S) {
-                    lse[s2] = ld_cluster_f32(cluster_addr(l_base + g * 4, s2));
-                    part[s2] = ld_cluster_f32x4(cluster_addr(o_base + (g * D + d4) * 4, s2));
-                }
-            }
+        cluster_sync_all();                                        // every partial and log-sum-exp has arrived
+        // one thread: one head, four consecutive dimensions, the S partials in rank order
+        for (int li = threadIdx.x; li * S + split < gn * (D / 4); li += DEC_WARPS * 32) {
+            const int item = li * S + split;
+            const int g = item / (D / 4), d4 = (item - g * (D / 4)) * 4;
             float mm = -INFINITY;
 #pragma unroll
-            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) mm = fmaxf(mm, lse[s2]);
+            for (int s2 = 0; s2 < 8; ++s2) if (s2 < S) mm = fmaxf(mm, recv_lse[s2][g]);
             float acc[4] = {0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
 #pragma unroll
             for (int s2 = 0; s2 < 8; ++s2) {
                 if (s2 < S) {
-                    const float w = lse[s2] == -INFINITY ? 0.f : fast_exp2(lse[s2] - mm);
-                    acc[0] += w * part[s2].x; acc[1] += w * part[s2].y; acc[2] += w * part[s2].z; acc[3] += w * part[s2].w;
+                    const float lse = recv_lse[s2][g];
+                    const float w = lse == -INFINITY ? 0.f : fast_exp2(lse - mm);
+                    const float4 part = recv_o[s2 * items_per_owner + li];
+                    acc[0] += w * part.x; acc[1] += w * part.y; acc[2] += w * part.z; acc[3] += w * part.w;
                     wsum += w;
                 }
             }
@@ -396,8 +405,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
             *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d4) = packed;
         }
-        cluster_sync_all();                                        // nobody leaves while its shared memory is being read
-        return;
+        return;                                                    // nobody reads this block's memory any more
     }
 
     // the last block of this (row, kv head, chunk) merges the splits
@@ -446,9 +454,9 @@ static int make_decode_map(CUtensorMap* map, const void* ptr, uint64_t rows, int
 
 template <int D, int NSTAGE, bool TMA>
 static int launch_decode_stages(const DecodeParams& p, const DecodeMaps& maps, int num_rows, cudaStream_t stream) {
-    // at least the four-warp merge buffer (4 x 16 x D float32) plus the block's output (16 x D) must fit
+    // at least the four-warp merge buffer (4 x 16 x D float32) must fit
     size_t smem = TMA ? (size_t)NSTAGE * 2 * ((D + 63) / 64) * 8192 + 1024 : (size_t)NSTAGE * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
-    const size_t merge = (size_t)(DEC_WARPS + 1) * 16 * D * sizeof(float);
+    const size_t merge = (size_t)DEC_WARPS * 16 * D * sizeof(float);
     if (smem < merge) smem = merge;
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, NSTAGE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -143,6 +143,9 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
 __device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float v;
     asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
