@@ -15,8 +15,9 @@ import torch
 from . import gemm_tc, ops
 
 _bf16_backend = "auto"
-AUTO_MAX_TOKENS = 16          # up to this many tokens ``auto`` takes the tcgen05 kernel (whole decode step, B200:
-                              # 16 tokens 1.10 ms against 1.13 ms with the library, 32 tokens 1.34 ms against 1.20 ms)
+AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen05 kernel (whole decode step, B200:
+                              # 24 tokens 1.057 ms against 1.098 ms with the library, 32 tokens 1.078 against 1.136 ms,
+                              # 48 tokens 1.61 against 1.18 ms: the 64-token tile re-reads the activations per block)
 
 
 def set_bf16_backend(name: str) -> None:
