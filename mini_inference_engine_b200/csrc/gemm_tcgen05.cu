@@ -254,10 +254,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 rope_slot[i] = t < p.M ? p.slots[t] : 0;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
-            for (int i = et; i < BN * half; i += 128) {
-                const int tt = i / half, jj = i - tt * half;
-                rope_cs[i] = p.cos_t[(int64_t)rope_pos[tt] * half + jj];
-                rope_cs[BN * half + i] = p.sin_t[(int64_t)rope_pos[tt] * half + jj];
+            // 128 / BN threads share a token's row of angles (no division by the run-time half in the loop)
+            constexpr int TOK_THREADS = BN >= 128 ? 1 : 128 / BN;     // threads that share a token's row of angles
+            for (int tt = et / TOK_THREADS; tt < BN; tt += 128 / TOK_THREADS) {
+                const int64_t row = (int64_t)rope_pos[tt] * half;
+                for (int jj = et % TOK_THREADS; jj < half; jj += TOK_THREADS) {
+                    rope_cs[tt * half + jj] = p.cos_t[row + jj];
+                    rope_cs[BN * half + tt * half + jj] = p.sin_t[row + jj];
+                }
             }
         }
         if (p.sq_in) {
@@ -268,9 +272,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             const int et = threadIdx.x - 64;
             for (int i0 = 0; i0 < BN; i0 += 128 / TPT) {
                 const int i = i0 + et / TPT, sub = et % TPT, t = b0 + i;
+                // the first sixteen shares per thread are fetched together (one round trip, not sixteen), then
+                // added in slot order; more than that (hundreds of slots) go one by one
+                const bool live = i < BN && t < p.M;
+                float v[16];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const int sl = sub + k * TPT;
+                    v[k] = (live && sl < p.sq_slots) ? __ldcg(p.sq_in + (int64_t)sl * p.sq_in_stride + t) : 0.f;
+                }
                 float sum = 0.f;
-                if (i < BN && t < p.M)
-                    for (int sl = sub; sl < p.sq_slots; sl += TPT) sum += __ldcg(p.sq_in + (int64_t)sl * p.sq_in_stride + t);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) sum += v[k];
+                if (live)
+                    for (int sl = sub + 16 * TPT; sl < p.sq_slots; sl += TPT) sum += __ldcg(p.sq_in + (int64_t)sl * p.sq_in_stride + t);
 #pragma unroll
                 for (int o = TPT >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
                 if (sub == 0 && i < BN) rstd_s[i] = t < p.M ? rsqrtf(sum / p.sq_width + p.sq_eps) : 1.f;
@@ -282,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             grid_dep_wait();
             const int rows_per = TC_BM / p.splits, idx = threadIdx.x - 64;
             if (idx < rows_per * (BN / 4)) {
-                const int n = a0 + split * rows_per + idx % rows_per, c = (idx / rows_per) * 4;
+                const int n = a0 + split * rows_per + (idx & (rows_per - 1)), c = (idx >> (31 - __clz(rows_per))) * 4;
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
