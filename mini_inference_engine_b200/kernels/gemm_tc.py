@@ -45,7 +45,10 @@ def plan(M: int, N: int, K: int) -> dict:
         tiles = -(-M // 128) * -(-N // bn)
     stage = 128 * 64 * 2 + bn * 64 * 2
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= 2 * NUM_SMS and k_tiles // (splits * 2) >= 2:
+    # few tokens stream the weights, and more blocks stream faster: split up to two blocks per SM.  Many
+    # tokens are bound by the tensor pipe: split only while half the SMs would otherwise idle.
+    room = 2 * NUM_SMS if swapped else NUM_SMS
+    while splits < 8 and tiles * splits * 2 <= room and k_tiles // (splits * 2) >= 2:
         splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
     per_split = -(-k_tiles // splits)
     recv = 128 * (bn + 4) * 4 if swapped and splits > 1 else 0     # the slots for the peers' partial rows, beside the ring
