@@ -49,7 +49,12 @@ def plan(M: int, N: int, K: int) -> dict:
     # tokens are bound by the tensor pipe: split only while half the SMs would otherwise idle.
     room = 2 * NUM_SMS if swapped else NUM_SMS
     while splits < 8 and tiles * splits * 2 <= room and k_tiles // (splits * 2) >= 2:
-        splits *= 2                                  # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least
+        # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least; more blocks than SMs only if
+        # each still streams eight k-tiles (a second wave of short blocks costs more than it brings: the
+        # q|k|v product of TinyLlama, 20 tiles, runs the whole decode step 11 us faster with 4 splits than 8)
+        if tiles * splits * 2 > NUM_SMS and k_tiles // (splits * 2) < 8:
+            break
+        splits *= 2
     per_split = -(-k_tiles // splits)
     recv = 128 * (bn + 4) * 4 if swapped and splits > 1 else 0     # the slots for the peers' partial rows, beside the ring
     stages = max(2, min(8, per_split, (TWO_PER_SM - 1024 - recv) // stage))
@@ -221,6 +226,8 @@ def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots,
     if not supports(x, w, out) or not can_fuse_rope(x, w, num_heads, num_kv_heads, head_dim, rotary_dim):
         raise GemmTcError("these operands cannot take the fused rotation epilogue")
     pl = plan(M, N, K)
+    pl["stages"] = min(pl["stages"], 4)      # the rotation's tables share the block's memory: a fifth stage takes it past what
+                                             # lets two blocks share an SM (whole decode step 0.868 ms with four, 0.901 with five)
     if deferred is not None:
         _launch_fused(x, w, bias, out, M, N, K, pl, False, _fuse_struct(deferred),
                       (positions, slots, cos, sin, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
