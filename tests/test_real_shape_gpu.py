@@ -1,5 +1,7 @@
 """The layer sizes of TinyLlama-1.1B (hidden 2048, 32 query / 4 kv heads of 64, feed-forward 5632,
-vocabulary 32000) with two layers, so that the kernels run at the sizes they are tuned for -- the
+vocabulary 32000) with two layers, and those of Llama-3-8B (hidden 4096, 32 query / 8 kv heads of 128,
+feed-forward 14336; one layer and a cut vocabulary, to keep the folder small), so that the kernels run
+at the sizes they are tuned for -- the
 tcgen05 products and prefill attention, the fused rotation epilogue, the cluster-merged decode
 attention -- and are still compared with the plain implementation, in float32 and in bfloat16:
 a prompt whole, the same prompt in portions, and its tail decoded token by token beside another
@@ -17,11 +19,14 @@ from helpers import close
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def folder(tmp_path_factory):
+@pytest.fixture(scope="module", params=[("tinyllama-1.1b", dict(num_hidden_layers=2)),
+                                        ("llama-3-8b", dict(num_hidden_layers=1, vocab_size=4096))],
+                ids=["tinyllama-1.1b", "llama-3-8b"])
+def folder(request, tmp_path_factory):
     from mini_inference_engine_b200.config import load_preset
     from mini_inference_engine_b200.weights import write_model_folder
-    cfg = dataclasses.replace(load_preset("tinyllama-1.1b"), num_hidden_layers=2)
+    preset, changes = request.param
+    cfg = dataclasses.replace(load_preset(preset), **changes)
     return write_model_folder(str(tmp_path_factory.mktemp("real")), cfg, seed=21)
 
 
@@ -29,8 +34,8 @@ def folder(tmp_path_factory):
 def oracle(folder):
     cfg, W = pl.read_config(folder), plain_weights(folder)
     rng = random.Random(3)
-    a = [rng.randrange(32000) for _ in range(300)]
-    b = [rng.randrange(32000) for _ in range(150)]
+    a = [rng.randrange(cfg["vocab"]) for _ in range(300)]
+    b = [rng.randrange(cfg["vocab"]) for _ in range(150)]
     out = {}
     for name, rnd in (("float32", pl.identity), ("bfloat16", pl.round_bf16)):
         out[name] = (pl.forward(cfg, W, a, rnd), pl.forward(cfg, W, b, rnd))
