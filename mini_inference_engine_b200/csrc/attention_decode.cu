@@ -1,21 +1,24 @@
 // Paged decode attention for bfloat16: one new token per request against its cached context,
 // grouped by kv head and split along the context (flash-decoding), with the merge of the splits
-// done by the last block to finish -- one launch per layer, no second kernel.
+// inside the same launch -- one kernel per layer, no second one.
 //
 // What the reference does in two Triton kernels (inference_engine/kernels/decode_attention.py:20-103:
 // a (batch, kv head, split) grid of tl.dot programs plus a log-sum-exp merge kernel) is here one
 // CUDA kernel on the warp-level tensor-core path (mma.sync m16n8k16, bfloat16 in, float32
-// accumulate); the work per byte of cache is too small for anything but the memory system to
-// matter, so the design is about reading every page once, in 16-byte pieces, with loads in flight
-// while the previous tile is multiplied:
+// accumulate); the work per byte of cache is too small for anything but the memory system and the
+// chain of latencies around it to matter:
 //
 //   grid = (splits, kv heads x head chunks, rows).  A block owns one request row, one kv head, up
 //   to 16 query heads of its group (the MMA's 16 rows) and one contiguous part of the context.
-//   Keys and values arrive in tiles of 64 positions through cp.async into padded shared memory
-//   (three or four stages in flight); warp w multiplies positions 16w..16w+15 of each tile, keeping its own running
-//   max / sum / output, and the four warps are merged once at the end.
-//   scores, softmax and accumulators are float32; P is rounded to bfloat16 for the P.V product, as
-//   in the reference (decode_attention.py:69).
+//   Keys and values arrive in tiles of 64 positions, two to four stages in flight, either 16 bytes
+//   per thread through cp.async into padded shared memory or a page per TMA copy into swizzled
+//   shared memory (the caller's choice, see ops.decode_uses_tma); warp w multiplies positions
+//   16w..16w+15 of each tile, keeping its own running max / sum / output, and the four warps are
+//   merged once at the end.  Scores, softmax and accumulators are float32; P is rounded to bfloat16
+//   for the P.V product, as in the reference (decode_attention.py:69).
+//   The row's lengths, its page table and every cached row but the newest token's are older than
+//   the step, so a block reads them and starts its copies before it waits for the kernel in front
+//   of it (programmatic dependent launch), and fetches the newest row again afterwards.
 //
 // Merging the splits, two ways.  (1) 2, 4 or 8 splits and no scratch given: the splits of a
 // (row, kv head, chunk) are launched as one thread-block cluster; every block sends its normalised
