@@ -22,6 +22,7 @@ struct DecodeParams {
     int cluster;             // 1: the splits of a (row, kv head, chunk) are a thread-block cluster and merge through shared memory
     float scale_log2e;
     int* error;              // host-visible error word (TMA path: a bounded wait that ran out)
+    uint32_t recv_offset;    // where the cluster merge's receive slots start in dynamic shared memory
 };
 
 // Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
@@ -64,9 +65,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __shared__ __align__(8) uint64_t full_bar[4];
     __shared__ int abort_flag;
     // cluster merge: what the other splits send this block (its share of the outputs, and every split's
-    // log-sum-exp), one slot per sender
-    __shared__ __align__(16) float4 recv_o[16 * (D / 4) + 8];
-    __shared__ float recv_lse[8][16];
+    // log-sum-exp), one slot per sender.  Behind the tiles in dynamic shared memory, and only there when the
+    // launch is a cluster: without splits these 5 KB would cost the fourth block on an SM.
+    float4* recv_o = reinterpret_cast<float4*>(smem_raw + p.recv_offset);               // [16 * (D / 4) + 8]
+    float (*recv_lse)[16] = reinterpret_cast<float (*)[16]>(recv_o + 16 * (D / 4) + 8); // [8][16]
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ __align__(16) float c_lse[16];
     __shared__ int s_pages[DEC_PAGE_SLOTS];                        // this block's page ids, fetched once
@@ -458,12 +460,15 @@ static int launch_decode_stages(const DecodeParams& p, const DecodeMaps& maps, i
     size_t smem = TMA ? (size_t)NSTAGE * 2 * ((D + 63) / 64) * 8192 + 1024 : (size_t)NSTAGE * 2 * DEC_TILE * (D + 8) * sizeof(bf16);
     const size_t merge = (size_t)DEC_WARPS * 16 * D * sizeof(float);
     if (smem < merge) smem = merge;
+    DecodeParams pp = p;
+    pp.recv_offset = (uint32_t)((smem + 15) & ~size_t(15));
+    if (p.cluster) smem = pp.recv_offset + (16 * (D / 4) + 8) * sizeof(float4) + 8 * 16 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, NSTAGE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid(p.splits, p.num_kv_heads * p.chunks, num_rows);
     const dim3 cluster(p.cluster ? p.splits : 1, 1, 1);
     return launch_kernel_cluster(decode_attention_kernel<D, NSTAGE, TMA>, grid, dim3(DEC_WARPS * 32), smem, stream, cluster,
-                                 maps.k, maps.v, p);
+                                 maps.k, maps.v, pp);
 }
 
 // Tiles in flight per block.  Few tiles per block (short contexts, many splits): two stages, so that
