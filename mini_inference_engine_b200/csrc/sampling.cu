@@ -29,7 +29,8 @@ template <bool CLUSTER>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int64_t* __restrict__ request, const int* __restrict__ position,
-              uint64_t seed, int* __restrict__ out, int vocab) {
+              uint64_t seed, int* __restrict__ out, int vocab,
+              int* __restrict__ host_out, const int* __restrict__ host_turn, int host_stride) {
     __shared__ float best_v[SAMPLE_THREADS / 32];
     __shared__ int best_i[SAMPLE_THREADS / 32];
     __shared__ float part_v;
@@ -90,7 +91,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         if (lane == 0) { part_v = bv; part_i = bi; }
     }
     if (!CLUSTER) {
-        if (threadIdx.x == 0) out[row] = bi < vocab ? bi : 0;
+        if (threadIdx.x == 0) {
+            const int tok = bi < vocab ? bi : 0;
+            out[row] = tok;
+            if (host_out) host_out[(host_turn ? *host_turn : 0) * host_stride + row] = tok;
+        }
         return;
     }
     cluster_sync_all();                                          // every slice's winner is in its block's shared memory
@@ -107,20 +112,29 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             take(bv, bi, ov, oi);
         }
-        if (lane == 0) out[row] = bi < vocab ? bi : 0;
+        if (lane == 0) {
+            const int tok = bi < vocab ? bi : 0;
+            out[row] = tok;
+            // the host's copy, written straight into its (pinned, device-visible) memory: a copy engine
+            // would take longer to start than this step's 32 bytes take to cross
+            if (host_out) host_out[(host_turn ? *host_turn : 0) * host_stride + row] = tok;
+        }
     }
     cluster_sync_all();                                          // nobody leaves while its shared memory is being read
 }
 
+// `host_out` (optional): pinned host memory [turns][host_stride] that the device can address; row r's
+// token also goes to host_out[*host_turn][r] (host_turn: a device pointer to the turn, or null for 0).
 extern "C" int mie_sample(const float* logits, const float* temperature, const int64_t* request,
                           const int* position, uint64_t seed, int* out, int rows, int vocab,
-                          cudaStream_t stream) {
+                          int* host_out, const int* host_turn, int host_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return MIE_ERR_BAD_ARG;
     if (rows > 65535) return MIE_ERR_TOO_LARGE;
     if (vocab < 4096)                                            // a small vocabulary: one block a row
         return launch_kernel(sample_kernel<false>, dim3(1, rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperature,
-                             request, position, seed, out, vocab);
+                             request, position, seed, out, vocab, host_out, host_turn, host_stride);
     return launch_kernel_cluster(sample_kernel<true>, dim3(SAMPLE_PARTS, rows), dim3(SAMPLE_THREADS), 0, stream,
-                                 dim3(SAMPLE_PARTS, 1, 1), logits, temperature, request, position, seed, out, vocab);
+                                 dim3(SAMPLE_PARTS, 1, 1), logits, temperature, request, position, seed, out, vocab,
+                                 host_out, host_turn, host_stride);
 }

@@ -111,7 +111,9 @@ class LLMEngine:
             self.tokenizer = AutoTokenizer.from_pretrained(model)
 
         most = max(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs, 256, *self.cfg.cuda_graph_batch_sizes)
-        self._pinned_tokens = [torch.empty(most, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        # the sampled tokens as the host sees them: two rows, taken in turns (step N's are read while step
+        # N+1 runs); the sampling kernel writes them itself (pinned memory is addressable from the device)
+        self._pinned_tokens = torch.zeros(2, most, dtype=torch.int32, pin_memory=True)
         self._sampled = torch.zeros(most, dtype=torch.int32, device=self.device)     # the last step's tokens, on the device
         self._turn = 0
         self._in_flight = None
@@ -129,21 +131,22 @@ class LLMEngine:
             self._capture_cuda_graphs()
 
     # ------------------------------------------------------------------ CUDA graphs of decode steps
-    def _sampling_extras(self, n, temps=None, reqs=None, outpos=None):
+    def _sampling_extras(self, n, temps=None, reqs=None, outpos=None, turn=0):
         t = np.zeros(n, dtype=np.float32)
         r = np.zeros(n, dtype=np.int64)
         p = np.zeros(n, dtype=np.int32)
         if temps is not None:
             k = len(temps)
             t[:k], r[:k], p[:k] = temps, reqs, outpos
-        return {"temperature": t, "request": r, "out_position": p}
+        return {"temperature": t, "request": r, "out_position": p, "host_turn": np.array([turn], dtype=np.int32)}
 
     def _forward_and_sample(self, ctx, tokens_out=None):
         logits = self.model.step(ctx)
         if logits.shape[0] == 0:
             return None
         return self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
-                                   ctx.extras["out_position"], out=tokens_out)
+                                   ctx.extras["out_position"], out=tokens_out,
+                                   host_out=self._pinned_tokens, host_turn=ctx.extras["host_turn"])
 
     @torch.inference_mode()
     def _capture_cuda_graphs(self):
@@ -297,9 +300,10 @@ class LLMEngine:
                 rows.append(self.runner.make_row(seq.cache, tokens, [n - 1] if last else []))
                 if last:
                     sample_seqs.append(seq)
+            turn = self._turn ^ 1                              # the row of the pinned token buffer that this step fills
             extras = self._sampling_extras(
                 len(sample_seqs), [s.params.temperature for s in sample_seqs], [s.seq_id for s in sample_seqs],
-                [s.num_output_tokens for s in sample_seqs]) if sample_seqs else None
+                [s.num_output_tokens for s in sample_seqs], turn) if sample_seqs else None
             # the seed of a sampled row: its own if it has one, else the engine's
             row_seeds = [self.cfg.seed if s.params.seed is None else s.params.seed for s in sample_seqs]
             seeds = {sd for sd, s in zip(row_seeds, sample_seqs) if s.params.temperature > 0}
@@ -317,7 +321,7 @@ class LLMEngine:
             if use_graph:
                 bs = next(s for s in self.graph_sizes if s >= len(batch))
                 g = self.graphs[bs]
-                ex = self._sampling_extras(bs, extras["temperature"], extras["request"], extras["out_position"])
+                ex = self._sampling_extras(bs, extras["temperature"], extras["request"], extras["out_position"], turn)
                 buf, layout = b.pack(rows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=ex)
                 assert layout["size"] == g.layout["size"]
                 b.to_device(buf, g.layout, into=g.buffer)
@@ -340,17 +344,18 @@ class LLMEngine:
                 if sample_seqs and len(seeds) <= 1:
                     self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
                                         ctx.extras["out_position"], out=self._sampled[:k],
-                                        seed=next(iter(seeds)) if seeds else None)
+                                        seed=next(iter(seeds)) if seeds else None,
+                                        host_out=self._pinned_tokens, host_turn=ctx.extras["host_turn"])
                 elif sample_seqs:           # requests with different seeds of their own: one launch per row
                     for i, sd in enumerate(row_seeds):
                         self.sampler.sample(logits[i:i + 1], ctx.extras["temperature"][i:i + 1],
                                             ctx.extras["request"][i:i + 1], ctx.extras["out_position"][i:i + 1],
                                             out=self._sampled[i:i + 1], seed=sd)
-            self._turn ^= 1
-            pinned = self._pinned_tokens[self._turn]
+                    self._pinned_tokens[turn, :k].copy_(self._sampled[:k], non_blocking=True)   # this rare way copies
+            self._turn = turn
+            pinned = self._pinned_tokens[turn]
             if k:
-                pinned[:k].copy_(self._sampled[:k], non_blocking=True)
-                self.d2h_bytes += 4 * k
+                self.d2h_bytes += 4 * k                        # written by the sampling kernel into pinned host memory
             done_event = torch.cuda.Event()
             done_event.record()
 

@@ -354,16 +354,28 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.T
 
 # --------------------------------------------------------------------------- sampling
 
-def sample(logits: torch.Tensor, temperature, request, position, seed: int, out: torch.Tensor):
+def sample(logits: torch.Tensor, temperature, request, position, seed: int, out: torch.Tensor,
+           host_out: torch.Tensor | None = None, host_turn: torch.Tensor | None = None):
     """Token ids [rows] from float32 logits [rows, vocab]; per-row temperature (0 = greedy), request
-    id (int64) and output position (int32) key the noise."""
+    id (int64) and output position (int32) key the noise.  ``host_out``: a pinned host tensor
+    [turns, n >= rows] int32 that also receives the tokens, in row ``host_turn[0]`` (a device int32
+    tensor; row 0 without it), written by the kernel itself (pinned memory is addressable from the
+    device), so that no copy has to follow."""
     rows, vocab = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be contiguous float32")
     _need(temperature.dtype == torch.float32 and request.dtype == torch.int64 and position.dtype == torch.int32
           and out.dtype == torch.int32, "sampling argument types")
+    host_ptr, stride = ctypes.c_void_p(0), 0
+    if host_out is not None:
+        _need(host_out.dtype == torch.int32 and host_out.dim() == 2 and host_out.is_pinned() and host_out.is_contiguous()
+              and host_out.shape[1] >= rows, "host_out must be a pinned int32 tensor [turns, n >= rows]")
+        if host_turn is not None:
+            _need(host_turn.is_cuda and host_turn.dtype == torch.int32 and host_turn.numel() >= 1, "host_turn must be a device int32 tensor")
+        host_ptr, stride = ctypes.c_void_p(host_out.data_ptr()), host_out.shape[1]
     lib = build.load("sampling")
     _check(lib.mie_sample(_ptr(logits), _ptr(temperature), _ptr(request), _ptr(position),
-                          ctypes.c_uint64(seed & ((1 << 64) - 1)), _ptr(out), rows, vocab, _stream()), "sample")
+                          ctypes.c_uint64(seed & ((1 << 64) - 1)), _ptr(out), rows, vocab, host_ptr,
+                          _ptr(host_turn) if host_out is not None else ctypes.c_void_p(0), stride, _stream()), "sample")
     return out
 
 

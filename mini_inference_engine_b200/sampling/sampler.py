@@ -16,9 +16,12 @@ class Sampler:
         self.seed = seed
 
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, request: torch.Tensor,
-               position: torch.Tensor, out: torch.Tensor | None = None, seed: int | None = None) -> torch.Tensor:
+               position: torch.Tensor, out: torch.Tensor | None = None, seed: int | None = None,
+               host_out: torch.Tensor | None = None, host_turn: torch.Tensor | None = None) -> torch.Tensor:
         """logits float32 [rows, vocab]; temperature float32 [rows]; request int64 [rows];
-        position int32 [rows] (index of the token being drawn among the request's outputs)."""
+        position int32 [rows] (index of the token being drawn among the request's outputs).
+        ``host_out`` / ``host_turn``: see ``ops.sample``."""
         if out is None:
             out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        return ops.sample(logits, temperature, request, position, self.seed if seed is None else seed, out)
+        return ops.sample(logits, temperature, request, position, self.seed if seed is None else seed, out,
+                          host_out, host_turn)
