@@ -56,7 +56,7 @@ class BatchBuilder:
         q_len = np.ones(R, dtype=np.int32)
         pos0 = np.zeros(R, dtype=np.int32)
         for i, r in enumerate(rows):
-            if not r.tokens:
+            if len(r.tokens) == 0:
                 raise ValueError("a batch row needs at least one token")
             q_len[i] = len(r.tokens)
             pos0[i] = r.pos0

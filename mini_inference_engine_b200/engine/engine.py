@@ -294,9 +294,12 @@ class LLMEngine:
             for seq, n in batch:
                 nc = seq.num_computed
                 last = nc + n == seq.num_tokens
-                tokens = seq.token_ids[nc:nc + n]
-                if tokens[-1] == PENDING:                  # sampled by the step in flight: read on the device
-                    tokens[-1] = -(seq.pending_index + 1)
+                if nc + n <= seq.prompt_len:
+                    tokens = seq.prompt_array[nc:nc + n]       # a view: a prompt portion
+                else:
+                    tokens = seq.token_ids[nc:nc + n]
+                    if tokens[-1] == PENDING:              # sampled by the step in flight: read on the device
+                        tokens[-1] = -(seq.pending_index + 1)
                 rows.append(self.runner.make_row(seq.cache, tokens, [n - 1] if last else []))
                 if last:
                     sample_seqs.append(seq)

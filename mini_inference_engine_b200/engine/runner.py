@@ -4,6 +4,7 @@ place, with the step function on top.  Generation (``LLMEngine``) and trace repl
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, RequestCache
@@ -26,7 +27,8 @@ class ModelRunner:
         """The batch row of a request whose pages for ``tokens`` are already reserved."""
         if self.has_state and rc.num_computed == 0 and rc.state_slot:
             self.storage.clear_state_slot(rc.state_slot)
-        return BatchRow(list(tokens), rc.num_computed, [list(t) for t in rc.tables], rc.state_slot, list(want))
+        toks = tokens if isinstance(tokens, np.ndarray) else list(tokens)      # an array (a prompt portion) goes through as it is
+        return BatchRow(toks, rc.num_computed, [list(t) for t in rc.tables], rc.state_slot, list(want))
 
     # ------------------------------------------------------------------ the step function
     @torch.inference_mode()

@@ -7,6 +7,8 @@ import enum
 import itertools
 import time
 
+import numpy as np
+
 from ..cache.manager import RequestCache
 from ..sampling.params import SamplingParams
 
@@ -24,6 +26,9 @@ class Sequence:
         self.seq_id = next(_ids) if seq_id is None else seq_id
         self.token_ids = list(prompt_ids)
         self.prompt_len = len(self.token_ids)
+        # the prompt once more as an array: a portion of it goes into a step's buffer as a slice, without
+        # turning two thousand Python integers into numbers again at every step
+        self.prompt_array = np.asarray(self.token_ids, dtype=np.int32)
         self.params = params
         self.cache = RequestCache()
         self.status = Status.WAITING
