@@ -143,6 +143,15 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
 __device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+// The same store, asynchronous: it also counts its 16 bytes on an mbarrier of the block it writes to
+// (`bar`, an address in that block's shared memory), so the receiver can wait for exactly what it is
+// owed instead of the whole cluster meeting at a barrier.
+__device__ __forceinline__ void st_async_cluster_f32x4(uint32_t addr, uint32_t bar, float a, float b, float c, float d) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
 }

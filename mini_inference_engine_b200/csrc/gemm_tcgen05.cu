@@ -14,8 +14,9 @@
 // Split-K without scratch memory: the blocks that share an output tile form a thread-block cluster
 // along grid.z (2, 4 or 8 blocks), and every block owns a share of the tile's rows.  SWAPPED (the
 // decode path, where the tail of the kernel is most of its time): each block sends its float32
-// partial rows straight from TMEM into the owner's shared memory (st.shared::cluster, one slot per
-// sender), one cluster barrier follows, and the owner adds up its slots locally.  NORMAL: each
+// partial rows straight from TMEM into the owner's shared memory (st.async to shared::cluster, one
+// slot per sender, every store counted on the owner's own mbarrier), and the owner adds up its slots
+// locally as soon as its 128 x BN sums have landed: no barrier across the cluster.  NORMAL: each
 // block leaves its partial tile in its own shared memory and, after a barrier, reads its share out
 // of the others' (ld.shared::cluster); a second barrier keeps everyone's memory alive meanwhile.
 // Either way the sum runs in rank order -- the same order every time -- with no global partial
@@ -134,6 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];
     __shared__ __align__(8) uint64_t tmem_full_bar;
+    __shared__ __align__(8) uint64_t recv_bar;               // push: counts the bytes of the peers' partial rows as they land
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -152,7 +154,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     // SWAPPED split-K sends partial rows into the peers' shared memory.  A block may be written to only
     // once it runs: everybody arrives here, and waits (long since satisfied) before its first send.
     const bool push = SWAPPED && p.push;
-    if (push) cluster_arrive_relaxed();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TC_BM;          // first row of the 128-row operand
@@ -166,9 +167,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         abort_flag = 0;
         for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&tmem_full_bar, 1);
+        mbar_init(&recv_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the barriers are used by the TMA unit
+        // what this block is owed: every block of the cluster sends it rows_per rows of BN sums
+        if (push) mbar_expect_tx(&recv_bar, (uint32_t)(TC_BM * BN * sizeof(float)));
     }
+    // Peers write into this block's memory and count on its barrier: both must exist first.  Everybody
+    // arrives here (thread 0 after it has set the barriers up) and waits, long since satisfied, before
+    // its first send.
+    if (push) cluster_arrive_release();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -209,7 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             }
         }
         __syncwarp();
-        if (push) cluster_wait();
+        if (push) cluster_wait_acquire();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
@@ -234,9 +242,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
         }
         __syncwarp();
-        if (push) cluster_wait();
+        if (push) cluster_wait_acquire();
     } else {
-        if (push) cluster_wait();                            // every block of the cluster runs: its memory may be written
+        if (push) cluster_wait_acquire();                    // every block of the cluster runs: its memory and barrier may be written
         // epilogue: warp q reads TMEM lanes 32q .. 32q+31; thread r owns row r of the MMA tile
         const int q = warp & 3;
         const int r = q * 32 + lane;
@@ -314,12 +322,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
             float* red = reinterpret_cast<float*>(tiles);     // the ring is free: every MMA has read its slot
             // where row r of the partial tile goes: the owner's slot for this sender (see the sum below)
-            uint32_t send_to = 0;
+            uint32_t send_to = 0, send_bar = 0;
             if (push) {
                 const int S = p.splits, rows_per = TC_BM / S;              // powers of two: masks and shifts
                 const int s_shift = 31 - __clz(S), rows_shift = 31 - __clz(rows_per);
                 const int owner = p.rope ? r & (S - 1) : r >> rows_shift, li = p.rope ? r >> s_shift : r & (rows_per - 1);
                 send_to = cluster_addr(tiles_base + p.recv_smem_offset, owner) + (uint32_t)((split * rows_per + li) * RED_LD) * 4u;
+                send_bar = cluster_addr(smem_u32(&recv_bar), owner);
             }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
@@ -331,7 +340,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 }
                 if (push) {
 #pragma unroll
-                    for (int i = 0; i < 16; i += 4) st_cluster_f32x4(send_to + (uint32_t)(c + i) * 4u, v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    for (int i = 0; i < 16; i += 4)
+                        st_async_cluster_f32x4(send_to + (uint32_t)(c + i) * 4u, send_bar, v[i], v[i + 1], v[i + 2], v[i + 3]);
                 } else if (p.splits > 1) {                     // leave the partial tile for the cluster
 #pragma unroll
                     for (int i = 0; i < 16; ++i) red[r * RED_LD + c + i] = v[i];
@@ -390,15 +400,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
 
     if (p.splits > 1) {
         // split-K: add the partial tiles of the cluster's blocks, each block its share of the rows.
-        // With `push` the partial rows are in this block's slots already (slot s = what rank s sent), so one
-        // barrier and local loads do; with the rotation a block owns every S-th row, which keeps a row and
-        // its partner (half a rotation apart, a multiple of S) with the same owner.
-        cluster_sync_all();
+        // With `push` the partial rows arrive in this block's slots (slot s = what rank s sent) and are
+        // counted on its own barrier: it waits for its 128 x BN sums and nobody else's, no barrier across
+        // the cluster; with the rotation a block owns every S-th row, which keeps a row and its partner
+        // (half a rotation apart, a multiple of S) with the same owner.
+        bool have_all = true;
+        if (push) { if (warp >= 2) have_all = mbar_wait(&recv_bar, 0, abort_p); }
+        else cluster_sync_all();
         const int S = p.splits;
         const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
         const int rows_shift = 31 - __clz(rows_per);         // rows_per is a power of two: shifts, no divisions, on this last stretch
         const int r_lo = split * rows_per;
-        if (warp >= 2 && !aborted) {
+        if (warp >= 2 && !aborted && have_all) {
             const int tid = threadIdx.x - 64;                // 0..127
             uint32_t peer[8];
 #pragma unroll
@@ -555,7 +568,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         if (!push) cluster_sync_all();                       // nobody leaves while its shared memory is being read
     }
 
-    if (aborted) {
+    __syncthreads();
+    if (abort_flag) {
         if (threadIdx.x == 0) atomicExch(p.error, 1);
         for (int i = 0; i < 64; ++i) __nanosleep(2000);       // let copies that are still in flight land
     }
