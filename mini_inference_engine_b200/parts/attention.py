@@ -41,6 +41,7 @@ class Attention(Mixer):
         if self.bias:
             specs.update({"q_proj.bias": TensorSpec((H * D,), "zeros"), "k_proj.bias": TensorSpec((Hkv * D,), "zeros"),
                           "v_proj.bias": TensorSpec((Hkv * D,), "zeros")})
+        specs.update(self.position.tensor_specs())       # a position encoding with tensors of its own
         return specs
 
     def bind(self, tensors, rt):
@@ -54,7 +55,7 @@ class Attention(Mixer):
             self.b_qkv = rt.place(torch.cat([tensors[n + "_proj.bias"].float() for n in "qkv"], 0).to(
                 torch.float32 if rt.dtype == torch.float32 else torch.bfloat16))
         self.w_o = rt.place(tensors["o_proj.weight"])
-        self.position.bind({}, rt)
+        self.position.bind({n: tensors[n] for n in self.position.tensor_specs()}, rt)
 
     def cache_need(self):
         return KVNeed(self.num_kv_heads, self.head_dim, self.window)
