@@ -20,6 +20,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from .pages import PageError, PagePool
 
 RELEASED = 0   # block-table entry of a page the window has passed: the scratch page
@@ -40,6 +42,15 @@ class RequestCache:
     first_live: list = field(default_factory=list)
     state_slot: int = 0
     num_computed: int = 0
+    version: int = 0                  # counts the changes of ``tables`` (the manager bumps it)
+    _arrays: tuple = field(default=(-1, None), repr=False, compare=False)
+
+    def table_arrays(self) -> list:
+        """``tables`` as int32 arrays, made again only after a change: a running request's table
+        changes once a page, the batch builder wants it every step.  Read-only by agreement."""
+        if self._arrays[0] != self.version:
+            self._arrays = (self.version, [np.array(t, dtype=np.int32) for t in self.tables])
+        return self._arrays[1]
 
 
 class CacheManager:
@@ -51,6 +62,7 @@ class CacheManager:
         self.block_size = block_size
         counts = num_pages if isinstance(num_pages, (list, tuple)) else [num_pages] * len(groups)
         self.pools = [PagePool(n) for n in counts]
+        self._windowed = any(g.window is not None for g in self.groups)
         # slot 0 is the scratch slot of padding rows, like page 0
         self.state_pool = PagePool(num_state_slots + 1) if num_state_slots > 0 else None
 
@@ -80,6 +92,7 @@ class CacheManager:
     def _ensure_tables(self, rc: RequestCache) -> None:
         if not rc.tables:
             rc.tables = [[] for _ in self.groups]
+            rc.version += 1
             rc.first_live = [0 for _ in self.groups]
 
     # ------------------------------------------------------------------ reserve / advance / free
@@ -90,12 +103,16 @@ class CacheManager:
     def reserve(self, rc: RequestCache, n_new: int, watermark: int = 0) -> bool:
         """Makes sure the request has pages for its next ``n_new`` tokens in every group; takes
         nothing when any group cannot give what is needed."""
+        last = -(-(rc.num_computed + n_new) // self.block_size)
+        if rc.tables and all(len(t) >= last for t in rc.tables):
+            return True                       # the common case of a decode step: the last page has room
         need = self.pages_needed(rc, n_new)
         if not all(self.pools[g].can_take(need[g], watermark) for g in range(len(self.groups))):
             return False
         for g, n in enumerate(need):
             if n:
                 rc.tables[g].extend(self.pools[g].take(n))
+                rc.version += 1
         return True
 
     def take_state_slot(self, rc: RequestCache) -> bool:
@@ -111,6 +128,8 @@ class CacheManager:
         passed; returns them per group (for tests)."""
         rc.num_computed += n
         released = [[] for _ in self.groups]
+        if not self._windowed:
+            return released
         for g in range(len(self.groups)):
             first = min(self._first_needed_page(g, rc.num_computed), len(rc.tables[g]))
             for i in range(rc.first_live[g], first):
@@ -120,6 +139,7 @@ class CacheManager:
                     rc.tables[g][i] = RELEASED
             if released[g]:
                 self.pools[g].give_back(released[g])
+                rc.version += 1
             rc.first_live[g] = max(rc.first_live[g], first)
         return released
 
@@ -129,6 +149,7 @@ class CacheManager:
         for g in range(len(self.groups)):
             self.pools[g].give_back([p for p in rc.tables[g] if p != RELEASED])
         rc.tables = [[] for _ in self.groups]
+        rc.version += 1
         rc.first_live = [0 for _ in self.groups]
         rc.num_computed = 0
         if self.state_pool is not None and rc.state_slot:

@@ -53,13 +53,13 @@ class BatchBuilder:
         that ride in the same transfer; they come back as ``ctx.extras[name]`` on the device."""
         R_real = len(rows)
         R = max(R_real, pad_rows or 0)
+        lens = [len(r.tokens) for r in rows]
+        if R_real and min(lens) == 0:
+            raise ValueError("a batch row needs at least one token")
         q_len = np.ones(R, dtype=np.int32)
         pos0 = np.zeros(R, dtype=np.int32)
-        for i, r in enumerate(rows):
-            if len(r.tokens) == 0:
-                raise ValueError("a batch row needs at least one token")
-            q_len[i] = len(r.tokens)
-            pos0[i] = r.pos0
+        q_len[:R_real] = lens
+        pos0[:R_real] = [r.pos0 for r in rows]
         q_start = np.zeros(R + 1, dtype=np.int32)
         np.cumsum(q_len, out=q_start[1:])
         T = int(q_start[-1])
@@ -101,35 +101,43 @@ class BatchBuilder:
         seg("row_q_start")[:] = q_start[:R]
         seg("row_q_len")[:] = q_len
         seg("row_ctx_len")[:] = ctx_len
-        tok, pos, trow, want = seg("token_ids"), seg("positions"), seg("token_row"), seg("want")
-        slots = [seg(f"slots{g}") for g in range(self.num_groups)]
-        tables = [seg(f"tables{g}").reshape(R, width) for g in range(self.num_groups)]
-        trow[:] = np.repeat(np.arange(R, dtype=np.int32), q_len)
+        seg("state_slots")[:R_real] = [r.state_slot for r in rows]
+        tok, pos, trow = seg("token_ids"), seg("positions"), seg("token_row")
+        # Per row only what has to be: its tokens, its block tables, its wanted places.  Positions and
+        # cache slots of all tokens come from the rows' numbers in one go (a decode step has one token
+        # a row, and many rows).
+        if R_real and max(lens) == 1:
+            trow[:] = np.arange(R, dtype=np.int32)
+            pos[:] = pos0
+            tok[:R_real] = [r.tokens[0] for r in rows]
+        else:
+            trow[:] = np.repeat(np.arange(R, dtype=np.int32), q_len)
+            pos[:] = pos0[trow] + (np.arange(T, dtype=np.int32) - q_start[:R][trow])
+            for r, a, m in zip(rows, q_start.tolist(), lens):
+                tok[a:a + m] = r.tokens
         ps = self.page_size
-        w = 0
-        for i, r in enumerate(rows):
-            a, b = int(q_start[i]), int(q_start[i + 1])
-            tok[a:b] = r.tokens
-            p = np.arange(r.pos0, r.pos0 + (b - a), dtype=np.int32)
-            pos[a:b] = p
-            seg("state_slots")[i] = r.state_slot
-            for g in range(self.num_groups):
-                t = np.asarray(r.tables[g], dtype=np.int32)
-                if len(t) > width:
-                    raise ValueError(f"block table of {len(t)} pages exceeds the width {width}")
-                if (int(p[-1]) // ps) >= len(t):
-                    raise ValueError("a batch row has no page for its last new token")
-                tables[g][i, :len(t)] = t
-                slots[g][a:b] = t[p // ps] * ps + p % ps
+        last_page = (ctx_len[:R_real] - 1) // ps
+        for g in range(self.num_groups):
+            tg = seg(f"tables{g}").reshape(R, width)
+            held = np.zeros(R_real, dtype=np.int32)
+            for i, r in enumerate(rows):
+                t = r.tables[g]
+                m = len(t)
+                if m > width:
+                    raise ValueError(f"block table of {m} pages exceeds the width {width}")
+                tg[i, :m] = t
+                held[i] = m
+            if R_real and bool((last_page >= held).any()):
+                raise ValueError("a batch row has no page for its last new token")
+            seg(f"slots{g}")[:] = tg[trow, pos // ps] * ps + pos % ps
+        wanted = []
+        for r, a, m in zip(rows, q_start.tolist(), lens):
             for j in r.want:
-                if not 0 <= j < b - a:
-                    raise ValueError(f"wanted place {j} is outside the row's {b - a} tokens")
-                want[w] = a + j
-                w += 1
-        for i in range(R_real, R):            # scratch rows
-            if w < W:
-                want[w] = int(q_start[i])
-                w += 1
+                if not 0 <= j < m:
+                    raise ValueError(f"wanted place {j} is outside the row's {m} tokens")
+                wanted.append(a + j)
+        wanted.extend(q_start[R_real:R].tolist())            # scratch rows
+        seg("want")[:] = wanted
         layout = dict(off=off, T=T, R=R, W=W, width=width, size=n, real_rows=R_real,
                       extras={k: v[:3] for k, v in extra_off.items()},
                       max_q_len=int(q_len.max()) if R else 0, max_ctx_len=int(ctx_len.max()) if R else 0,

@@ -291,28 +291,34 @@ class LLMEngine:
             return None
         with _nvtx_range("prepare"):
             rows, sample_seqs = [], []
+            make_row = self.runner.make_row
+            pure_decode = True
             for seq, n in batch:
-                nc = seq.num_computed
-                last = nc + n == seq.num_tokens
+                nc = seq.cache.num_computed
+                last = nc + n == len(seq.token_ids)
                 if nc + n <= seq.prompt_len:
                     tokens = seq.prompt_array[nc:nc + n]       # a view: a prompt portion
                 else:
                     tokens = seq.token_ids[nc:nc + n]
                     if tokens[-1] == PENDING:              # sampled by the step in flight: read on the device
                         tokens[-1] = -(seq.pending_index + 1)
-                rows.append(self.runner.make_row(seq.cache, tokens, [n - 1] if last else []))
+                rows.append(make_row(seq.cache, tokens, (n - 1,) if last else ()))
                 if last:
                     sample_seqs.append(seq)
+                if n != 1 or not last:
+                    pure_decode = False
             turn = self._turn ^ 1                              # the row of the pinned token buffer that this step fills
-            extras = self._sampling_extras(
-                len(sample_seqs), [s.params.temperature for s in sample_seqs], [s.seq_id for s in sample_seqs],
-                [s.num_output_tokens for s in sample_seqs], turn) if sample_seqs else None
             # the seed of a sampled row: its own if it has one, else the engine's
             row_seeds = [self.cfg.seed if s.params.seed is None else s.params.seed for s in sample_seqs]
             seeds = {sd for sd, s in zip(row_seeds, sample_seqs) if s.params.temperature > 0}
-            pure_decode = len(sample_seqs) == len(batch) and all(n == 1 for _, n in batch)
             use_graph = (pure_decode and self.graph_sizes and len(batch) <= self.graph_sizes[-1]
                          and seeds <= {self.cfg.seed})
+            # sampling inputs ride in the step's buffer; a step replayed from a graph has its bucket's rows
+            bs = next(s for s in self.graph_sizes if s >= len(batch)) if use_graph else 0
+            extras = self._sampling_extras(
+                bs if use_graph else len(sample_seqs), [s.params.temperature for s in sample_seqs],
+                [s.seq_id for s in sample_seqs], [len(s.token_ids) - s.prompt_len for s in sample_seqs],
+                turn) if sample_seqs else None
 
         with _nvtx_range("forward"):
             b = self.runner.builder
@@ -322,10 +328,8 @@ class LLMEngine:
                     and len(rows[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and seeds <= {self.cfg.seed}):
                 pg = self._portion_graph(rows, extras, k)
             if use_graph:
-                bs = next(s for s in self.graph_sizes if s >= len(batch))
                 g = self.graphs[bs]
-                ex = self._sampling_extras(bs, extras["temperature"], extras["request"], extras["out_position"], turn)
-                buf, layout = b.pack(rows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=ex)
+                buf, layout = b.pack(rows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=extras)
                 assert layout["size"] == g.layout["size"]
                 b.to_device(buf, g.layout, into=g.buffer)
                 g.graph.replay()
@@ -368,10 +372,12 @@ class LLMEngine:
         for seq, n in batch:
             self.cache.advance(seq.cache, n)
         ending = []
+        max_len = self.cfg.max_model_len
         for i, seq in enumerate(sample_seqs):
             seq.pending_index = i
             seq.token_ids.append(PENDING)
-            if seq.num_output_tokens >= seq.params.max_tokens or seq.num_tokens >= self.cfg.max_model_len:
+            total = len(seq.token_ids)
+            if total - seq.prompt_len >= seq.params.max_tokens or total >= max_len:
                 self.scheduler.finish(seq)                 # its pages may go to the next step: that one runs after this one
                 ending.append(seq)
         return _InFlight(sample_seqs, [s.num_tokens - 1 for s in sample_seqs], ending, pinned, done_event)

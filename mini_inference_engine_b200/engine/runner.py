@@ -28,7 +28,7 @@ class ModelRunner:
         if self.has_state and rc.num_computed == 0 and rc.state_slot:
             self.storage.clear_state_slot(rc.state_slot)
         toks = tokens if isinstance(tokens, np.ndarray) else list(tokens)      # an array (a prompt portion) goes through as it is
-        return BatchRow(toks, rc.num_computed, [list(t) for t in rc.tables], rc.state_slot, list(want))
+        return BatchRow(toks, rc.num_computed, rc.table_arrays(), rc.state_slot, want)
 
     # ------------------------------------------------------------------ the step function
     @torch.inference_mode()

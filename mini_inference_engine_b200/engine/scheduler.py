@@ -72,8 +72,12 @@ class Scheduler:
         decodes, prefills = [], []
         preemptions_before = self.num_preemptions
 
+        in_prompt = []
         for seq in list(self.running):                                   # 1. decodes
-            if seq.status is not Status.RUNNING or seq.num_new_tokens != 1:
+            if seq.status is not Status.RUNNING:
+                continue
+            if len(seq.token_ids) - seq.cache.num_computed != 1:
+                in_prompt.append(seq)
                 continue
             if budget == 0:
                 break
@@ -81,7 +85,7 @@ class Scheduler:
                 decodes.append((seq, 1))
                 budget -= 1
 
-        for seq in list(self.running):                                   # 2. prompts in flight
+        for seq in in_prompt:                                            # 2. prompts in flight
             if seq.status is not Status.RUNNING or seq.num_new_tokens <= 1 or budget == 0:
                 continue
             n = min(seq.num_new_tokens, budget)
