@@ -97,7 +97,10 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch
     if M == 0:
         return out
     if isinstance(x, gemm_tc.DeferredNorm):
-        return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
+        if w_interleaved.shape[0] % 16 == 0:
+            return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
+        gu = gemm_tc.gemm(x, w_interleaved, torch.empty(M, 2 * inter, dtype=out_dtype, device=out.device))
+        return ops.swiglu(gu, out, interleaved=True)       # the fused epilogue pairs rows within groups of 16
     if uses_tcgen05(x, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and gemm_tc.supports(x, w_interleaved, out):
         return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
     gu = linear(x, w_interleaved, None, out_dtype)

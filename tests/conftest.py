@@ -25,6 +25,13 @@ TINY = {
                    num_attention_heads=3, num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-6,
                    rope_theta=500000.0, max_position_embeddings=256, tie_word_embeddings=True,
                    architectures=["LlamaForCausalLM"]),
+    # wide enough (five 64-wide K tiles) that single-token steps in bfloat16 split K on the tensor-core
+    # product and fold rotation, residual sums and norms into it; a feed-forward width whose doubled
+    # size is no multiple of 16, an odd vocabulary, three query heads a key head
+    "tiny_d": dict(vocab_size=1031, hidden_size=320, intermediate_size=300, num_hidden_layers=2,
+                   num_attention_heads=6, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-5,
+                   rope_theta=50000.0, max_position_embeddings=192, tie_word_embeddings=False,
+                   architectures=["LlamaForCausalLM"]),
 }
 
 

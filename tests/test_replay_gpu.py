@@ -16,7 +16,7 @@ from replay_driver import Replay
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [5, 17, 33, 64, 100, 128, 2, 49], "tiny_b": [1, 60, 37, 255, 130, 16, 97, 200],
-           "tiny_c": [3, 96, 31, 50, 17, 64, 80, 9]}
+           "tiny_c": [3, 96, 31, 50, 17, 64, 80, 9], "tiny_d": [7, 150, 64, 33, 2, 120, 48, 191]}
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
@@ -63,7 +63,7 @@ def collect(got, entries, logits):
     assert logits is None or i == len(logits)
 
 
-CASES = [(n, d) for n in ("tiny_a", "tiny_b", "tiny_c") for d in ("float32", "bfloat16")]
+CASES = [(n, d) for n in ("tiny_a", "tiny_b", "tiny_c", "tiny_d") for d in ("float32", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype_name", CASES)
