@@ -121,6 +121,9 @@ def test_random_requests_never_lose_or_share_a_page(seed):
             assert sorted(held) == m.pools[g].held_pages()
         slots = [rc.state_slot for rc in live]
         assert len(slots) == len(set(slots)) and 0 not in slots
+        for rc in live:                                   # the arrays the batch builder gets are never stale
+            if rc.tables:
+                assert [t.tolist() for t in rc.table_arrays()] == rc.tables
     for rc in live:
         m.free(rc)
     m.check()
@@ -144,6 +147,56 @@ def test_batch_packing_positions_slots_and_wanted_places():
     assert ctx.block_tables[0].tolist() == [[7, 2, 9], [4, 6, 0], [3, 0, 0]]
     assert ctx.state_slots.tolist() == [1, 2, 3]
     assert ctx.max_q_len == 5 and ctx.max_ctx_len == 34
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_batch_packing_of_random_batches_token_by_token(seed):
+    """Single decoded tokens beside portions, tables as lists or arrays, one or two groups, padded or
+    not: every token's position, row and cache slot against the definition, one token at a time."""
+    rng = random.Random(seed)
+    G, ps = rng.choice([1, 2]), rng.choice([4, 16])
+    b = BatchBuilder(G, ps, "cpu", max_position=4096)
+    R = rng.randrange(1, 12)
+    only_decode = seed % 3 == 0
+    rows = []
+    for _ in range(R):
+        n = 1 if only_decode or rng.random() < 0.5 else rng.randrange(2, 50)
+        pos0 = rng.randrange(0, 300)
+        pages = -(-(pos0 + n) // ps) + rng.randrange(0, 2)
+        tabs = [[rng.randrange(1, 900) for _ in range(pages)] for _ in range(G)]
+        if rng.random() < 0.5:
+            tabs = [np.array(t, dtype=np.int32) for t in tabs]
+        toks = [rng.randrange(-4, 1000) for _ in range(n)]
+        if n > 1 and rng.random() < 0.5:
+            toks = np.array(toks, dtype=np.int32)
+        rows.append(BatchRow(toks, pos0, tabs, rng.randrange(0, 5), sorted(rng.sample(range(n), rng.randrange(0, min(n, 3) + 1)))))
+    pad = R + rng.randrange(0, 4) if seed % 2 else None
+    width = max(len(t) for r in rows for t in r.tables) + rng.randrange(0, 3) if seed % 2 else None
+    ctx = b.to_device(*b.pack(rows, pad_rows=pad, table_width=width))
+    tok, pos, trow, want = [], [], [], []
+    slots = [[] for _ in range(G)]
+    for i, r in enumerate(rows):
+        for j, t in enumerate(list(r.tokens)):
+            if j in r.want:
+                want.append(len(tok))
+            tok.append(int(t)); pos.append(r.pos0 + j); trow.append(i)
+            for g in range(G):
+                slots[g].append(int(r.tables[g][(r.pos0 + j) // ps]) * ps + (r.pos0 + j) % ps)
+    for i in range(R, pad or R):                           # scratch rows: token 0 at position 0 of page 0
+        want.append(len(tok))
+        tok.append(0); pos.append(0); trow.append(i)
+        for g in range(G):
+            slots[g].append(0)
+    assert ctx.token_ids.tolist() == tok and ctx.positions.tolist() == pos and ctx.token_row.tolist() == trow
+    assert ctx.want.tolist() == want
+    for g in range(G):
+        assert ctx.slots[g].tolist() == slots[g]
+        for i, r in enumerate(rows):
+            have = ctx.block_tables[g][i].tolist()
+            assert have[:len(r.tables[g])] == list(map(int, r.tables[g])) and not any(have[len(r.tables[g]):])
+    assert ctx.row_q_len.tolist() == [len(r.tokens) for r in rows] + [1] * ((pad or R) - R)
+    assert ctx.row_ctx_len.tolist() == [r.pos0 + len(r.tokens) for r in rows] + [1] * ((pad or R) - R)
+    assert ctx.state_slots.tolist() == [r.state_slot for r in rows] + [0] * ((pad or R) - R)
 
 
 def test_batch_packing_padding_rows_and_extras():
