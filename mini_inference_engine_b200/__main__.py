@@ -6,6 +6,7 @@ benchmarks/profile_decode.py (``--graphs --batch --prompt --steps``) keep their 
     python -m mini_inference_engine_b200 generate   --model DIR --prompt-ids 1,2,3 --max-tokens 16
     python -m mini_inference_engine_b200 latency    --preset tinyllama-1.1b --batches 1 8 64 --prompt 512 --steps 100
     python -m mini_inference_engine_b200 throughput --preset tinyllama-1.1b --batch 32 --workload mixed
+    python -m mini_inference_engine_b200 profile-decode --preset tinyllama-1.1b --graphs 1 --batch 32 --steps 50
     python -m mini_inference_engine_b200 make-model --preset tiny-llama-a --seed 0 --out DIR
 
 A model is a folder (``--model``) or a preset with random weights (``--preset`` + ``--seed``), which
@@ -108,8 +109,17 @@ def make_workload(kind: str, n: int, seed: int, vocab: int):
 
 
 def cmd_throughput(args):
+    import gc
+
     import torch
 
+    if args.batches:                       # several concurrency caps, one engine after the other
+        for bs in args.batches:
+            one = argparse.Namespace(**{**vars(args), "batch": bs, "batches": None})
+            cmd_throughput(one)
+            gc.collect()
+            torch.cuda.empty_cache()
+        return
     from . import SamplingParams
     eng = _engine(args, max_num_seqs=args.batch)
     reqs = make_workload(args.workload, args.num_requests, 0, eng.vocab_size)
@@ -129,6 +139,49 @@ def cmd_throughput(args):
         "kv_cache_tokens": eng.cache.pools[0].num_pages * eng.cfg.block_size,
         "output_tokens": out_tokens, "prompt_tokens": in_tokens, "output_tok_per_s": out_tokens / secs,
         "total_tok_per_s": (out_tokens + in_tokens) / secs}))
+
+
+def cmd_profile_decode(args):
+    """Steady-state decode at one batch size, for a profiler (the workload of
+    benchmarks/profile_decode.py:29-42): every engine step is wrapped in NVTX ranges (schedule /
+    prepare / forward / sample), the measured steps in a range "decode_steps".  Without a profiler it
+    still says what a step costs: wall and device time, kernels of this package and launch calls."""
+    import torch
+
+    from . import SamplingParams
+    from .kernels import ops
+    from . import EngineConfig
+    forced = {"max_num_seqs": args.batch} if args.batch > EngineConfig().max_num_seqs else {}
+    eng = _engine(args, use_cuda_graphs=bool(args.graphs), **forced)
+    for i in range(args.batch):
+        ids = [1 % eng.vocab_size] + [(1000 + (i * 7 + j) % 30000) % eng.vocab_size for j in range(args.prompt - 1)]
+        eng.add_request(ids, SamplingParams(max_tokens=args.steps + 30, ignore_eos=True))
+    while any(s.num_new_tokens > 1 for s in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(20):
+        eng.step()
+    eng.drain()
+    torch.cuda.synchronize()
+    launches0, graph0 = ops.launches, eng.num_graph_steps
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.nvtx.range_push("decode_steps")
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(args.steps):
+        eng.step()
+    eng.drain()
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    torch.cuda.nvtx.range_pop()
+    graph_steps = eng.num_graph_steps - graph0
+    nodes = eng.graphs[next(b for b in eng.graph_sizes if b >= args.batch)].kernels if graph_steps else 0   # of the bucket the batch ran in
+    print("RESULT " + json.dumps({
+        "batch": args.batch, "prompt_len": args.prompt, "steps": args.steps, "graphs": bool(args.graphs),
+        "wall_ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": start.elapsed_time(end) / args.steps,
+        "graph_steps": graph_steps,
+        "kernels_per_step": nodes if graph_steps else (ops.launches - launches0) / args.steps,
+        "launch_calls_per_step": 1 if graph_steps else (ops.launches - launches0) / args.steps}))
 
 
 def cmd_make_model(args):
@@ -168,7 +221,16 @@ def main(argv=None):
     t.add_argument("--batch", type=int, default=32)
     t.add_argument("--workload", choices=["mixed", "fixed"], default="mixed")
     t.add_argument("--num-requests", type=int, default=256)
+    t.add_argument("--batches", type=int, nargs="+", default=None, help="several values of --batch, one run each")
     t.set_defaults(fn=cmd_throughput)
+
+    pd = sub.add_parser("profile-decode", help="steady-state decode at one batch size under NVTX ranges, for a profiler")
+    _model_args(pd)
+    pd.add_argument("--graphs", type=int, default=1)
+    pd.add_argument("--batch", type=int, default=32)
+    pd.add_argument("--prompt", type=int, default=512)
+    pd.add_argument("--steps", type=int, default=50)
+    pd.set_defaults(fn=cmd_profile_decode)
 
     m = sub.add_parser("make-model", help="write a model folder with random weights")
     m.add_argument("--preset", required=True)

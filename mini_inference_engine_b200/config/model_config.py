@@ -14,7 +14,6 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass, field, fields
-from typing import Any
 
 
 class ConfigError(ValueError):

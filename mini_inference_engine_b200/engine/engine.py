@@ -25,7 +25,7 @@ from ..sampling.sampler import Sampler
 from ..weights import read_model_folder
 from .runner import ModelRunner
 from .scheduler import Scheduler
-from .sequence import Sequence, Status
+from .sequence import Sequence
 
 ACTIVATION_RESERVE = 768 * 2 ** 20      # kept free for activations when sizing the cache (inference_engine/engine.py:51)
 

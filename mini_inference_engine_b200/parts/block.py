@@ -5,7 +5,7 @@ is fused into the *next* norm, so a block takes the pending ``delta`` and return
 add+norm, after the last layer into the final norm)."""
 from __future__ import annotations
 
-from .base import Part, ResidualSink, build_part, register_part
+from .base import Part, ResidualSink, register_part
 
 
 def _sink_for(producer, consumer, norm, res, num_tokens):

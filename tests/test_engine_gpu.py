@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_llama as pl
-from conftest import TINY, plain_weights
+from conftest import plain_weights
 from helpers import TOL
 
 pytestmark = pytest.mark.gpu
@@ -234,3 +234,29 @@ def test_long_prompts_in_portions_replayed_from_graphs(dtype_name, model_folders
     assert outs[4] == outs[0]
     for p, ids in zip(prompts, outs[4]):
         assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
+
+
+def test_command_line_in_process(model_folders, tmp_path, capsys):
+    """The command line's sub-commands on a tiny model: a written model folder loads, generation by
+    ids follows the plain implementation, and the latency and profile-decode loops report a step."""
+    import json
+
+    from mini_inference_engine_b200.__main__ import main
+    out = str(tmp_path / "made")
+    main(["make-model", "--preset", "tiny-llama-a", "--seed", "3", "--out", out])
+    capsys.readouterr()
+    main(["generate", "--model", out, "--prompt-ids", "1,5,17,3", "--prompt-ids", "9,8", "--max-tokens", "6", "--ignore-eos",
+          "--dtype", "float32"])
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert [l["prompt_len"] for l in lines] == [4, 2] and all(len(l["output_ids"]) == 6 for l in lines)
+    cfg, W = pl.read_config(out), plain_weights(out)
+    assert_tokens_follow_plain(cfg, W, pl.identity, [1, 5, 17, 3], lines[0]["output_ids"], torch.float32)
+    main(["latency", "--model", out, "--batches", "1", "3", "--prompt", "20", "--steps", "4"])
+    got = capsys.readouterr().out
+    assert "bs=  1" in got and "bs=  3" in got and "ms/token-step" in got
+    for graphs in ("1", "0"):
+        main(["profile-decode", "--model", out, "--graphs", graphs, "--batch", "3", "--prompt", "20", "--steps", "5"])
+        res = json.loads(next(l for l in capsys.readouterr().out.splitlines() if l.startswith("RESULT "))[7:])
+        assert res["graphs"] == (graphs == "1") and res["graph_steps"] == (5 if graphs == "1" else 0)
+        assert res["kernels_per_step"] > 10 and res["device_ms_per_step"] > 0
+        assert res["launch_calls_per_step"] == (1 if graphs == "1" else res["kernels_per_step"])

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_llama as pl
-from helpers import close, scattered_tables
+from helpers import close
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -220,7 +220,7 @@ def test_blocks_that_fold_their_norms_into_the_products():
 def test_run_order_is_data_a_layer_twice_and_a_shared_cache(tmp_path):
     """A model whose run order names layer 0 twice (own cache each time) and lets layer 1 read the
     cache that the first run of layer 0 wrote.  Whole sequence == portion + single tokens."""
-    from mini_inference_engine_b200.config import LlamaConfig, RunEntry, load_config
+    from mini_inference_engine_b200.config import RunEntry, load_config
     from mini_inference_engine_b200.engine.runner import ModelRunner
     from mini_inference_engine_b200.cache import RequestCache
     from mini_inference_engine_b200.models.decoder import DecoderModel, expected_tensors

@@ -10,7 +10,7 @@ import torch
 
 import plain_llama as pl
 from conftest import TINY, plain_weights
-from helpers import TOL, close, first_bad_row
+from helpers import close, first_bad_row
 from replay_driver import Replay
 
 pytestmark = pytest.mark.gpu

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 def register_toy():
     from mini_inference_engine_b200.config import LlamaConfig, register_architecture
-    from mini_inference_engine_b200.config.model_config import LayerSpec, PartSpec
+    from mini_inference_engine_b200.config.model_config import PartSpec
     from mini_inference_engine_b200.parts import Mixer, StateNeed, register_part
     from mini_inference_engine_b200.weights import TensorSpec
 
