@@ -243,19 +243,20 @@ def test_command_line_in_process(model_folders, tmp_path, capsys):
 
     from mini_inference_engine_b200.__main__ import main
     out = str(tmp_path / "made")
+    small = ["--overrides", '{"num_blocks": 64}']        # not the default cache of most of the device's memory
     main(["make-model", "--preset", "tiny-llama-a", "--seed", "3", "--out", out])
     capsys.readouterr()
     main(["generate", "--model", out, "--prompt-ids", "1,5,17,3", "--prompt-ids", "9,8", "--max-tokens", "6", "--ignore-eos",
-          "--dtype", "float32"])
+          "--dtype", "float32"] + small)
     lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
     assert [l["prompt_len"] for l in lines] == [4, 2] and all(len(l["output_ids"]) == 6 for l in lines)
     cfg, W = pl.read_config(out), plain_weights(out)
     assert_tokens_follow_plain(cfg, W, pl.identity, [1, 5, 17, 3], lines[0]["output_ids"], torch.float32)
-    main(["latency", "--model", out, "--batches", "1", "3", "--prompt", "20", "--steps", "4"])
+    main(["latency", "--model", out, "--batches", "1", "3", "--prompt", "20", "--steps", "4"] + small)
     got = capsys.readouterr().out
     assert "bs=  1" in got and "bs=  3" in got and "ms/token-step" in got
     for graphs in ("1", "0"):
-        main(["profile-decode", "--model", out, "--graphs", graphs, "--batch", "3", "--prompt", "20", "--steps", "5"])
+        main(["profile-decode", "--model", out, "--graphs", graphs, "--batch", "3", "--prompt", "20", "--steps", "5"] + small)
         res = json.loads(next(l for l in capsys.readouterr().out.splitlines() if l.startswith("RESULT "))[7:])
         assert res["graphs"] == (graphs == "1") and res["graph_steps"] == (5 if graphs == "1" else 0)
         assert res["kernels_per_step"] > 10 and res["device_ms_per_step"] > 0
