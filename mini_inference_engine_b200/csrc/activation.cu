@@ -18,13 +18,20 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
-// Eight outputs per thread with 16-byte loads and stores (bfloat16, inter % 8 == 0).
+// Eight outputs per thread with 16-byte loads and stores (bfloat16, inter % 8 == 0).  The result is
+// rounded to bfloat16, so the exponential and the division are the hardware approximations (two ulp
+// each in float32): with the library's the kernel issued instructions all the time and reached 0.6 of
+// the memory bandwidth on 2,048 tokens.  Token and place within it are counted along the grid-stride
+// loop instead of divided out of a 64-bit index every time.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int inter8,
                                      int interleaved) {
     pdl_enter();
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = idx / inter8;
-        const int i8 = (int)(idx - t * inter8);
+    const unsigned stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;   // the grid is capped: both fit
+    const unsigned stride_t = stride / (unsigned)inter8, stride_i = stride - stride_t * (unsigned)inter8;
+    int64_t t = first / (unsigned)inter8;
+    int i8 = (int)(first - (unsigned)t * (unsigned)inter8);
+    for (int64_t idx = first; idx < total8; idx += stride, t += stride_t, i8 += (int)stride_i) {
+        if (i8 >= inter8) { i8 -= inter8; ++t; }
         const bf16* row = gu + t * 16 * inter8;
         float g[8], u[8];
         if (interleaved) {
@@ -50,8 +57,8 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
         __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            ho[j] = __floats2bfloat162_rn(g[2 * j] / (1.0f + expf(-g[2 * j])) * u[2 * j],
-                                          g[2 * j + 1] / (1.0f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
+            ho[j] = __floats2bfloat162_rn(__fdividef(g[2 * j], 1.0f + __expf(-g[2 * j])) * u[2 * j],
+                                          __fdividef(g[2 * j + 1], 1.0f + __expf(-g[2 * j + 1])) * u[2 * j + 1]);
         *reinterpret_cast<uint4*>(out + idx * 8) = o;
     }
 }
