@@ -17,7 +17,8 @@ from . import gemm_tc, ops
 _bf16_backend = "auto"
 AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen05 kernel (whole decode step, B200:
                               # 24 tokens 1.057 ms against 1.098 ms with the library, 32 tokens 1.078 against 1.136 ms,
-                              # 48 tokens 1.61 against 1.18 ms: the 64-token tile re-reads the activations per block)
+                              # 48 tokens 1.61 against 1.18 ms: with the 64-token tile the partial rows' way to their
+                              # owners and the owners' sums take 25 us a layer instead of 8)
 
 
 def set_bf16_backend(name: str) -> None:
