@@ -161,3 +161,58 @@ def test_admission_waits_for_a_state_slot():
     sched.add(a), sched.add(b)
     assert sched.schedule() == [(a, 3)]
     assert list(sched.waiting) == [b]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_workloads_keep_the_invariants(seed):
+    """Random prompts and output lengths, arrivals spread over the run, pools from roomy to so tight
+    that requests are preempted: every step keeps the budget, runs a request at most once, puts the
+    decoded tokens first, covers what it runs with pages, and in the end everything ran to its length
+    and every page and slot is back."""
+    import random
+    rng = random.Random(seed)
+    budget = rng.choice([16, 40, 64, 256])
+    max_seqs = rng.choice([2, 4, 8])
+    chunked = seed % 4 != 3
+    longest = 20 if not chunked else 90            # without chunking a prompt must fit a budget whole
+    num_blocks = rng.choice([12, 16, 24, 64])
+    sched, cache = make(num_blocks, budget=budget, max_num_seqs=max_seqs, chunked=chunked, slots=max_seqs)
+    todo = []
+    for _ in range(rng.randrange(5, 14)):
+        p, o = rng.randrange(1, min(longest, budget if not chunked else longest) + 1), rng.randrange(1, 30)
+        if sched.can_ever_fit(p + o):
+            todo.append(Sequence(list(range(p)), SamplingParams(max_tokens=o, ignore_eos=True)))
+    assert todo
+    want = {id(s): (s.prompt_len, s.params.max_tokens) for s in todo}
+    pending, done, steps = list(todo), [], 0
+    while pending or sched.has_work():
+        steps += 1
+        assert steps < 20000, "the scheduler does not terminate"
+        while pending and rng.random() < 0.4:
+            sched.add(pending.pop(0))
+        if not sched.has_work():
+            sched.add(pending.pop(0))
+        batch = sched.schedule()
+        assert batch, "work is left but nothing was scheduled"
+        assert sum(n for _, n in batch) <= budget and all(n >= 1 for _, n in batch)
+        assert len({id(s) for s, _ in batch}) == len(batch)
+        kinds = [s.num_new_tokens == 1 for s, _ in batch]
+        assert kinds == sorted(kinds, reverse=True), "decoded tokens come first"
+        assert len(sched.running) <= max_seqs
+        for s, n in batch:
+            assert s.status is Status.RUNNING and n <= s.num_new_tokens
+            assert (chunked or n == s.num_new_tokens)
+            assert all(len(t) * 16 >= s.num_computed + n for t in s.cache.tables)
+            assert s.cache.state_slot != 0
+        for s in sched.waiting:
+            assert s.num_computed == 0 and s.cache.state_slot == 0 and s.cache.tables in ([], [[]])
+        before = set(id(s) for s in sched.running)
+        fake_step(sched, cache, batch)
+        cache.check()
+        done += [s for s, _ in batch if s.status is Status.FINISHED]
+        assert before >= set(id(s) for s in sched.running)
+    assert sorted(id(s) for s in done) == sorted(want)
+    for s in done:
+        assert (s.prompt_len, s.num_output_tokens) == want[id(s)]
+    assert cache.num_free() == cache.pools[0].num_usable
+    assert cache.state_pool.num_free == cache.state_pool.num_usable
