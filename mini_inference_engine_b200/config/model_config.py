@@ -30,12 +30,24 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (``block``) of a mixer, a feed-forward and their norms."""
+    """One layer: the registered arrangement ``block`` and the parts it is made of, by role name.
+    Which roles there are, and which category of part fills each (mixer, feed_forward, norm, ...), is
+    the block class's business (its ``roles``); Llama's ``prenorm_residual`` has ``mixer``,
+    ``feed_forward``, ``mixer_norm`` and ``feed_forward_norm``.  A role reads as an attribute too:
+    ``layer.mixer`` is ``layer.parts["mixer"]``."""
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: dict
+
+    def __getattr__(self, role):
+        parts = object.__getattribute__(self, "parts")
+        if role in parts:
+            return parts[role]
+        raise AttributeError(f"layer of block {object.__getattribute__(self, 'block')!r} has no part {role!r} "
+                             f"(it has {', '.join(sorted(parts))})")
+
+    def with_part(self, role: str, spec: PartSpec) -> "LayerSpec":
+        """A copy of this layer with one part exchanged (or added)."""
+        return LayerSpec(self.block, {**self.parts, role: spec})
 
 
 @dataclass(frozen=True)
@@ -60,6 +72,8 @@ class ModelSpec:
     head: PartSpec
     max_position: int
     eos_token_id: int
+    # checkpoint tensors that the model does not read and that are no error when present (fnmatch patterns)
+    ignore: tuple = ()
 
 
 _REQUIRED = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
@@ -92,6 +106,15 @@ class LlamaConfig:
         missing = [k for k in _REQUIRED if k not in c]
         if missing:
             raise ConfigError(f"config.json lacks required key(s): {', '.join(missing)}")
+        # Keys that change the arithmetic and that this model does not honour are refused; the reference
+        # does not read them (inference_engine/config.py:27-42) and would compute something else silently.
+        if c.get("rope_scaling") is not None:
+            raise ConfigError(f"rope_scaling {c['rope_scaling']!r} is not supported: the rotation uses "
+                              "theta^(-2j/d) unscaled (remove the key only if the checkpoint was trained without it)")
+        if c.get("hidden_act", "silu") != "silu":
+            raise ConfigError(f"hidden_act {c['hidden_act']!r} is not supported: the feed-forward is SwiGLU (silu)")
+        if c.get("mlp_bias"):
+            raise ConfigError("mlp_bias true is not supported: the feed-forward has no biases")
         heads = c["num_attention_heads"]
         eos = c.get("eos_token_id", 2)           # inference_engine/config.py:26,41
         if isinstance(eos, list):
@@ -151,8 +174,7 @@ class LlamaConfig:
         for i in range(self.num_hidden_layers):
             p = f"model.layers.{i}."
             norm = dict(size=self.hidden_size, eps=self.rms_norm_eps)
-            layers.append(LayerSpec(
-                block="prenorm_residual",
+            layers.append(LayerSpec("prenorm_residual", dict(
                 mixer=PartSpec("attention", dict(
                     hidden_size=self.hidden_size, num_heads=self.num_attention_heads,
                     num_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
@@ -166,7 +188,7 @@ class LlamaConfig:
                                       p + "mlp."),
                 mixer_norm=PartSpec("rmsnorm", norm, p + "input_layernorm."),
                 feed_forward_norm=PartSpec("rmsnorm", norm, p + "post_attention_layernorm."),
-            ))
+            )))
         head_prefix = "model.embed_tokens." if self.tie_word_embeddings else "lm_head."
         return ModelSpec(
             vocab_size=self.vocab_size,
@@ -180,6 +202,8 @@ class LlamaConfig:
                                               tied=self.tie_word_embeddings), head_prefix),
             max_position=self.max_position_embeddings,
             eos_token_id=self.eos_token_id,
+            # older checkpoints store the rotation's frequencies; a tied model may still carry a head
+            ignore=("*rotary_emb.inv_freq",) + (("lm_head.weight",) if self.tie_word_embeddings else ()),
         )
 
 

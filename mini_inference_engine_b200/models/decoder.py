@@ -20,14 +20,15 @@ from ..weights.loader import TensorSpec, check_and_bind
 
 
 def _layer_parts(layer_spec):
-    mixer = build_part("mixer", layer_spec.mixer)
-    ff = build_part("feed_forward", layer_spec.feed_forward)
-    n1 = build_part("norm", layer_spec.mixer_norm)
-    n2 = build_part("norm", layer_spec.feed_forward_norm)
-    block = part_class("block", layer_spec.block)(mixer, ff, n1, n2)
-    named = [(layer_spec.mixer.prefix, mixer), (layer_spec.feed_forward.prefix, ff),
-             (layer_spec.mixer_norm.prefix, n1), (layer_spec.feed_forward_norm.prefix, n2)]
-    return block, named
+    """Builds the parts a layer's block class asks for (its ``roles``: role name -> part category)
+    from the layer's description and hands them to the block by role name."""
+    cls = part_class("block", layer_spec.block)
+    roles = cls.roles
+    if set(roles) != set(layer_spec.parts):
+        raise ValueError(f"block {layer_spec.block!r} is made of {', '.join(sorted(roles))}; the layer describes "
+                         f"{', '.join(sorted(layer_spec.parts))}")
+    built = {role: build_part(roles[role], layer_spec.parts[role]) for role in roles}
+    return cls(**built), [(layer_spec.parts[role].prefix, built[role]) for role in roles]
 
 
 class _Skeleton:
@@ -67,15 +68,12 @@ def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
 
 
 class DecoderModel:
-    def __init__(self, spec: ModelSpec, state: dict, rt: Runtime, where: str = "checkpoint",
-                 ignore: tuple = ("*rotary_emb.inv_freq",)):
+    def __init__(self, spec: ModelSpec, state: dict, rt: Runtime, where: str = "checkpoint"):
         sk = _Skeleton(spec)
         self.spec = spec
         self.rt = rt
         tied = spec.head.prefix == spec.embedding.prefix
-        if tied:
-            ignore = tuple(ignore) + ("lm_head.weight",)
-        tensors = check_and_bind(state, sk.expected(), ignore=ignore, where=where)
+        tensors = check_and_bind(state, sk.expected(), ignore=tuple(spec.ignore), where=where)
         for prefix, part in sk.named:
             local = {n: tensors[prefix + n] for n in part.tensor_specs()}
             part.bind(local, rt)
@@ -94,7 +92,7 @@ class DecoderModel:
         self._takes_next = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]
         needs: dict = {}
         for e in self.run_order:                   # a cache's shape is what the layers that use it declare
-            need = self.blocks[e.layer].mixer.cache_need()
+            need = self.blocks[e.layer].cache_need()
             if e.cache in needs and needs[e.cache] != need:
                 raise ValueError(f"cache {e.cache} is used by layers with different needs: {needs[e.cache]} and {need}")
             needs[e.cache] = need
@@ -117,8 +115,7 @@ class DecoderModel:
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        for obj in [self.embedding, self.final_norm, self.head] + [p for b in self.blocks for p in
-                                                                  (b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm)]:
+        for obj in [self.embedding, self.final_norm, self.head] + [p for b in self.blocks for p in b.parts()]:
             for v in vars(obj).values():
                 if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                     seen.add(v.data_ptr())

@@ -11,18 +11,37 @@ from .base import Part, ResidualSink, register_part
 def _sink_for(producer, consumer, norm, res, num_tokens):
     """The offer to ``producer`` (None if it would not take one): it may add to the stream itself when
     the part behind ``norm`` can take that norm as a factor on its first product."""
-    if not getattr(producer, "takes_sink", False) or consumer is None:
+    if not getattr(producer, "takes_sink", False) or consumer is None or norm is None:
         return None
     ok = getattr(consumer, "defers_norm", None)
     return ResidualSink(res, norm) if ok is not None and ok(num_tokens) else None
 
 
-class PreNormResidual(Part):
-    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+class Block(Part):
+    """An arrangement of parts.  ``roles`` names the parts it is made of and the category each is
+    built from (role -> "mixer" | "feed_forward" | "norm" | ...); the model builds them from the
+    layer's description and passes them to the constructor by role name.  A block has one cache: what
+    ``cache_need()`` says (by default its ``mixer``'s need, nothing for a block without one)."""
+    roles: dict = {}
+
+    def __init__(self, **parts):
+        for role, part in parts.items():
+            setattr(self, role, part)
+        self._roles = tuple(parts)
+
+    def parts(self) -> list:
+        return [getattr(self, r) for r in self._roles]
+
+    def cache_need(self):
+        mixer = getattr(self, "mixer", None)
+        return mixer.cache_need() if mixer is not None else None
+
+    def forward(self, delta, res, ctx, cache):
+        raise NotImplementedError
+
+
+class PreNormResidual(Block):
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
     def forward(self, delta, res, ctx, cache, next_block=None):
         """``next_block``: the block that runs after this one, if it reads the stream through a norm

@@ -63,6 +63,63 @@ def test_model_spec_is_data_and_sizes_come_from_config():
     assert "lm_head.weight" in expected_tensors(load_config(dict(TINY["tiny_a"])).model_spec())
 
 
+@pytest.mark.parametrize("key,value,word", [
+    ("rope_scaling", {"rope_type": "llama3", "factor": 8.0}, "rope_scaling"),
+    ("rope_scaling", {"type": "linear", "factor": 2.0}, "rope_scaling"),
+    ("hidden_act", "gelu", "hidden_act"),
+    ("mlp_bias", True, "mlp_bias"),
+])
+def test_keys_that_change_the_arithmetic_and_are_not_honoured_are_refused(key, value, word):
+    """The reference reads none of these (inference_engine/config.py:27-42) and would compute something
+    else without a word; here such a config.json does not load."""
+    with pytest.raises(ConfigError, match=word):
+        load_config(dict(TINY["tiny_a"], **{key: value}))
+
+
+def test_the_same_keys_at_their_neutral_values_load():
+    cfg = load_config(dict(TINY["tiny_a"], rope_scaling=None, hidden_act="silu", mlp_bias=False))
+    assert cfg == load_config(dict(TINY["tiny_a"]))
+
+
+def test_what_a_checkpoint_may_hold_beside_the_model_is_named_by_the_spec():
+    tied = load_config(dict(TINY["tiny_b"])).model_spec()
+    untied = load_config(dict(TINY["tiny_a"])).model_spec()
+    assert "lm_head.weight" in tied.ignore and "lm_head.weight" not in untied.ignore
+    assert any("inv_freq" in pat for pat in untied.ignore)
+    import inspect
+    from mini_inference_engine_b200.models import decoder
+    src = inspect.getsource(decoder)
+    assert "inv_freq" not in src and "lm_head" not in src       # the generic model names no tensor of any architecture
+
+
+def test_a_layer_is_what_its_block_class_says_it_is_made_of():
+    """A block with other parts than Llama's (one norm, mixer and feed-forward side by side) is a new
+    registered class, not an edit of the framework: the layer's description is role -> part."""
+    from mini_inference_engine_b200.config import LayerSpec, PartSpec
+    from mini_inference_engine_b200.models.decoder import _layer_parts
+    from mini_inference_engine_b200.parts import register_part
+    from mini_inference_engine_b200.parts.block import Block
+
+    class SideBySide(Block):
+        roles = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    register_part("block", "toy_side_by_side_cpu", SideBySide)
+    h = 32
+    parts = dict(norm=PartSpec("rmsnorm", dict(size=h, eps=1e-5), "n."),
+                 mixer=PartSpec("attention", dict(hidden_size=h, num_heads=2, num_kv_heads=1, head_dim=16,
+                                                  position=PartSpec("none", dict(head_dim=16, max_position=8))), "a."),
+                 feed_forward=PartSpec("swiglu", dict(hidden_size=h, intermediate_size=48), "f."))
+    block, named = _layer_parts(LayerSpec("toy_side_by_side_cpu", parts))
+    assert [p for p, _ in named] == ["n.", "a.", "f."] and block.parts() == [part for _, part in named]
+    assert block.cache_need().num_kv_heads == 1 and block.cache_need().head_dim == 16
+    layer = LayerSpec("toy_side_by_side_cpu", parts)
+    assert layer.mixer is parts["mixer"] and layer.with_part("norm", parts["norm"]).parts == parts
+    with pytest.raises(AttributeError, match="mixer_norm"):
+        layer.mixer_norm
+    with pytest.raises(ValueError, match="is made of"):
+        _layer_parts(LayerSpec("prenorm_residual", parts))
+
+
 def test_engine_config_overrides():
     c = EngineConfig.from_overrides({"max_num_batched_tokens": 48, "num_blocks": 9})
     assert c.max_num_batched_tokens == 48 and c.num_blocks == 9 and c.block_size == 16

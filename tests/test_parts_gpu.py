@@ -127,11 +127,11 @@ def test_block_part(dt):
     rt = rt_for(dt)
     h, H, Hkv, D, I, T = 48, 3, 3, 16, 80, 19
     norm = dict(size=h, eps=1e-5)
-    ls = LayerSpec("prenorm_residual",
-                   PartSpec("attention", dict(hidden_size=h, num_heads=H, num_kv_heads=Hkv, head_dim=D,
-                                              position=PartSpec("rope", dict(head_dim=D, rotary_dim=D, theta=1e4, max_position=32))), "a."),
-                   PartSpec("swiglu", dict(hidden_size=h, intermediate_size=I), "f."),
-                   PartSpec("rmsnorm", norm, "n1."), PartSpec("rmsnorm", norm, "n2."))
+    ls = LayerSpec("prenorm_residual", dict(
+        mixer=PartSpec("attention", dict(hidden_size=h, num_heads=H, num_kv_heads=Hkv, head_dim=D,
+                                         position=PartSpec("rope", dict(head_dim=D, rotary_dim=D, theta=1e4, max_position=32))), "a."),
+        feed_forward=PartSpec("swiglu", dict(hidden_size=h, intermediate_size=I), "f."),
+        mixer_norm=PartSpec("rmsnorm", norm, "n1."), feed_forward_norm=PartSpec("rmsnorm", norm, "n2.")))
     block, named = _layer_parts(ls)
     W = {}
     for i, (prefix, part) in enumerate(named):
@@ -167,11 +167,11 @@ def test_blocks_that_fold_their_norms_into_the_products():
     norm = dict(size=h, eps=eps)
     blocks, Ws = [], []
     for b in range(2):
-        ls = LayerSpec("prenorm_residual",
-                       PartSpec("attention", dict(hidden_size=h, num_heads=H, num_kv_heads=Hkv, head_dim=D,
-                                                  position=PartSpec("rope", dict(head_dim=D, rotary_dim=D, theta=1e4, max_position=64))), "a."),
-                       PartSpec("swiglu", dict(hidden_size=h, intermediate_size=I), "f."),
-                       PartSpec("rmsnorm", norm, "n1."), PartSpec("rmsnorm", norm, "n2."))
+        ls = LayerSpec("prenorm_residual", dict(
+            mixer=PartSpec("attention", dict(hidden_size=h, num_heads=H, num_kv_heads=Hkv, head_dim=D,
+                                             position=PartSpec("rope", dict(head_dim=D, rotary_dim=D, theta=1e4, max_position=64))), "a."),
+            feed_forward=PartSpec("swiglu", dict(hidden_size=h, intermediate_size=I), "f."),
+            mixer_norm=PartSpec("rmsnorm", norm, "n1."), feed_forward_norm=PartSpec("rmsnorm", norm, "n2.")))
         block, named = _layer_parts(ls)
         W = {}
         for i, (prefix, part) in enumerate(named):

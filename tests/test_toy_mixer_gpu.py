@@ -54,7 +54,7 @@ def register_toy():
             spec = super().model_spec()
             layers = list(spec.layers)
             for i in range(1, len(layers), 2):
-                layers[i] = dataclasses.replace(layers[i], mixer=PartSpec(
+                layers[i] = layers[i].with_part("mixer", PartSpec(
                     "toy_ema", dict(hidden_size=self.hidden_size, state_size=24, decay=0.9), f"model.layers.{i}.ema."))
             return dataclasses.replace(spec, layers=tuple(layers))
 

@@ -108,14 +108,14 @@ def register_toys():
             spec = super().model_spec()
             layers = list(spec.layers)
             for i in (0, 2):
-                layers[i] = dataclasses.replace(layers[i], feed_forward=PartSpec(
+                layers[i] = layers[i].with_part("feed_forward", PartSpec(
                     "toy_routed_relu", dict(hidden_size=self.hidden_size, expert_size=EXPERT_SIZE, num_experts=EXPERTS),
                     f"model.layers.{i}.moe."))
             for i in (1, 2):
                 params = dict(layers[i].mixer.params)
                 params["position"] = PartSpec("toy_learned_shift", dict(
                     head_dim=self.head_dim, max_position=self.max_position_embeddings, gain=GAIN))
-                layers[i] = dataclasses.replace(layers[i], mixer=dataclasses.replace(layers[i].mixer, params=params))
+                layers[i] = layers[i].with_part("mixer", dataclasses.replace(layers[i].mixer, params=params))
             return dataclasses.replace(spec, layers=tuple(layers))
 
     global routed_parts, shift_parts
