@@ -47,31 +47,43 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML while the timed region runs (reads only)."""
+    """SM clocks and throttle reasons while the timed region runs, read by ``nvidia-smi`` in a process of
+    its own (a sampling thread in this process would take the interpreter away from the step loop that is
+    being timed).  Reads only; NVML in this process is the fallback where nvidia-smi is missing."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self):
-        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
-        self._thread = None
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._proc = self._log = self._thread = None
+        self._stop = threading.Event()
 
     def __enter__(self):
+        import subprocess
+        exe = shutil.which("nvidia-smi")
+        if exe:
+            try:
+                self._log = tempfile.NamedTemporaryFile("w+", prefix="mie_b200_clocks_", suffix=".csv", delete=False)
+                self._proc = subprocess.Popen([exe, "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                               "-lms", "100"], stdout=self._log, stderr=subprocess.DEVNULL)
+                return self
+            except OSError:
+                self._proc = None
         try:
             import pynvml
             pynvml.nvmlInit()
             h = pynvml.nvmlDeviceGetHandleByIndex(0)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
-            names = {getattr(pynvml, n): n[len("nvmlClocksThrottleReason"):] for n in dir(pynvml)
-                     if n.startswith("nvmlClocksThrottleReason") and n not in
-                     ("nvmlClocksThrottleReasonNone", "nvmlClocksThrottleReasonAll", "nvmlClocksThrottleReasonGpuIdle")}
 
             def run():
                 while not self._stop.is_set():
                     try:
                         self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
-                        r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                        self.reasons.update(n for bit, n in names.items() if bit and r & bit)
                     except Exception:      # noqa: BLE001 - sampling must never end the run
                         pass
-                    time.sleep(0.05)
+                    time.sleep(0.25)
 
             self._thread = threading.Thread(target=run, daemon=True)
             self._thread.start()
@@ -83,10 +95,32 @@ class ClockSampler:
         self._stop.set()
         if self._thread:
             self._thread.join(timeout=2)
+        if self._proc is not None:
+            time.sleep(0.12)               # let a last sample land
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:              # noqa: BLE001
+                self._proc.kill()
+            self._log.flush()
+            self._log.seek(0)
+            for line in self._log.read().splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) != 2 + len(self.REASONS) or not f[0].isdigit():
+                    continue
+                self.samples.append(int(f[0]))
+                if f[1].isdigit():
+                    self.max_mhz = int(f[1])
+                self.reasons.update(n for n, v in zip(self.REASONS, f[2:]) if v == "Active")
+            self._log.close()
+            try:
+                os.unlink(self._log.name)
+            except OSError:
+                pass
 
     def summary(self):
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons)}
+                "samples": len(self.samples), "reasons": sorted(self.reasons)}
 
 
 def prompts_for(batch, length, vocab):

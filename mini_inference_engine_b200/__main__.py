@@ -6,6 +6,7 @@ benchmarks/profile_decode.py (``--graphs --batch --prompt --steps``) keep their 
     python -m mini_inference_engine_b200 generate   --model DIR --prompt-ids 1,2,3 --max-tokens 16
     python -m mini_inference_engine_b200 latency    --preset tinyllama-1.1b --batches 1 8 64 --prompt 512 --steps 100
     python -m mini_inference_engine_b200 throughput --preset tinyllama-1.1b --batch 32 --workload mixed
+    python -m mini_inference_engine_b200 throughput --preset llama-3-8b --workload long
     python -m mini_inference_engine_b200 profile-decode --preset tinyllama-1.1b --graphs 1 --batch 32 --steps 50
     python -m mini_inference_engine_b200 make-model --preset tiny-llama-a --seed 0 --out DIR
 
@@ -98,12 +99,20 @@ def cmd_latency(args):
         print(f"bs={b:3d}  {ms:7.3f} ms/token-step  ({b / ms * 1e3:9.1f} tok/s)", flush=True)
 
 
+LONG_WORKLOAD = dict(num_requests=64, batch=64, max_model_len=8192, max_num_batched_tokens=2048)
+
+
 def make_workload(kind: str, n: int, seed: int, vocab: int):
-    """benchmarks/bench_throughput.py:34-44: mixed = prompt U[128,512], output U[64,512]; fixed = 256/256."""
+    """benchmarks/bench_throughput.py:34-44: mixed = prompt U[128,512], output U[64,512]; fixed = 256/256.
+    ``long`` is not the reference's: prompts U[512,4096] with 256 generated tokens each, so that prompts go
+    in several portions of the token budget beside the decoding requests."""
     rng = random.Random(seed)
     reqs = []
     for _ in range(n):
-        p, o = (rng.randint(128, 512), rng.randint(64, 512)) if kind == "mixed" else (256, 256)
+        if kind == "long":
+            p, o = rng.randint(512, 4096), 256
+        else:
+            p, o = (rng.randint(128, 512), rng.randint(64, 512)) if kind == "mixed" else (256, 256)
         reqs.append(([1 % vocab] + [rng.randint(min(100, vocab - 1), vocab - 1) for _ in range(p - 1)], o))
     return reqs
 
@@ -113,6 +122,11 @@ def cmd_throughput(args):
 
     import torch
 
+    long = args.workload == "long"
+    if args.batch is None:
+        args.batch = LONG_WORKLOAD["batch"] if long else 32
+    if args.num_requests is None:
+        args.num_requests = LONG_WORKLOAD["num_requests"] if long else 256
     if args.batches:                       # several concurrency caps, one engine after the other
         for bs in args.batches:
             one = argparse.Namespace(**{**vars(args), "batch": bs, "batches": None})
@@ -121,10 +135,19 @@ def cmd_throughput(args):
             torch.cuda.empty_cache()
         return
     from . import SamplingParams
-    eng = _engine(args, max_num_seqs=args.batch)
+    forced = dict(max_num_seqs=args.batch)
+    if args.workload == "long":            # contexts of up to 4,352 positions: the model's limit permitting
+        ov = json.loads(args.overrides) if args.overrides else {}
+        forced.update({k: LONG_WORKLOAD[k] for k in ("max_model_len", "max_num_batched_tokens") if k not in ov})
+    eng = _engine(args, **forced)
     reqs = make_workload(args.workload, args.num_requests, 0, eng.vocab_size)
+    too_long = [len(i) + o for i, o in reqs if len(i) + o > eng.cfg.max_model_len]
+    if too_long:
+        raise SystemExit(f"the workload needs {max(too_long)} positions; this model and these overrides allow "
+                         f"{eng.cfg.max_model_len}")
     eng.generate([ids for ids, _ in reqs[:4]], SamplingParams(max_tokens=16, ignore_eos=True))
-    eng.num_steps = eng.num_graph_steps = 0
+    eng.num_steps = eng.num_graph_steps = eng.num_portion_graph_steps = 0
+    eng.scheduler.num_preemptions = 0
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = eng.generate([ids for ids, _ in reqs], [SamplingParams(max_tokens=o, ignore_eos=True) for _, o in reqs])
@@ -135,6 +158,8 @@ def cmd_throughput(args):
     print("RESULT " + json.dumps({
         "system": "engine", "batch": args.batch, "workload": args.workload, "num_requests": len(reqs),
         "seconds": secs, "steps": eng.num_steps, "graph_steps": eng.num_graph_steps,
+        "portion_graph_steps": eng.num_portion_graph_steps,
+        "eager_steps": eng.num_steps - eng.num_graph_steps - eng.num_portion_graph_steps,
         "preemptions": eng.scheduler.num_preemptions,
         "kv_cache_tokens": eng.cache.pools[0].num_pages * eng.cfg.block_size,
         "output_tokens": out_tokens, "prompt_tokens": in_tokens, "output_tok_per_s": out_tokens / secs,
@@ -218,9 +243,9 @@ def main(argv=None):
 
     t = sub.add_parser("throughput", help="offline throughput on the reference's synthetic workloads")
     _model_args(t)
-    t.add_argument("--batch", type=int, default=32)
-    t.add_argument("--workload", choices=["mixed", "fixed"], default="mixed")
-    t.add_argument("--num-requests", type=int, default=256)
+    t.add_argument("--batch", type=int, default=None, help="most requests running at once (32; 64 for --workload long)")
+    t.add_argument("--workload", choices=["mixed", "fixed", "long"], default="mixed")
+    t.add_argument("--num-requests", type=int, default=None, help="256; 64 for --workload long")
     t.add_argument("--batches", type=int, nargs="+", default=None, help="several values of --batch, one run each")
     t.set_defaults(fn=cmd_throughput)
 

@@ -71,12 +71,12 @@ extern "C" int mie_swiglu(const void* gu, void* out, int act_tag, int num_tokens
     const int threads = 256;
     if (act_tag == MIE_BF16 && inter % 8 == 0 && (reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
         int64_t blocks8 = (total / 8 + threads - 1) / threads;
-        if (blocks8 > 148 * 16) blocks8 = 148 * 16;
+        if (blocks8 > device_sm_count() * 16) blocks8 = device_sm_count() * 16;
         return launch_kernel(swiglu_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out,
                              total / 8, inter / 8, interleaved);
     }
     int64_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (act_tag == MIE_F32)
         return launch_kernel(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inter, interleaved);
     else if (act_tag == MIE_BF16)

@@ -4,6 +4,7 @@
 #pragma once
 #include "mma_common.cuh"
 #include "tcgen05_common.cuh"      // mbarrier, TMA copies, bounded waits, the tensor-map encoder
+#include "range_check.cuh"
 
 #define DEC_WARPS 4
 #define DEC_TILE 64
@@ -23,6 +24,8 @@ struct DecodeParams {
     float scale_log2e;
     int* error;              // host-visible error word (TMA path: a bounded wait that ran out)
     uint32_t recv_offset;    // where the cluster merge's receive slots start in dynamic shared memory
+    int64_t check_pages;     // pages in each cache, for the range check of block-table entries (0: unchecked)
+    int* report;             // range report (range_check.cuh); null: nowhere
 };
 
 // Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
@@ -128,7 +131,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int* table = p.block_tables + (int64_t)row * p.table_stride;
     const int first_page = kbeg >> p.page_shift;
     const int n_pages = ntiles > 0 ? ((kend - 1) >> p.page_shift) - first_page + 1 : 0;
-    for (int i = threadIdx.x; i < min(n_pages, DEC_PAGE_SLOTS); i += DEC_WARPS * 32) s_pages[i] = table[first_page + i];
+    const int64_t page_limit = p.check_pages > 0 ? p.check_pages : ((int64_t)1 << 40);
+    for (int i = threadIdx.x; i < min(n_pages, DEC_PAGE_SLOTS); i += DEC_WARPS * 32)
+        s_pages[i] = checked_page(table[first_page + i], page_limit, p.report, MIE_K_ATTENTION_DECODE, first_page + i);
     __syncthreads();
     constexpr int CHUNKS_PER_ROW = D / 8;                          // 16-byte pieces per key
     const int rows_per_copy = min(p.page_size, DEC_TILE);          // TMA: one copy = one page (or a 64-row piece of it)
@@ -142,7 +147,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (lane < copies) {
                     const int key = k0 + lane * rows_per_copy;
                     const int pi = (key >> p.page_shift) - first_page;
-                    const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                    const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : checked_page(table[first_page + pi], page_limit, p.report, MIE_K_ATTENTION_DECODE, first_page + pi);
                     const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
                     unsigned char* kd = tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES + (size_t)lane * rows_per_copy * 128;
 #pragma unroll
@@ -161,7 +166,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int key = k0 + r;
             if (key < kend) {
                 const int pi = (key >> p.page_shift) - first_page;
-                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : checked_page(table[first_page + pi], page_limit, p.report, MIE_K_ATTENTION_DECODE, first_page + pi);
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1))) * D + c;
                 cp_async16(kd + r * DP + c, p.k_cache + src);
                 cp_async16(vd + r * DP + c, p.v_cache + src);
@@ -210,7 +215,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 const int which = threadIdx.x / CHUNKS_PER_ROW, c = (threadIdx.x - which * CHUNKS_PER_ROW) * 8;
                 const int r = newest - (kbeg + t * DEC_TILE);
                 const int pi = (newest >> p.page_shift) - first_page;
-                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : checked_page(table[first_page + pi], page_limit, p.report, MIE_K_ATTENTION_DECODE, first_page + pi);
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (newest & (p.page_size - 1))) * D + c;
                 const uint4 v = __ldcg(reinterpret_cast<const uint4*>((which ? p.v_cache : p.k_cache) + src));
                 if (TMA) *reinterpret_cast<uint4*>(tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES + which * KV_TILE_BYTES + swz_tile_off(r, c / 8)) = v;
@@ -497,7 +502,8 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                    int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
-                                   cudaStream_t stream, int stages = 0, int64_t num_pages = 0) {
+                                   cudaStream_t stream, int stages = 0, int64_t num_pages = 0,
+                                   int64_t check_pages = 0, int* report = nullptr) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -520,6 +526,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;
+    p.check_pages = check_pages; p.report = report;
     // TMA copies (see the kernel): head sizes 64 and 128, pages of 8 positions or more, a caller that says
     // how many pages the caches hold (num_pages; the entry point that must not allocate passes 0)
     DecodeMaps maps;

@@ -25,6 +25,12 @@
  *    race on it: serialise them, e.g. by issuing them on one stream.  The counters are cleared on
  *    the stream at the start of every call, so a call does not depend on what the last one left.
  *  - No cudaMalloc, cudaFree or allocating library routine is called.
+ *  - The kernel is launched with the programmatic-stream-serialization attribute, like every kernel
+ *    of this library, and reads the lengths, the block tables and every cached row except the newest
+ *    (position ctx - 1 of a row) BEFORE it waits for the kernel in front of it on the stream.  So the
+ *    kernel directly in front may write only that newest position of each row's cache (and q); a
+ *    caller whose preceding kernel writes older positions, the tables or the lengths must put a stream
+ *    synchronisation, an event or any ordinary launch between the two, or set MIE_B200_PDL=0.
  */
 #pragma once
 #include <cuda_runtime.h>

@@ -13,6 +13,7 @@
 //   S = Q K^T for the warp's 16 rows x 64 keys, masked by position (j <= p, j > p - window),
 //   online softmax in base 2 with float32 max / sum, P rounded to bfloat16, O += P V.
 #include "mma_common.cuh"
+#include "range_check.cuh"
 
 #define PRE_WARPS 4
 #define PRE_BM 64
@@ -28,6 +29,8 @@ struct PrefillParams {
     bf16* out;
     int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
     float scale_log2e;
+    int64_t check_pages;     // pages in each cache, for the range check of block-table entries
+    int* report;             // range report (range_check.cuh)
 };
 
 template <int D>
@@ -96,7 +99,8 @@ prefill_attention_kernel(const PrefillParams p) {
     const int* table = p.block_tables + (int64_t)row * p.table_stride;
     const int first_page = kbeg >> p.page_shift;
     const int n_pages = ((k_hi - 1) >> p.page_shift) - first_page + 1;
-    for (int i = threadIdx.x; i < min(n_pages, PRE_PAGE_SLOTS); i += PRE_WARPS * 32) s_pages[i] = table[first_page + i];
+    for (int i = threadIdx.x; i < min(n_pages, PRE_PAGE_SLOTS); i += PRE_WARPS * 32)
+        s_pages[i] = checked_page(table[first_page + i], p.check_pages, p.report, MIE_K_ATTENTION_PREFILL, first_page + i);
     __syncthreads();
     constexpr int CHUNKS_PER_ROW = D / 8;
     auto load_tile = [&](int t, int stage) {
@@ -108,7 +112,7 @@ prefill_attention_kernel(const PrefillParams p) {
             const int key = k0 + r;
             if (key >= k_lo && key < k_hi) {
                 const int pi = (key >> p.page_shift) - first_page;
-                const int page = pi < PRE_PAGE_SLOTS ? s_pages[pi] : table[first_page + pi];
+                const int page = pi < PRE_PAGE_SLOTS ? s_pages[pi] : checked_page(table[first_page + pi], p.check_pages, p.report, MIE_K_ATTENTION_PREFILL, first_page + pi);
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1))) * D + c;
                 cp_async16(kd + r * DP + c, p.k_cache + src);
                 cp_async16(vd + r * DP + c, p.v_cache + src);
@@ -240,7 +244,7 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
                                      const int* block_tables, int table_stride, const int* row_q_start,
                                      const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens,
                                      void* out, int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                     float scale, int window, int min_q_len, cudaStream_t stream) {
+                                     float scale, int window, int min_q_len, long long num_pages, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (head_dim < 16 || head_dim > PRE_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return MIE_ERR_BAD_ARG;
@@ -256,6 +260,7 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.min_q_len = min_q_len;
     p.scale_log2e = scale * 1.4426950408889634f;
+    p.check_pages = num_pages > 0 ? (int64_t)num_pages : ((int64_t)1 << 40); p.report = g_range_report;
     switch (head_dim) {
         case 16: return launch_prefill<16>(p, num_tokens, stream);
         case 32: return launch_prefill<32>(p, num_tokens, stream);

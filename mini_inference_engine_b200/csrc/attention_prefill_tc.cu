@@ -33,6 +33,7 @@
 #include <type_traits>
 
 #include "tcgen05_common.cuh"
+#include "range_check.cuh"
 
 #define FA_BM 128
 #define FA_BN 128
@@ -46,6 +47,8 @@ struct FaParams {
     int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
     int pair;                // 1: a block takes two query tiles of a row (see the kernel), 0: one
     float scale_log2e;
+    int64_t check_pages;     // pages in each cache, for the range check of block-table entries
+    int* report;             // range report (range_check.cuh)
 };
 
 // MN-major B operand tile with the 128-byte swizzle: 64 elements of N contiguous in a 128-byte row,
@@ -209,7 +212,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
             };
             auto page_of = [&](int g) {                           // lane's page id in key tile g (0 if it has no copy there)
                 if (g >= G || lane >= copies_of(g)) return 0;
-                return table[(key0_of(g) + lane * rows_per_copy) >> p.page_shift];
+                const int entry = (key0_of(g) + lane * rows_per_copy) >> p.page_shift;
+                return checked_page(table[entry], p.check_pages, p.report, MIE_K_ATTENTION_PREFILL_TC, entry);
             };
             int page_next = page_of(0);
             for (int g = 0; g < G; ++g) {
@@ -483,7 +487,7 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     // pairs) once the tiles of all heads are more than the GPU runs at a time
     const int tiles = (num_tokens + FA_BM - 1) / FA_BM + p.num_rows;
     FaParams pp = p;
-    pp.pair = (int64_t)tiles * p.num_heads > 148 * (D == 64 ? 2 : 1);
+    pp.pair = (int64_t)tiles * p.num_heads > (int64_t)device_sm_count() * (D == 64 ? 2 : 1);
     const dim3 grid(pp.pair ? (tiles + p.num_rows + 1) / 2 : tiles, p.num_heads);
     return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, pp);
 }
@@ -514,6 +518,7 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.min_q_len = min_q_len; p.pair = 0;
     p.scale_log2e = scale * 1.4426950408889634f;
+    p.check_pages = num_pages; p.report = g_range_report;
     CUtensorMap mq, mk, mv;
     const int box_rows = page_size < FA_BN ? page_size : FA_BN;
     const uint64_t cache_rows = (uint64_t)num_pages * num_kv_heads * page_size;

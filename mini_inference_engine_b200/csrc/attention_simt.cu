@@ -17,6 +17,7 @@
 // tile staged in shared memory is used by up to 8 pairs.  Within a warp, lane j scores key j of
 // the tile, then each lane owns output dimensions lane, lane+32, ...
 #include "common.cuh"
+#include "range_check.cuh"
 
 #define ATT_WARPS 8
 #define ATT_KEYS 32
@@ -51,7 +52,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
                        const int* __restrict__ row_q_len, const int* __restrict__ row_ctx_len,
                        int num_rows, T* __restrict__ out, int num_heads, int num_kv_heads,
                        int head_dim, int page_size, int page_shift, float scale, int window,
-                       int QT, int HG, int min_q_len) {
+                       int QT, int HG, int min_q_len, int64_t num_pages, int* report) {
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_row, s_q0;
     const int D = head_dim, DP = head_dim + 4;
@@ -77,6 +78,10 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     if (r < 0) return;
     const int q0 = s_q0;
     const int q_len = row_q_len[r], ctx_len = row_ctx_len[r], q_start = row_q_start[r];
+    if (ctx_len > table_stride * page_size) {      // more positions than the row's block table covers: reported, row left alone
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_POSITION, MIE_K_ATTENTION_SIMT, r, ctx_len);
+        return;
+    }
     const int G = num_heads / num_kv_heads;
     const int chunks = (G + HG - 1) / HG;
     const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
@@ -112,7 +117,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
             const int key = k0 + jj;
             float kf[Vec<T>::N], vf[Vec<T>::N];
             if (key >= k_lo && key < k_hi) {
-                const int page = table[key >> page_shift];
+                const int page = checked_page(table[key >> page_shift], num_pages, report, MIE_K_ATTENTION_SIMT, key >> page_shift);
                 const int off = key & (page_size - 1);
                 const int64_t src = (((int64_t)page * num_kv_heads + kvh) * page_size + off) * D + c;
                 Vec<T>::load(k_cache + src, kf);
@@ -179,7 +184,7 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows,
                                    int num_tokens, void* out, int act_tag, int num_heads, int num_kv_heads,
                                    int head_dim, int page_size, float scale, int window, int min_q_len,
-                                   cudaStream_t stream) {
+                                   long long num_pages, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (head_dim < 16 || head_dim > ATT_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -199,14 +204,14 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
         return launch_kernel(paged_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG, min_q_len);
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
     } else if (act_tag == MIE_BF16) {
         e = cudaFuncSetAttribute(paged_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         return launch_kernel(paged_attention_kernel<bf16>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (bf16*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG, min_q_len);
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
     }
     return MIE_ERR_BAD_ARG;
 }

@@ -61,12 +61,28 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Streaming multiprocessors of the current device, asked once per device.
+static inline int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // Programmatic dependent launch.  Every kernel of this package starts with pdl_enter(): it lets the
 // next kernel in the stream be scheduled at once (its blocks become resident and run their own
 // prologue) and then waits until the kernels before it have completed and their writes are visible.
 // What is gained is the launch gap between dependent kernels; what keeps it correct is that no
-// kernel reads or writes global memory before its wait, and that every block of every kernel
-// waits, so "the kernel before me is complete" carries over the whole chain.  Launched without the
+// kernel writes global memory, or reads anything that a kernel of the same step writes, before its
+// wait, and that every block of every kernel waits, so "the kernel before me is complete" carries
+// over the whole chain.  Three kernels do read before their wait, and only what is older than the
+// step: the tcgen05 product its weights (and, with the rotation epilogue, positions, slots and the
+// cos/sin rows), decode attention the lengths, block tables and every cached row but the newest.  Launched without the
 // attribute (MIE_B200_PDL=0), both instructions do nothing.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

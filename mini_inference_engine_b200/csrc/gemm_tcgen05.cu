@@ -56,6 +56,7 @@
 // host-visible memory, stops issuing work, lets copies in flight land, still takes part in the
 // cluster's barriers, frees its TMEM and returns.
 #include "tcgen05_common.cuh"
+#include "range_check.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
@@ -80,6 +81,8 @@ struct TcParams {
     const float* cos_t; const float* sin_t;          // [max_pos, rotary_dim / 2]
     bf16* k_cache; bf16* v_cache;                    // [pages, kv_heads, page_size, head_dim]
     int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, page_shift, max_pos, write_cache;
+    int64_t num_pages;                               // pages in each cache, for the range check of the slots
+    int* report;                                     // range report (range_check.cuh)
     uint32_t rope_smem_offset;                       // where the rotation's tables start inside dynamic shared memory
     uint32_t recv_smem_offset;                       // with `push`: where the slots for the peers' partial rows start
     int push;                                        // split-K by sending partial rows to their owners (SWAPPED, when the slots fit)
@@ -257,9 +260,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             const int half = p.rotary_dim >> 1, et = threadIdx.x - 64;
             for (int i = et; i < BN; i += 128) {
                 const int t = b0 + i;
-                int pos = t < p.M ? p.positions[t] : 0;
-                rope_pos[i] = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
-                rope_slot[i] = t < p.M ? p.slots[t] : 0;
+                // a position or slot out of range is reported; its token is rotated by row 0 and not stored
+                int pos = t < p.M ? p.positions[t] : 0, slot = t < p.M ? p.slots[t] : 0;
+                if (range_position(pos, p.max_pos) != MIE_RANGE_OK) {
+                    range_report(p.report, MIE_RANGE_POSITION, MIE_K_GEMM_QKV_ROPE, t, pos);
+                    pos = 0; slot = -1;
+                } else if (p.write_cache && range_slot(slot, p.num_pages, p.page_size) != MIE_RANGE_OK) {
+                    range_report(p.report, MIE_RANGE_SLOT, MIE_K_GEMM_QKV_ROPE, t, slot);
+                    slot = -1;
+                }
+                rope_pos[i] = pos;
+                rope_slot[i] = slot;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
             // 128 / BN threads share a token's row of angles (no division by the run-time half in the loop)
@@ -491,6 +502,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                                 store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                             } else if (p.write_cache) {
                                 const int slot = rope_slot[c + j];
+                                if (slot < 0) continue;                 // out of range: reported when it was fetched
                                 const int page = slot >> p.page_shift, off = slot & (p.page_size - 1);
                                 const bool is_k = hd < p.num_heads + p.num_kv_heads;
                                 const int kvh = hd - p.num_heads - (is_k ? 0 : p.num_kv_heads);
@@ -664,6 +676,7 @@ static int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, con
 struct RopeFuseArgs {
     const int* positions; const int* slots; const float* cos_t; const float* sin_t; void* k_cache; void* v_cache;
     int num_heads, num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache;
+    long long num_pages;
 };
 
 // The residual epilogue and the deferred norm factor (see the header comment); null pointers switch a
@@ -721,6 +734,8 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
         p.page_shift = 0;
         while ((1 << p.page_shift) < rope->page_size) ++p.page_shift;
         p.write_cache = rope->write_cache;
+        p.num_pages = rope->num_pages > 0 ? (int64_t)rope->num_pages : ((int64_t)1 << 40);
+        p.report = g_range_report;
     }
     p.k_tiles = (K + TC_BK - 1) / TC_BK;
     while (splits > 1 && splits > p.k_tiles) splits >>= 1;
@@ -758,9 +773,9 @@ extern "C" int mie_gemm_tc_qkv_rope(const void* x, const void* w, const void* bi
                                     int bn, int splits, int stages, int pdl, const int* positions, const int* slots,
                                     const float* cos_t, const float* sin_t, void* k_cache, void* v_cache, int num_heads,
                                     int num_kv_heads, int head_dim, int rotary_dim, int page_size, int max_pos,
-                                    int write_cache, cudaStream_t stream) {
+                                    int write_cache, long long num_pages, cudaStream_t stream) {
     RopeFuseArgs r = {positions, slots, cos_t, sin_t, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim,
-                      page_size, max_pos, write_cache};
+                      page_size, max_pos, write_cache, num_pages};
     return gemm_tc_launch(x, w, bias, bias_tag, y, MIE_BF16, M, N, K, 1, bn, splits, stages, 0, pdl, &r, stream);
 }
 
@@ -771,9 +786,9 @@ extern "C" int mie_gemm_tc_fused(const void* x, const void* w, const void* bias,
                                  int K, int bn, int splits, int stages, int swiglu, int pdl, const TcFuse* fuse,
                                  const int* positions, const int* slots, const float* cos_t, const float* sin_t,
                                  void* k_cache, void* v_cache, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
-                                 int page_size, int max_pos, int write_cache, cudaStream_t stream) {
+                                 int page_size, int max_pos, int write_cache, long long num_pages, cudaStream_t stream) {
     RopeFuseArgs r = {positions, slots, cos_t, sin_t, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim,
-                      page_size, max_pos, write_cache};
+                      page_size, max_pos, write_cache, num_pages};
     return gemm_tc_launch(x, w, bias, bias_tag, y, y_tag, M, N, K, 1, bn, splits, stages, swiglu, pdl, positions ? &r : nullptr,
                           stream, fuse);
 }

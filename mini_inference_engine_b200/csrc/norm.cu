@@ -9,16 +9,22 @@
 // `rows` (optional) gathers: output row b is computed from input row rows[b] and the residual
 // is left untouched -- the row selection before the final norm (inference_engine/model.py:182-184).
 #include "common.cuh"
+#include "range_check.cuh"
 
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ res,
                                    const void* __restrict__ w, int w_tag, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int n, float eps, int use_smem) {
+                                   const int* __restrict__ rows, int n, float eps, int use_smem,
+                                   int num_in_rows, int* report) {
     extern __shared__ float row_cache[];
     __shared__ float red[33];
     pdl_enter();
     const int b = blockIdx.x;
     const int64_t r = rows ? rows[b] : b;
+    if (rows && range_row(r, num_in_rows) != MIE_RANGE_OK) {      // a gathered row that does not exist: reported, not read
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_ROW, MIE_K_NORM, b, (int)r);
+        return;
+    }
     float* res_row = res + r * n;
     const TD* d_row = delta ? delta + r * n : nullptr;
     float ss = 0.f;
@@ -44,11 +50,16 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restri
 // 8 x 1024 x 8 elements), float32 residual read and written as float4 pairs.
 template <int PER_THREAD>
 __global__ void add_rmsnorm_bf16x8_kernel(const bf16* __restrict__ delta, float* __restrict__ res, const void* __restrict__ w,
-                                          int w_tag, bf16* __restrict__ out, const int* __restrict__ rows, int n, float eps) {
+                                          int w_tag, bf16* __restrict__ out, const int* __restrict__ rows, int n, float eps,
+                                          int num_in_rows, int* report) {
     __shared__ float red[33];
     pdl_enter();
     const int b = blockIdx.x;
     const int64_t r = rows ? rows[b] : b;
+    if (rows && range_row(r, num_in_rows) != MIE_RANGE_OK) {
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_ROW, MIE_K_NORM, b, (int)r);
+        return;
+    }
     float* res_row = res + r * n;
     const bf16* d_row = delta ? delta + r * n : nullptr;
     float v[PER_THREAD][8];
@@ -96,7 +107,7 @@ __global__ void add_rmsnorm_bf16x8_kernel(const bf16* __restrict__ delta, float*
 // residual already holds the embedding).
 extern "C" int mie_add_rmsnorm(const void* delta, float* res, const void* w, int w_tag, void* out,
                                int act_tag, const int* rows, int num_rows, int n, float eps,
-                               cudaStream_t stream) {
+                               int num_in_rows, cudaStream_t stream) {
     if (num_rows <= 0) return 0;
     if (n <= 0) return MIE_ERR_BAD_ARG;
     const bool aligned = ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(out)) % 16) == 0;
@@ -107,16 +118,16 @@ extern "C" int mie_add_rmsnorm(const void* delta, float* res, const void* w, int
         const int per = (n8 + threads - 1) / threads;
         if (per <= 1)
             return launch_kernel(add_rmsnorm_bf16x8_kernel<1>, dim3(num_rows), dim3(threads), 0, stream, (const bf16*)delta, res, w,
-                                 w_tag, (bf16*)out, rows, n, eps);
+                                 w_tag, (bf16*)out, rows, n, eps, num_in_rows, g_range_report);
         if (per <= 2)
             return launch_kernel(add_rmsnorm_bf16x8_kernel<2>, dim3(num_rows), dim3(threads), 0, stream, (const bf16*)delta, res, w,
-                                 w_tag, (bf16*)out, rows, n, eps);
+                                 w_tag, (bf16*)out, rows, n, eps, num_in_rows, g_range_report);
         if (per <= 4)
             return launch_kernel(add_rmsnorm_bf16x8_kernel<4>, dim3(num_rows), dim3(threads), 0, stream, (const bf16*)delta, res, w,
-                                 w_tag, (bf16*)out, rows, n, eps);
+                                 w_tag, (bf16*)out, rows, n, eps, num_in_rows, g_range_report);
         if (per <= 16)
             return launch_kernel(add_rmsnorm_bf16x8_kernel<16>, dim3(num_rows), dim3(threads), 0, stream, (const bf16*)delta, res, w,
-                                 w_tag, (bf16*)out, rows, n, eps);
+                                 w_tag, (bf16*)out, rows, n, eps, num_in_rows, g_range_report);
     }
     int threads = 32;
     while (threads < 1024 && threads * 4 < n) threads <<= 1;
@@ -125,9 +136,9 @@ extern "C" int mie_add_rmsnorm(const void* delta, float* res, const void* w, int
     const size_t smem = use_smem ? smem_bytes : 0;
     if (act_tag == MIE_F32)
         return launch_kernel(add_rmsnorm_kernel<float, float>, dim3(num_rows), dim3(threads), smem, stream,
-                             (const float*)delta, res, w, w_tag, (float*)out, rows, n, eps, use_smem);
+                             (const float*)delta, res, w, w_tag, (float*)out, rows, n, eps, use_smem, num_in_rows, g_range_report);
     else if (act_tag == MIE_BF16)
         return launch_kernel(add_rmsnorm_kernel<bf16, bf16>, dim3(num_rows), dim3(threads), smem, stream,
-                             (const bf16*)delta, res, w, w_tag, (bf16*)out, rows, n, eps, use_smem);
+                             (const bf16*)delta, res, w, w_tag, (bf16*)out, rows, n, eps, use_smem, num_in_rows, g_range_report);
     return MIE_ERR_BAD_ARG;
 }

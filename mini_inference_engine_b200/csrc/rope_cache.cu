@@ -10,6 +10,7 @@
 // rotated k and plain v go to slot `slots[t]` of the layer's pages
 // (inference_engine/model.py:130-134), page layout [page, kv_head, slot_in_page, head_dim].
 #include "common.cuh"
+#include "range_check.cuh"
 
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ cos_t,
                                   float* __restrict__ sin_t, int max_pos, int half) {
@@ -37,12 +38,20 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ sin_t, T* __restrict__ k_cache,
                                   T* __restrict__ v_cache, int num_heads, int num_kv_heads,
                                   int head_dim, int rotary_dim, int page_size, int max_pos,
-                                  int write_cache) {
+                                  int write_cache, int64_t num_pages, int* report) {
     pdl_enter();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
-    int pos = positions[t];
-    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);   // checked on the host; keeps reads inside the table
+    const int pos = positions[t];
+    // positions and slots are made on the host; one out of range is reported and its token left alone
+    if (half > 0 && range_position(pos, max_pos) != MIE_RANGE_OK) {
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_POSITION, MIE_K_ROPE_CACHE, t, pos);
+        return;
+    }
+    if (write_cache && range_slot(slots[t], num_pages, page_size) != MIE_RANGE_OK) {
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_SLOT, MIE_K_ROPE_CACHE, t, slots[t]);
+        return;
+    }
     const float* cs = cos_t + (int64_t)pos * half;
     const float* sn = sin_t + (int64_t)pos * half;
     T* row = qkv + (int64_t)t * (num_heads + 2 * num_kv_heads) * head_dim;
@@ -93,12 +102,20 @@ __device__ __forceinline__ void rotate8(const uint4& lo, const uint4& hi, const 
 __global__ void rope_cache_bf16x8_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int num_heads, int num_kv_heads,
-                                         int head_dim, int rotary_dim, int page_size, int max_pos, int write_cache) {
+                                         int head_dim, int rotary_dim, int page_size, int max_pos, int write_cache,
+                                         int64_t num_pages, int* report) {
     pdl_enter();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1, h8 = half >> 3, d8 = head_dim >> 3, tail8 = (head_dim - rotary_dim) >> 3;
-    int pos = positions[t];
-    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const int pos = positions[t];
+    if (range_position(pos, max_pos) != MIE_RANGE_OK) {
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_POSITION, MIE_K_ROPE_CACHE, t, pos);
+        return;
+    }
+    if (write_cache && range_slot(slots[t], num_pages, page_size) != MIE_RANGE_OK) {
+        if (threadIdx.x == 0) range_report(report, MIE_RANGE_SLOT, MIE_K_ROPE_CACHE, t, slots[t]);
+        return;
+    }
     const float* cs = cos_t + (int64_t)pos * half;
     const float* sn = sin_t + (int64_t)pos * half;
     bf16* row = qkv + (int64_t)t * (num_heads + 2 * num_kv_heads) * head_dim;
@@ -141,7 +158,7 @@ extern "C" int mie_rope_cache_write(void* qkv, int act_tag, const int* positions
                                     const float* cos_t, const float* sin_t, void* k_cache, void* v_cache,
                                     int num_tokens, int num_heads, int num_kv_heads, int head_dim,
                                     int rotary_dim, int page_size, int max_pos, int write_cache,
-                                    cudaStream_t stream) {
+                                    long long num_pages, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (head_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || page_size <= 0)
         return MIE_ERR_BAD_ARG;
@@ -155,15 +172,15 @@ extern "C" int mie_rope_cache_write(void* qkv, int act_tag, const int* positions
         while (t8 < 256 && t8 * 8 < work) t8 <<= 1;
         return launch_kernel(rope_cache_bf16x8_kernel, dim3(num_tokens), dim3(t8), 0, stream, (bf16*)qkv, positions, slots, cos_t,
                              sin_t, (bf16*)k_cache, (bf16*)v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
-                             max_pos, write_cache);
+                             max_pos, write_cache, (int64_t)num_pages, g_range_report);
     }
     if (act_tag == MIE_F32)
         return launch_kernel(rope_cache_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
             (float*)qkv, positions, slots, cos_t, sin_t, (float*)k_cache, (float*)v_cache, num_heads,
-            num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache);
+            num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache, (int64_t)num_pages, g_range_report);
     else if (act_tag == MIE_BF16)
         return launch_kernel(rope_cache_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream,
             (bf16*)qkv, positions, slots, cos_t, sin_t, (bf16*)k_cache, (bf16*)v_cache, num_heads,
-            num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache);
+            num_kv_heads, head_dim, rotary_dim, page_size, max_pos, write_cache, (int64_t)num_pages, g_range_report);
     return MIE_ERR_BAD_ARG;
 }

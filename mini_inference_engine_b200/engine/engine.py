@@ -386,6 +386,7 @@ class LLMEngine:
         with _nvtx_range("sample"):
             fl.event.synchronize()
             new_tokens = fl.pinned[:len(fl.seqs)].tolist()
+        ops.check_range_errors()           # an integer out of range that a kernel refused to follow
         ops.check_tc_errors()
         gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result
         now = time.perf_counter()

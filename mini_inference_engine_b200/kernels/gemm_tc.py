@@ -11,8 +11,8 @@ from dataclasses import dataclass
 import torch
 
 from . import build, ops
+from .device import num_sms
 
-NUM_SMS = 148
 SMEM_BUDGET = 226 * 1024
 TWO_PER_SM = 112 * 1024
 
@@ -47,12 +47,13 @@ def plan(M: int, N: int, K: int) -> dict:
     splits = 1
     # few tokens stream the weights, and more blocks stream faster: split up to two blocks per SM.  Many
     # tokens are bound by the tensor pipe: split only while half the SMs would otherwise idle.
-    room = 2 * NUM_SMS if swapped else NUM_SMS
+    sms = num_sms()
+    room = 2 * sms if swapped else sms
     while splits < 8 and tiles * splits * 2 <= room and k_tiles // (splits * 2) >= 2:
         # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least; more blocks than SMs only if
         # each still streams eight k-tiles (a second wave of short blocks costs more than it brings: the
         # q|k|v product of TinyLlama, 20 tiles, runs the whole decode step 11 us faster with 4 splits than 8)
-        if tiles * splits * 2 > NUM_SMS and k_tiles // (splits * 2) < 8:
+        if tiles * splits * 2 > sms and k_tiles // (splits * 2) < 8:
             break
         splits *= 2
     per_split = -(-k_tiles // splits)
@@ -125,14 +126,14 @@ def splits_k(M: int, N: int, K: int) -> bool:
 
 
 def _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, fuse: _Fuse, rope_args=None):
-    lib = build.load("gemm_tcgen05")
+    lib = ops.load("gemm_tcgen05")
     null = ctypes.c_void_p(0)
     if rope_args is None:
-        rope_c = (null, null, null, null, null, null, 0, 0, 0, 0, 0, 0, 0)
+        rope_c = (null, null, null, null, null, null, 0, 0, 0, 0, 0, 0, 0, ctypes.c_longlong(0))
     else:
         positions, slots, cos, sin, k_cache, v_cache, H, Hkv, D, rot, page, write_cache = rope_args
         rope_c = (ops._ptr(positions), ops._ptr(slots), ops._ptr(cos), ops._ptr(sin), ops._ptr(k_cache), ops._ptr(v_cache),
-                  H, Hkv, D, rot, page, cos.shape[0], int(write_cache))
+                  H, Hkv, D, rot, page, cos.shape[0], int(write_cache), ctypes.c_longlong(k_cache.shape[0]))
     rc = lib.mie_gemm_tc_fused(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                                ops._ptr(out), ops.tag(out) if out is not None else ops.tag(x), M, N, K, pl["bn"], pl["splits"],
                                pl["stages"], int(swiglu), int(pl.get("pdl", pdl_enabled)), ctypes.byref(fuse), *rope_c,
@@ -188,7 +189,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False,
             raise GemmTcError("a deferred norm factor needs few tokens and a split K")
         _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, _fuse_struct(deferred))
         return out
-    lib = build.load("gemm_tcgen05")
+    lib = ops.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                          ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], pl["splits"], pl["stages"],
                          int(swiglu), int(pl.get("pdl", pdl_enabled)), ops._stream())
@@ -233,12 +234,12 @@ def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots,
                       (positions, slots, cos, sin, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
                        write_cache))
         return out
-    lib = build.load("gemm_tcgen05")
+    lib = ops.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc_qkv_rope(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                                   ops._ptr(out), M, N, K, pl["bn"], pl["splits"], pl["stages"], int(pdl_enabled),
                                   ops._ptr(positions), ops._ptr(slots), ops._ptr(cos), ops._ptr(sin), ops._ptr(k_cache),
                                   ops._ptr(v_cache), num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
-                                  cos.shape[0], int(write_cache), ops._stream())
+                                  cos.shape[0], int(write_cache), ctypes.c_longlong(k_cache.shape[0]), ops._stream())
     ops._check(rc, f"gemm_tc_qkv_rope M{M} N{N} K{K} {pl}")
     return out
 

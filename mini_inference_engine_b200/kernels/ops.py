@@ -11,6 +11,7 @@ import math
 import torch
 
 from . import build
+from .device import num_sms
 
 F32, BF16 = 0, 1
 _TAGS = {torch.float32: F32, torch.bfloat16: BF16}
@@ -60,6 +61,48 @@ def _check(code: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
+# --------------------------------------------------------------------------- range report
+# Four int32 in pinned host memory that the kernels write directly (code, kernel, index, value): see
+# csrc/range_check.cuh.  Every library that checks ranges is told the address when it is loaded.
+_RANGE_CODES = {1: "token id outside the vocabulary (or the fed-back tokens)", 2: "position outside the position table "
+                "(or more positions than the block table covers)", 3: "cache slot outside the cache",
+                4: "block-table entry outside the page pool", 5: "row index outside the batch"}
+_RANGE_KERNELS = {1: "embedding", 2: "rope_cache", 3: "norm", 4: "attention_simt", 5: "attention_decode",
+                  6: "attention_prefill", 7: "attention_prefill_tc", 8: "gemm_tcgen05 (q|k|v with rotation)"}
+_range_report: torch.Tensor | None = None
+_range_told: set = set()
+
+
+def range_report() -> torch.Tensor:
+    global _range_report
+    if _range_report is None:
+        with torch.inference_mode(False):        # made inside a step, it would refuse to be cleared outside one
+            _range_report = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+    return _range_report
+
+
+def load(name: str):
+    """The library of ``csrc/<name>.cu``, told where the range report lives if it checks ranges."""
+    lib = build.load(name)
+    if name not in _range_told:
+        _range_told.add(name)
+        if hasattr(lib, "mie_set_range_report"):
+            lib.mie_set_range_report(ctypes.c_void_p(range_report().data_ptr()))
+    return lib
+
+
+def check_range_errors() -> None:
+    """Raises if a kernel met an integer out of range since the last call (after a synchronise): the
+    kernel skipped that access, so the step's result is not valid."""
+    if _range_report is None:
+        return
+    code, kernel, index, value = _range_report.tolist()
+    if code:
+        _range_report.numpy()[:] = 0
+        raise KernelError(f"{_RANGE_KERNELS.get(kernel, kernel)}: {_RANGE_CODES.get(code, code)}: "
+                          f"value {value} at index {index}; the access was skipped and the step's output is not valid")
+
+
 def _need(cond: bool, msg: str) -> None:
     if not cond:
         raise KernelError(msg)
@@ -81,8 +124,9 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, feedbac
     _need(out.dtype == torch.float32 and out.shape == (ids.numel(), h) and out.is_contiguous(),
           "embedding output must be contiguous float32 [tokens, hidden]")
     _need(table.is_contiguous(), "embedding table must be contiguous")
-    lib = build.load("embedding")
-    _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(feedback), _ptr(out), ids.numel(), h, V, _stream()),
+    lib = load("embedding")
+    _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(feedback), _ptr(out), ids.numel(), h, V,
+                             feedback.numel() if feedback is not None else 0, _stream()),
            "embedding")
     return out
 
@@ -106,9 +150,9 @@ def add_rmsnorm(delta, res: torch.Tensor, weight: torch.Tensor, eps: float, out:
         _need(rows.numel() == num_rows, "one gathered row per output row")
     else:
         _need(res.shape[0] == num_rows, "output rows must match residual rows")
-    lib = build.load("norm")
+    lib = load("norm")
     _check(lib.mie_add_rmsnorm(_ptr(delta), _ptr(res), _ptr(weight), tag(weight), _ptr(out), tag(out),
-                               _ptr(rows), num_rows, n, ctypes.c_float(eps), _stream()), "add_rmsnorm")
+                               _ptr(rows), num_rows, n, ctypes.c_float(eps), res.shape[0], _stream()), "add_rmsnorm")
     return out
 
 
@@ -137,10 +181,11 @@ def rope_cache_write(qkv: torch.Tensor, positions, slots, cos, sin, k_cache, v_c
     _i32(slots, "slots")
     _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache type must match qkv")
     _need(cos.shape[1] * 2 == rotary_dim, "rotation table does not match rotary_dim")
-    lib = build.load("rope_cache")
+    lib = load("rope_cache")
     _check(lib.mie_rope_cache_write(_ptr(qkv), tag(qkv), _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin),
                                     _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim,
-                                    rotary_dim, page_size, cos.shape[0], int(write_cache), _stream()),
+                                    rotary_dim, page_size, cos.shape[0], int(write_cache),
+                                    ctypes.c_longlong(k_cache.shape[0]), _stream()),
            "rope_cache_write")
 
 
@@ -162,12 +207,13 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
     _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "q, caches and out must share a type")
     _need(out.is_contiguous(), "attention output must be contiguous")
     rows = row_q_len.numel()
-    lib = build.load("attention_simt")
+    lib = load("attention_simt")
     _check(lib.mie_paged_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
                                    _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                    _ptr(row_ctx_len), rows, num_tokens, _ptr(out), tag(q), num_heads,
                                    num_kv_heads, head_dim, page_size, ctypes.c_float(scale),
-                                   int(window or 0), int(min_q_len), _stream()), "paged_attention")
+                                   int(window or 0), int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), _stream()),
+           "paged_attention")
     return out
 
 
@@ -185,12 +231,12 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
                  (row_ctx_len, "row_ctx_len")):
         _i32(t, n)
     _need(out.is_contiguous(), "attention output must be contiguous")
-    lib = build.load("attention_prefill")
+    lib = load("attention_prefill")
     _check(lib.mie_prefill_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
                                      _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                      _ptr(row_ctx_len), row_q_len.numel(), num_tokens, _ptr(out), num_heads,
                                      num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window or 0),
-                                     int(min_q_len), _stream()), "prefill_attention")
+                                     int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), _stream()), "prefill_attention")
     return out
 
 
@@ -208,7 +254,7 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
                  (row_ctx_len, "row_ctx_len")):
         _i32(t, n)
     _need(out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(), "contiguous caches and output")
-    lib = build.load("attention_prefill_tc")
+    lib = load("attention_prefill_tc")
     _check(lib.mie_prefill_attention_tc(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
                                         ctypes.c_int64(k_cache.shape[0]), _ptr(block_tables), block_tables.shape[1],
                                         _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len), row_q_len.numel(),
@@ -227,7 +273,6 @@ def check_tc_errors() -> None:
             raise KernelError(f"a block of {name} gave up waiting on a barrier; its output is not valid")
 
 
-NUM_SMS = 148
 _workspaces: dict = {}
 
 
@@ -250,7 +295,7 @@ def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
     256 keys a part, inference_engine/kernels/decode_attention.py:117-125)."""
     blocks = max(1, rows * kv_units)
     splits = 1
-    while splits < 8 and blocks * splits * 2 <= 2 * NUM_SMS and splits * 64 < max_ctx:
+    while splits < 8 and blocks * splits * 2 <= 2 * num_sms() and splits * 64 < max_ctx:
         splits *= 2
     return splits
 
@@ -265,7 +310,7 @@ def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False) -> 
     at four stages want two, which puts twice as many on an SM (batch 256, 512 keys: 34 us against
     46 us)."""
     tiles = -(-(-(-max(1, max_ctx) // splits)) // 64)
-    if blocks > 3 * NUM_SMS:
+    if blocks > 3 * num_sms():
         return 3 if tma else 2            # TMA tiles are unpadded: three stages still put four blocks on an SM (256 x 512: 29.2 us, two stages 30.7)
     return 3 if tiles <= 4 else 4
 
@@ -278,7 +323,7 @@ def decode_uses_tma(blocks: int) -> bool:
     40.0 us; 8 x 512: 7.5 against 7.1 us) -- the copies were never the bound there, the softmax
     bookkeeping per 16 keys is.  Cache slots beyond a request's context are copied along with their
     page and must hold finite values (the cache storage starts as zeros)."""
-    return blocks > 3 * NUM_SMS
+    return blocks > 3 * num_sms()
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
@@ -313,13 +358,13 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
         part_o = _workspace(q.device, "decode_part_o", rows * num_heads * splits * head_dim, torch.float32)
         part_lse = _workspace(q.device, "decode_part_lse", rows * num_heads * splits, torch.float32)
         counters = _workspace(q.device, "decode_counters", rows * num_kv_heads * chunks, torch.int32)
-    lib = build.load("attention_decode")
+    lib = load("attention_decode")
     _check(lib.mie_decode_attention(_ptr(q), ctypes.c_int64(q_stride), _ptr(k_cache), _ptr(v_cache),
                                     _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                     _ptr(row_ctx_len), rows, _ptr(out), num_heads, num_kv_heads, head_dim,
                                     page_size, ctypes.c_float(scale), int(window or 0), int(splits),
                                     _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0),
-                                    ctypes.c_int64(k_cache.shape[0] if tma else 0), _stream()),
+                                    ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]), _stream()),
            "decode_attention")
     return out
 

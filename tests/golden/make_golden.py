@@ -1,6 +1,7 @@
 """Makes tests/golden/*.json: logits of brave30/mini-inference-engine's own ``LlamaModel`` run on the
-CPU in float32 on two tiny random models, for the plain implementation (tests/plain_llama.py) to be
-checked against.
+CPU on two tiny random models: in float32, for the plain implementation (tests/plain_llama.py) to be
+checked against, and in bfloat16 (the reference's serving type, with its roundings: residual, normed
+value, rotation products and logits in bfloat16), for the bfloat16 engine to be anchored on.
 
     python tests/golden/make_golden.py /path/to/mini-inference-engine
 
@@ -129,13 +130,30 @@ def run_reference(ref_root: str, name: str, seed: int) -> dict:
         out.append(model.forward(torch.tensor(ids[p:p + 1]), torch.tensor([p]), meta))
     cut = torch.cat(out, 0)
     keep = [0, 1, n // 2, n - 2, n - 1]
+
+    # the same model as the reference serves it: bfloat16 weights, activations, tables and logits
+    # (inference_engine/engine.py:36, inference_engine/model.py:84-115), whole prompt
+    model16 = LlamaModel(cfg, {k: v.clone() for k, v in W.items()}, device="cpu", dtype=torch.bfloat16,
+                         use_triton_rmsnorm=False, use_triton_decode_attn=False)
+    model16.kv_cache = KVCache(cfg, nb, bs, torch.bfloat16, "cpu")
+    table = [5, 2, 9, 7][: -(-n // bs)]
+    meta = AttentionMetadata(slot_mapping=slots(0, n), prefills=[PrefillChunk(0, n, n, None, None)])
+    whole16 = model16.forward(torch.tensor(ids), torch.arange(n), meta).float()
     return dict(config=c, seed=seed, prompt=ids, positions=keep,
                 logits=[[float(x) for x in whole[p]] for p in keep],
+                logits_bf16=[[float(x) for x in whole16[p]] for p in keep],
+                reference_bf16_vs_float32_max_abs=float((whole16 - whole).abs().max()),
                 reference_cut_vs_whole_max_abs=float((cut - whole).abs().max()))
 
 
+def reference_root() -> str:
+    if len(sys.argv) != 2 or not os.path.isdir(os.path.join(sys.argv[1], "inference_engine")):
+        sys.exit(__doc__)
+    return sys.argv[1]
+
+
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = reference_root()
     for name, seed in (("tiny_a", 11), ("tiny_b", 12)):
         g = run_reference(ref, name, seed)
         with open(os.path.join(HERE, name + ".json"), "w") as f:
@@ -184,7 +202,7 @@ def run_reference_scheduler(ref_root: str, case: dict) -> dict:
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = reference_root()
     out = {name: run_reference_scheduler(ref, case) for name, case in SCHED_CASES.items()}
     with open(os.path.join(HERE, "scheduler.json"), "w") as f:
         json.dump(out, f)

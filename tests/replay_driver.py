@@ -13,6 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 class Replay:
     def __init__(self, model_dir, dtype, out_dir, max_tokens, vocab, extra_args=()):
         self.out_dir, self.vocab, self.n = str(out_dir), vocab, 0
+        self.pages = {}          # with --show-pages: step -> {request id: [page ids per cache group]}
         os.makedirs(self.out_dir, exist_ok=True)
         self.proc = subprocess.Popen(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
@@ -28,6 +29,9 @@ class Replay:
         self.proc.stdin.write(json.dumps(msg) + "\n")
         self.proc.stdin.flush()
         line = self.proc.stdout.readline()
+        if line.startswith(f"pages {step} "):
+            self.pages[step] = json.loads(line.split(" ", 2)[2])
+            line = self.proc.stdout.readline()
         if line.strip() != f"done {step}":
             rest = self.proc.stdout.read()
             raise RuntimeError(f"trace_run said {line!r} {rest!r} (exit {self.proc.poll()})")

@@ -123,7 +123,8 @@ def test_mixed_batches_with_pages_used_again(name, dtype_name, model_folders, tm
     waiting = list(reqs)
     live: dict = {}
     got: dict = {}
-    with Replay(model_folders[name], dtype_name, tmp_path, 4 * longest, vocab) as rp:
+    owners: dict = {}            # page id -> the requests that held it at some step
+    with Replay(model_folders[name], dtype_name, tmp_path, 4 * longest, vocab, extra_args=("--show-pages",)) as rp:
         steps = 0
         while waiting or live:
             while waiting and len(live) < 4 and rng.random() < 0.7:
@@ -147,8 +148,17 @@ def test_mixed_batches_with_pages_used_again(name, dtype_name, model_folders, tm
             if not entries:
                 continue
             collect(got, filed, rp.step(entries, end=ended))
+            for rid, groups in rp.pages[rp.n - 1].items():
+                for page in groups[0]:
+                    assert page != 0, "the scratch page was handed to a request"
+                    owners.setdefault(page, set()).add(rid)
+            held_now = [p for groups in rp.pages[rp.n - 1].values() for p in groups[0]]
+            assert len(held_now) == len(set(held_now)), "two requests of one step hold the same page"
             steps += 1
         assert steps > 20
+    # the point of the small pool: pages did go from one request to another
+    assert sum(len(r) > 1 for r in owners.values()) >= 4, f"pages were not used again: {owners}"
+    assert max(owners) <= 4 * longest // 16
     check(name, model_folders[name], dtype_name, got, reqs)
 
 

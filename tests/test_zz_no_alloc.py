@@ -1,7 +1,7 @@
 """The decode-attention entry point that allocates nothing (csrc/attention_decode_static.h), called
 through its exported C symbol the way a host program without an allocator would call it: inputs and
 outputs only.  Its output is compared with the existing entry point's (scratch passed in by the
-caller) on two calls in a row, because the second call finds the library's scratch array as the
+caller) and with the plain attention formula on two calls in a row, because the second call finds the library's scratch array as the
 first one left it.  This file is collected last on purpose: if it fails, a run that stops at the
 first failure has already run every other test."""
 import ctypes
@@ -10,6 +10,7 @@ import math
 import pytest
 import torch
 
+import plain_llama as pl
 from helpers import close, scattered_tables
 
 pytestmark = pytest.mark.gpu
@@ -25,11 +26,24 @@ def _case(H, Hkv, D, page, ctxs, seed):
     for r, t in enumerate(tables):
         bt[r, :len(t)] = torch.tensor(t)
     rows = len(ctxs)
-    return dict(
+    return dict(tables=tables, ctxs=ctxs,
         q=torch.randn(rows, H, D).bfloat16().to(DEV), k=torch.randn(num_pages, Hkv, page, D).bfloat16().to(DEV),
         v=torch.randn(num_pages, Hkv, page, D).bfloat16().to(DEV), bt=bt.to(DEV),
         q_start=torch.arange(rows, dtype=torch.int32, device=DEV), q_len=torch.ones(rows, dtype=torch.int32, device=DEV),
         ctx=torch.tensor(ctxs, dtype=torch.int32, device=DEV), H=H, Hkv=Hkv, D=D, page=page, rows=rows)
+
+
+def _plain(c):
+    """The newest token of every row attending to its request's keys, gathered from the pages on the host."""
+    k, v, q = c["k"].float().cpu(), c["v"].float().cpu(), c["q"].float().cpu()
+    out = []
+    for r, (table, ctx) in enumerate(zip(c["tables"], c["ctxs"])):
+        kk = torch.cat([k[p] for p in table], 1)[:, :ctx].transpose(0, 1)          # [ctx, kv_heads, D]
+        vv = torch.cat([v[p] for p in table], 1)[:, :ctx].transpose(0, 1)
+        qq = torch.zeros(ctx, c["H"], c["D"])
+        qq[-1] = q[r]
+        out.append(pl.causal_attention(qq, kk, vv, 1.0 / math.sqrt(c["D"]))[-1])
+    return torch.stack(out)
 
 
 def _call_static(lib, c, splits, out):
@@ -55,7 +69,8 @@ def test_static_scratch_entry_point_matches_the_existing_one_twice_in_a_row():
         rc = _call_static(lib, c, splits, got)
         assert rc == 0, lib.mie_decode_attention_static_error().decode()
         torch.cuda.synchronize()
-        close(got, want, torch.bfloat16, f"static entry point, call {call}")
+        close(got, want, torch.bfloat16, f"static entry point against the existing one, call {call}")
+        close(got, _plain(c), torch.bfloat16, f"static entry point against the plain formula, call {call}")
     # nothing was allocated by the entry point itself: a further call leaves free memory unchanged
     got2 = torch.full_like(want, 99.0)
     torch.cuda.synchronize()
