@@ -5,7 +5,9 @@ side otherwise), the tile of the other side, how far to split K so that all SMs 
 depth of the shared-memory ring."""
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -118,6 +120,114 @@ def _fuse_struct(deferred: DeferredNorm | None = None, res=None, norm_weight=Non
     return f
 
 
+# --------------------------------------------------------------------------- chains of few-token products
+# csrc/gemm_chain.cu runs up to four products that follow one another in ONE launch whose blocks stay on
+# their SMs and stream weights ahead through the whole chain.  The fused products of a decode step (the
+# ones with the residual, norm-factor, SwiGLU and rotation epilogues) are queued here while a model runs
+# its step inside ``chaining()`` and go out together: when four are queued, when any other kernel of this
+# package is about to launch (ops.before_launch), or when the context ends.  Outside ``chaining()`` such a
+# product is a chain of one.  Off unless MIE_B200_CHAIN=1 (or ``chain_enabled`` is set): measured on B200
+# the chain loses against one launch per product at TinyLlama's sizes (see the kernel's header).
+
+class _ChainOp(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("bias_tag", ctypes.c_int),
+                ("out", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int), ("swiglu", ctypes.c_int),
+                ("positions", ctypes.c_void_p), ("slots", ctypes.c_void_p), ("cos_t", ctypes.c_void_p),
+                ("sin_t", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("num_heads", ctypes.c_int), ("num_kv_heads", ctypes.c_int), ("head_dim", ctypes.c_int),
+                ("rotary_dim", ctypes.c_int), ("page_size", ctypes.c_int), ("max_pos", ctypes.c_int),
+                ("write_cache", ctypes.c_int), ("num_pages", ctypes.c_longlong),
+                ("res", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("norm_w_tag", ctypes.c_int),
+                ("xw_out", ctypes.c_void_p), ("sq_out", ctypes.c_void_p), ("sq_stride", ctypes.c_int),
+                ("sq_in", ctypes.c_void_p), ("sq_slots", ctypes.c_int), ("sq_in_stride", ctypes.c_int),
+                ("sq_width", ctypes.c_float), ("sq_eps", ctypes.c_float)]
+
+
+CHAIN_MAX_TOKENS = 32
+CHAIN_MAX_OPS = 4
+CHAIN_SPLITS = 8
+chain_enabled = os.environ.get("MIE_B200_CHAIN", "0") == "1"
+_chain: list = []            # queued (op, tensors kept alive, M)
+_chain_depth = 0             # > 0 inside chaining()
+chain_launches = 0           # launches of the chain kernel so far, and the products they carried
+chain_products = 0
+
+
+def chain_takes(M: int, N: int, K: int, rope=None) -> bool:
+    """Whether the chain kernel runs this fused product: few tokens; with the rotation, heads that do not
+    straddle 128-row tiles and rotation partners that share an owner (every eighth row)."""
+    if not chain_enabled or M < 1 or M > CHAIN_MAX_TOKENS or K % 8 or N % 8:
+        return False
+    if rope is not None:
+        head_dim, rotary_dim = rope
+        bn = 16 if M <= 16 else 32
+        if head_dim <= 0 or 128 % head_dim or rotary_dim % 2 or (rotary_dim // 2) % CHAIN_SPLITS or bn * rotary_dim * 4 > 16 * 1024:
+            return False
+    return True
+
+
+def chain_slots(N: int) -> int:
+    """Shares of sum(res^2) per token that a residual epilogue of the chain kernel writes."""
+    return -(-N // 128) * CHAIN_SPLITS
+
+
+def flush_chain() -> None:
+    """Launches what is queued, as one chain."""
+    global chain_launches, chain_products
+    if not _chain:
+        return
+    queued = list(_chain)
+    _chain.clear()
+    arr = (_ChainOp * len(queued))(*[q[0] for q in queued])
+    lib = ops.load("gemm_chain")
+    rc = lib.mie_gemm_chain(arr, len(queued), queued[0][2], 0, int(pdl_enabled), ops.raw_stream())
+    ops._check(rc, f"gemm_chain of {len(queued)} products, {queued[0][2]} tokens, N x K "
+               + ", ".join(f"{q[0].N} x {q[0].K}" for q in queued))
+    chain_launches += 1
+    chain_products += len(queued)
+
+
+ops.before_launch.append(flush_chain)
+
+
+@contextlib.contextmanager
+def chaining():
+    """Inside, fused few-token products are queued and launched as chains (see above)."""
+    global _chain_depth
+    _chain_depth += 1
+    try:
+        yield
+    finally:
+        _chain_depth -= 1
+        if _chain_depth == 0:
+            flush_chain()
+
+
+def _chain_submit(x, w, bias, out, M, N, K, swiglu, fuse: "_Fuse", rope_args) -> None:
+    op = _ChainOp()
+    op.x, op.w, op.N, op.K, op.swiglu = x.data_ptr(), w.data_ptr(), N, K, int(swiglu)
+    if bias is not None:
+        op.bias, op.bias_tag = bias.data_ptr(), ops.tag(bias)
+    if out is not None:
+        op.out = out.data_ptr()
+    keep = [x, w, bias, out]
+    if rope_args is not None:
+        positions, slots, cos, sin, k_cache, v_cache, H, Hkv, D, rot, page, write_cache = rope_args
+        op.positions, op.slots, op.cos_t, op.sin_t = positions.data_ptr(), slots.data_ptr(), cos.data_ptr(), sin.data_ptr()
+        op.k_cache, op.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+        op.num_heads, op.num_kv_heads, op.head_dim, op.rotary_dim, op.page_size = H, Hkv, D, rot, page
+        op.max_pos, op.write_cache, op.num_pages = cos.shape[0], int(write_cache), k_cache.shape[0]
+        keep += [positions, slots, cos, sin, k_cache, v_cache]
+    for f in ("res", "norm_w", "norm_w_tag", "xw_out", "sq_out", "sq_stride", "sq_in", "sq_slots", "sq_in_stride",
+              "sq_width", "sq_eps"):
+        setattr(op, f, getattr(fuse, f))
+    if _chain and _chain[0][2] != M:
+        flush_chain()
+    _chain.append((op, keep, M))
+    if _chain_depth == 0 or len(_chain) == CHAIN_MAX_OPS:
+        flush_chain()
+
+
 def splits_k(M: int, N: int, K: int) -> bool:
     """Whether the plan for these sizes puts the weight on the 128-row side and splits K across a
     cluster: the form whose owners' sum carries the rotation, residual and norm-factor epilogues."""
@@ -125,7 +235,12 @@ def splits_k(M: int, N: int, K: int) -> bool:
     return bool(pl["swapped"] and pl["splits"] >= 2 and -(-K // 64) >= pl["splits"] and pl["bn"] <= 128)
 
 
-def _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, fuse: _Fuse, rope_args=None):
+def _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, fuse: _Fuse, rope_args=None, keep=(), chain=None):
+    if chain if chain is not None else chain_takes(M, N, K, (rope_args[8], rope_args[9]) if rope_args is not None else None):
+        _chain_submit(x, w, bias, out, M, N, K, swiglu, fuse, rope_args)
+        if _chain:
+            _chain[-1][1].extend(keep)
+        return
     lib = ops.load("gemm_tcgen05")
     null = ctypes.c_void_p(0)
     if rope_args is None:
@@ -159,12 +274,14 @@ def gemm_residual(x, w: torch.Tensor, res: torch.Tensor, bias=None, norm_weight=
         raise GemmTcError("the residual epilogue needs few tokens and a split K")
     out = None
     xw = sq = None
+    chain = not force and chain_takes(M, N, K)
     if norm_weight is not None:
-        slots = -(-N // 128) * max(pl["splits"], 4)
+        slots = chain_slots(N) if chain else -(-N // 128) * max(pl["splits"], 4)
         xw = torch.empty(M, N, dtype=torch.bfloat16, device=res.device)
         sq = torch.empty(slots, max(M, pl["bn"] * -(-M // pl["bn"])), dtype=torch.float32, device=res.device)
         out = DeferredNorm(xw, sq, slots, N, eps)
-    _launch_fused(xt, w, bias, None, M, N, K, pl, False, _fuse_struct(deferred, res, norm_weight, xw, sq))
+    _launch_fused(xt, w, bias, None, M, N, K, pl, False, _fuse_struct(deferred, res, norm_weight, xw, sq),
+                  keep=(res, norm_weight, xw, sq, deferred.sq if deferred is not None else None), chain=chain)
     return out
 
 
@@ -187,7 +304,8 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False,
     if deferred is not None:
         if not pl["swapped"]:
             raise GemmTcError("a deferred norm factor needs few tokens and a split K")
-        _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, _fuse_struct(deferred))
+        _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, _fuse_struct(deferred), keep=(deferred.sq,),
+                      chain=None if not force else False)
         return out
     lib = ops.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
@@ -229,10 +347,10 @@ def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots,
     pl = plan(M, N, K)
     pl["stages"] = min(pl["stages"], 4)      # the rotation's tables share the block's memory: a fifth stage takes it past what
                                              # lets two blocks share an SM (whole decode step 0.868 ms with four, 0.901 with five)
-    if deferred is not None:
+    if deferred is not None or chain_takes(M, N, K, (head_dim, rotary_dim)):
         _launch_fused(x, w, bias, out, M, N, K, pl, False, _fuse_struct(deferred),
                       (positions, slots, cos, sin, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, page_size,
-                       write_cache))
+                       write_cache), keep=(deferred.sq,) if deferred is not None else ())
         return out
     lib = ops.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc_qkv_rope(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
@@ -246,6 +364,11 @@ def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots,
 
 def check_error() -> None:
     """Raises if a block of an earlier launch gave up a bounded wait (call after a synchronise)."""
+    lib = build._libs.get("gemm_chain")
+    if lib is not None and lib.mie_gemm_chain_error():
+        lib.mie_gemm_chain_clear_error()
+        raise GemmTcError("a block of the chain kernel gave up waiting (on a barrier, on its peers or on the other "
+                          "blocks); the output is not valid")
     lib = build._libs.get("gemm_tcgen05")
     if lib is None:                     # never loaded: nothing was launched
         return

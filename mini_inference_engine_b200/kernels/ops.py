@@ -41,8 +41,17 @@ def _ptr(t):
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+before_launch: list = []     # callables run before any launch of this package (a pending chain of products goes first)
+
+
 def _stream():
     """The current CUDA stream's handle.  Asked on every launch (a graph capture switches streams)."""
+    for hook in before_launch:
+        hook()
+    return raw_stream()
+
+
+def raw_stream():
     if _raw_stream is not None:                      # the direct query; a tenth of the cost of the Stream object
         return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -126,6 +126,10 @@ class DecoderModel:
     def step(self, ctx: StepContext) -> torch.Tensor:
         if self.storage is None:
             raise RuntimeError("allocate_cache() must be called before step()")
+        with self.rt.step_scope():
+            return self._step(ctx)
+
+    def _step(self, ctx: StepContext) -> torch.Tensor:
         res = self.embedding.forward(ctx)
         delta = None
         last = len(self.run_order) - 1

@@ -157,8 +157,17 @@ class Runtime:
     def product_sources(self, *weights) -> set:
         """The kernel sources behind ``linear`` for these weights."""
         if self.dtype == torch.float32 or any(w is not None and w.dtype == torch.float32 for w in weights):
-            return {"gemm_simt"} if self.dtype == torch.float32 else {"gemm_simt", "gemm_tcgen05"}
-        return {"gemm_tcgen05"}
+            return {"gemm_simt"} if self.dtype == torch.float32 else {"gemm_simt", "gemm_tcgen05", "gemm_chain"}
+        return {"gemm_tcgen05", "gemm_chain"}
+
+    def step_scope(self):
+        """A context for one step of a model: in bfloat16 the fused few-token products queued inside it go
+        out as chains, one launch for several products (kernels/gemm_tc.py: chaining)."""
+        if self.dtype == torch.bfloat16:
+            from ..kernels import gemm_tc
+            return gemm_tc.chaining()
+        import contextlib
+        return contextlib.nullcontext()
 
     def defers_norm(self, num_tokens: int, w: torch.Tensor) -> bool:
         """Whether the product with ``w`` can take the norm in front of it as a factor on its sums

@@ -769,3 +769,53 @@ def test_gemm_tc_deferred_norm_factor_with_rotation(ops):
         pg, off = int(slots[t]) // page, int(slots[t]) % page
         close(kc[pg, :, off], pl.apply_rope(k.view(M, Hkv, D), ang)[t], torch.bfloat16, f"cached k of token {t}")
         close(vc[pg, :, off], v.view(M, Hkv, D)[t], torch.bfloat16, f"cached v of token {t}")
+
+
+# --------------------------------------------------------------------------- the chain kernel (off by default)
+
+@pytest.fixture()
+def chain_on():
+    from mini_inference_engine_b200.kernels import gemm_tc
+    before, gemm_tc.chain_enabled = gemm_tc.chain_enabled, True
+    yield gemm_tc
+    gemm_tc.flush_chain()
+    gemm_tc.chain_enabled = before
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 32])
+def test_chain_of_four_products_in_one_launch(chain_on, M):
+    """Output projection (residual + next norm) -> gate/up with the norm factor and SwiGLU -> down (residual + next
+    norm) -> a plain product with the norm factor, queued and launched as ONE chain, against the plain formulas; at
+    sizes that give blocks empty K slices (K = 320: five k-tiles for eight splits) and tiles beyond the last row."""
+    gemm_tc = chain_on
+    torch.manual_seed(M)
+    h, I, N4 = 320, 456, 200
+    attn = (torch.randn(M, h) * 0.5).bfloat16()
+    Wo, Wgu = (torch.randn(h, h) * 0.05).bfloat16(), (torch.randn(2 * I, h) * 0.05).bfloat16()
+    Wd, W4 = (torch.randn(h, I) * 0.05).bfloat16(), (torch.randn(N4, h) * 0.05).bfloat16()
+    n1, n2 = (1 + 0.1 * torch.randn(h)).bfloat16(), (1 + 0.1 * torch.randn(h)).bfloat16()
+    res0 = torch.randn(M, h)
+    res = res0.clone().to(DEV)
+    launches = gemm_tc.chain_launches
+    with gemm_tc.chaining():
+        d1 = gemm_tc.gemm_residual(attn.to(DEV), Wo.to(DEV), res, None, n1.to(DEV), 1e-5)
+        act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        gemm_tc.gemm(d1, Wgu.to(DEV), act, swiglu=True)
+        d2 = gemm_tc.gemm_residual(act, Wd.to(DEV), res, None, n2.to(DEV), 1e-5)
+        out = torch.empty(M, N4, dtype=torch.bfloat16, device=DEV)
+        gemm_tc.gemm(d2, W4.to(DEV), out)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    assert gemm_tc.chain_launches == launches + 1
+    r1 = res0 + attn.float() @ Wo.float().t()
+    x1 = pl.round_bf16(r1 * n1.float())                                   # what the chain hands on: bf16(res * w)
+    f1 = torch.rsqrt((r1 ** 2).mean(-1, keepdim=True) + 1e-5)
+    gu = (x1 @ Wgu.float().t()) * f1
+    a = pl.round_bf16(torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2])
+    r2 = r1 + a @ Wd.float().t()
+    x2 = pl.round_bf16(r2 * n2.float())
+    f2 = torch.rsqrt((r2 ** 2).mean(-1, keepdim=True) + 1e-5)
+    want = (x2 @ W4.float().t()) * f2
+    close(act, a, torch.bfloat16, "chain: gate/up + SwiGLU")
+    assert (res.cpu() - r2).abs().max() <= 2e-2 * r2.abs().max()
+    close(out, want, torch.bfloat16, "chain: last product")
