@@ -3,7 +3,7 @@ inference_engine/config.py:45-56; the two Triton switches have no counterpart he
 (every GPU op is this package's own CUDA), and ``num_blocks`` and ``seed`` are added:
 tests need tiny page pools (the reference can only shrink its pool through the memory
 fraction, tests/test_correctness.py:46), and seeded sampling needs a seed; ``overlap_steps`` and
-``graph_prompt_portions`` switch two things that the reference does not have."""
+``graph_prompt_portions`` (with ``split_step_max_tokens``) switch two things that the reference does not have."""
 from __future__ import annotations
 
 from dataclasses import dataclass, fields
@@ -22,7 +22,11 @@ class EngineConfig:
     num_blocks: int | None = None           # explicit pool size in pages (page 0 included); None = from memory
     seed: int = 0                           # sampling seed
     overlap_steps: bool = True              # launch step N+1 before reading step N's tokens (they are fed back on the device)
-    graph_prompt_portions: int = 4          # graphs kept for steps that are one prompt portion of a length seen before (0 = none)
+    graph_prompt_portions: int = 16         # graphs kept for prompt portions, by padded length (0 = none: such steps launch kernel by kernel)
+    split_step_max_tokens: int = 512        # a portion of up to this many tokens beside decoding requests runs as a graph of
+                                            # its own after the decode graph (the weights are read twice, the host launches
+                                            # twice instead of 200 times); a longer one keeps the device busy longer than the
+                                            # host needs for its launches, and the step stays one batch
 
     def __post_init__(self):
         if self.block_size < 16 or self.block_size & (self.block_size - 1) or self.block_size > 128:

@@ -44,10 +44,17 @@ PENDING = -1          # in token_ids: a token that the step in flight is samplin
 
 
 class _InFlight:
-    """A launched step whose sampled tokens the host has not read yet."""
+    """A launched step whose sampled tokens the host has not read yet.  ``sources``: (pinned row, count)
+    in the order of ``seqs`` -- one entry, or two when the step ran as two graphs."""
 
-    def __init__(self, seqs, places, ending, pinned, event):
-        self.seqs, self.places, self.ending, self.pinned, self.event = seqs, places, ending, pinned, event
+    def __init__(self, seqs, places, ending, sources, event):
+        self.seqs, self.places, self.ending, self.sources, self.event = seqs, places, ending, sources, event
+
+    def tokens(self) -> list:
+        out = []
+        for row, n in self.sources:
+            out += row[:n].tolist()
+        return out
 
 
 class _DecodeGraph:
@@ -114,7 +121,10 @@ class LLMEngine:
         # the sampled tokens as the host sees them: two rows, taken in turns (step N's are read while step
         # N+1 runs); the sampling kernel writes them itself (pinned memory is addressable from the device)
         self._pinned_tokens = torch.zeros(2, most, dtype=torch.int32, pin_memory=True)
-        self._sampled = torch.zeros(most, dtype=torch.int32, device=self.device)     # the last step's tokens, on the device
+        # a prompt portion that runs as a graph of its own beside the decode graph leaves its token apart
+        self._pinned_portion = torch.zeros(2, 8, dtype=torch.int32, pin_memory=True)
+        self._portion_slot = most
+        self._sampled = torch.zeros(most + 8, dtype=torch.int32, device=self.device)   # the last step's tokens, on the device
         self._turn = 0
         self._in_flight = None
         self.graphs: dict = {}
@@ -140,13 +150,14 @@ class LLMEngine:
             t[:k], r[:k], p[:k] = temps, reqs, outpos
         return {"temperature": t, "request": r, "out_position": p, "host_turn": np.array([turn], dtype=np.int32)}
 
-    def _forward_and_sample(self, ctx, tokens_out=None):
+    def _forward_and_sample(self, ctx, tokens_out=None, host_out=None, seed=None):
         logits = self.model.step(ctx)
         if logits.shape[0] == 0:
             return None
         return self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
-                                   ctx.extras["out_position"], out=tokens_out,
-                                   host_out=self._pinned_tokens, host_turn=ctx.extras["host_turn"])
+                                   ctx.extras["out_position"], out=tokens_out, seed=seed,
+                                   host_out=self._pinned_tokens if host_out is None else host_out,
+                                   host_turn=ctx.extras["host_turn"])
 
     @torch.inference_mode()
     def _capture_cuda_graphs(self):
@@ -185,43 +196,64 @@ class LLMEngine:
                   f"in {time.perf_counter() - t0:.1f} s")
 
     # ------------------------------------------------------------------ CUDA graphs of prompt portions
-    PORTION_GRAPH_MIN_TOKENS = 128
+    PORTION_GRAPH_MIN_TOKENS = 2
+
+    @staticmethod
+    def _padded_length(n: int) -> int:
+        """The token count of the graph that serves a portion of ``n`` tokens: the next multiple of 32 up to
+        256 tokens, of 64 up to 1,024, of 128 beyond (at most an eighth more tokens than the portion has)."""
+        step = 32 if n <= 256 else (64 if n <= 1024 else 128)
+        return -(-n // step) * step
+
+    def _portion_rows(self, row, padded: int):
+        """The portion's row and, behind it, a scratch row that brings the batch to ``padded`` tokens: its
+        tokens sit at positions 0.. of page 0 (every block-table entry 0, state slot 0), nobody wants their
+        logits, and what they write lands in the scratch page."""
+        from .batch import BatchRow
+        extra = padded - len(row.tokens)
+        if extra == 0:
+            return [row]
+        pages = -(-extra // self.cfg.block_size)
+        zeros = [np.zeros(pages, dtype=np.int32) for _ in row.tables]
+        return [row, BatchRow(np.zeros(extra, dtype=np.int32), 0, zeros, 0, ())]
 
     @torch.inference_mode()
-    def _portion_graph(self, rows, extras, wanted: int):
-        """The captured step for a batch that is one portion of one prompt, if a step of the same
-        shape (tokens, wanted logits) has run before; else None, and the shape is remembered.
-        Long prompts are cut into portions of the token budget, so their steps repeat in shape:
-        launching some 160 kernels one by one costs the host about 3 ms a step, more than a short
-        portion takes on the device.  What differs between replays -- tokens, positions, block table,
-        sampling inputs -- lives in the graph's static input buffer; the context bound that kernels
-        plan by is the model's longest.  At most ``graph_prompt_portions`` graphs are kept (the least
-        recently used one goes).  The reference launches such steps eagerly."""
-        n = len(rows[0].tokens)
-        key = (n, wanted)
+    def _portion_graph(self, row, extras, wanted: int):
+        """The captured step for ONE prompt portion, if a step of the same padded shape (tokens, wanted
+        logits) has run before; else None, and the shape is remembered.  Launching some 160 kernels one by
+        one costs the host about 3 ms a step, more than a short portion takes on the device; portions are
+        cut by what is left of the token budget, so their lengths are rounded up (``_padded_length``) for
+        shapes to repeat.  What differs between replays -- tokens, positions, block table, the split between
+        the portion and its padding, sampling inputs -- lives in the graph's static input buffer; the context
+        bound that kernels plan by is the model's longest.  At most ``graph_prompt_portions`` graphs are kept
+        (the least recently used one goes).  The reference launches such steps eagerly."""
+        n = len(row.tokens)
+        padded = self._padded_length(n)
+        key = (padded, padded == n, wanted)
         g = self._portion_graphs.get(key)
         if g is not None:
             self._portion_graphs[key] = self._portion_graphs.pop(key)        # most recently used last
             return g
         if not self._portion_seen.get(key):
-            if len(self._portion_seen) > 64:
+            if len(self._portion_seen) > 256:
                 self._portion_seen.clear()
             self._portion_seen[key] = 1
             return None
         b = self.runner.builder
-        buf, layout = b.pack(rows, table_width=self.max_blocks_per_seq, extras=extras)
+        buf, layout = b.pack(self._portion_rows(row, padded), table_width=self.max_blocks_per_seq, extras=extras)
         layout["max_ctx_len"] = self.cfg.max_model_len
-        static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
+        layout["q_len"] = None              # the split between portion and padding changes from replay to replay:
+        static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)     # kernels for both kinds of row are captured
         ctx = b.to_device(buf, layout, into=static)
         ctx.token_feedback = self._sampled
-        tokens = self._sampled[:wanted]
+        tokens = self._sampled[self._portion_slot:self._portion_slot + wanted]
         # no warm-up run: a step of this shape has run before (kernels built, buffers sized), and running
         # this one twice would write the request's cache twice -- harmless, but not free
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph, pool=self._graph_pool):
-            self._forward_and_sample(ctx, tokens)
+            self._forward_and_sample(ctx, tokens, host_out=self._pinned_portion)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         g = _DecodeGraph(graph, layout, static, tokens, ops.launches - before)
@@ -290,10 +322,9 @@ class LLMEngine:
         if not batch:
             return None
         with _nvtx_range("prepare"):
-            rows, sample_seqs = [], []
+            rows, sample_seqs, decoding, others = [], [], [], []
             make_row = self.runner.make_row
-            pure_decode = True
-            for seq, n in batch:
+            for i, (seq, n) in enumerate(batch):
                 nc = seq.cache.num_computed
                 last = nc + n == len(seq.token_ids)
                 if nc + n <= seq.prompt_len:
@@ -305,44 +336,73 @@ class LLMEngine:
                 rows.append(make_row(seq.cache, tokens, (n - 1,) if last else ()))
                 if last:
                     sample_seqs.append(seq)
-                if n != 1 or not last:
-                    pure_decode = False
-            turn = self._turn ^ 1                              # the row of the pinned token buffer that this step fills
+                (decoding if n == 1 and last else others).append(i)
+            turn = self._turn ^ 1                              # the row of the pinned token buffers that this step fills
             # the seed of a sampled row: its own if it has one, else the engine's
             row_seeds = [self.cfg.seed if s.params.seed is None else s.params.seed for s in sample_seqs]
             seeds = {sd for sd, s in zip(row_seeds, sample_seqs) if s.params.temperature > 0}
-            use_graph = (pure_decode and self.graph_sizes and len(batch) <= self.graph_sizes[-1]
-                         and seeds <= {self.cfg.seed})
-            # sampling inputs ride in the step's buffer; a step replayed from a graph has its bucket's rows
-            bs = next(s for s in self.graph_sizes if s >= len(batch)) if use_graph else 0
-            extras = self._sampling_extras(
-                bs if use_graph else len(sample_seqs), [s.params.temperature for s in sample_seqs],
-                [s.seq_id for s in sample_seqs], [len(s.token_ids) - s.prompt_len for s in sample_seqs],
-                turn) if sample_seqs else None
+            graphs_ok = bool(self.graph_sizes) and len(decoding) <= self.graph_sizes[-1] and seeds <= {self.cfg.seed}
+            use_graph = graphs_ok and not others
+            # One prompt portion, alone or beside requests that decode, runs as a graph of its padded length
+            # -- beside the decode bucket's graph if there is one: two replays instead of some 200 launches
+            # that cost the host more than the step costs the device.  The rows of the two replays do not
+            # depend on one another, so the split changes nothing in what each computes.
+            portion_graph = (graphs_ok and self.cfg.use_cuda_graphs and self.cfg.graph_prompt_portions > 0
+                             and len(others) == 1 and len(rows[others[0]].tokens) >= self.PORTION_GRAPH_MIN_TOKENS
+                             and (not decoding or len(rows[others[0]].tokens) <= self.cfg.split_step_max_tokens))
+
+        def extras_for(seqs, pad_to):
+            if not seqs:
+                return self._sampling_extras(pad_to, turn=turn) if pad_to else None
+            return self._sampling_extras(pad_to or len(seqs), [s.params.temperature for s in seqs], [s.seq_id for s in seqs],
+                                         [len(s.token_ids) - s.prompt_len for s in seqs], turn)
 
         with _nvtx_range("forward"):
             b = self.runner.builder
-            k = len(sample_seqs)
-            pg = None
-            if (not use_graph and self.cfg.use_cuda_graphs and self.cfg.graph_prompt_portions > 0 and len(rows) == 1
-                    and len(rows[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and seeds <= {self.cfg.seed}):
-                pg = self._portion_graph(rows, extras, k)
-            if use_graph:
+            sources = []
+            if use_graph or (portion_graph and decoding):      # ---- the requests that decode, from their bucket's graph
+                drows = [rows[i] for i in decoding]
+                dseqs = [batch[i][0] for i in decoding]
+                bs = next(s for s in self.graph_sizes if s >= len(drows))
                 g = self.graphs[bs]
-                buf, layout = b.pack(rows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=extras)
+                buf, layout = b.pack(drows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=extras_for(dseqs, bs))
                 assert layout["size"] == g.layout["size"]
                 b.to_device(buf, g.layout, into=g.buffer)
                 g.graph.replay()
-                self.num_graph_steps += 1
                 self.h2d_bytes += buf.nbytes
-            elif pg is not None:                           # one portion of one prompt, of a shape seen before
-                buf, layout = b.pack(rows, table_width=self.max_blocks_per_seq, extras=extras)
-                assert layout["size"] == pg.layout["size"]
-                b.to_device(buf, pg.layout, into=pg.buffer)
-                pg.graph.replay()
-                self.num_portion_graph_steps += 1
+                sources.append((self._pinned_tokens[turn], len(dseqs)))
+                for k, seq in enumerate(dseqs):
+                    seq.pending_index = k
+                if use_graph:
+                    self.num_graph_steps += 1
+            if use_graph:
+                pass
+            elif portion_graph:                                # ---- the one prompt portion, from a graph of its padded length
+                row = rows[others[0]]
+                pseq = batch[others[0]][0]
+                pseqs = [pseq] if row.want else []
+                extras = extras_for(pseqs, 0) or self._sampling_extras(0, turn=turn)
+                pg = self._portion_graph(row, extras, len(pseqs))
+                tokens = self._sampled[self._portion_slot:self._portion_slot + len(pseqs)]
+                if pg is not None:
+                    buf, layout = b.pack(self._portion_rows(row, self._padded_length(len(row.tokens))),
+                                         table_width=self.max_blocks_per_seq, extras=extras)
+                    assert layout["size"] == pg.layout["size"]
+                    b.to_device(buf, pg.layout, into=pg.buffer)
+                    pg.graph.replay()
+                    self.num_portion_graph_steps += 1
+                else:                                          # the first time a shape occurs: launched kernel by kernel
+                    buf, layout = b.pack([row], extras=extras)
+                    ctx = b.to_device(buf, layout)
+                    ctx.token_feedback = self._sampled
+                    self._forward_and_sample(ctx, tokens, host_out=self._pinned_portion)
                 self.h2d_bytes += buf.nbytes
-            else:
+                if pseqs:
+                    sources.append((self._pinned_portion[turn], 1))
+                    pseq.pending_index = self._portion_slot
+            else:                                              # ---- any other mix: one batch, launched kernel by kernel
+                k = len(sample_seqs)
+                extras = extras_for(sample_seqs, 0)
                 buf, layout = b.pack(rows, extras=extras)
                 ctx = b.to_device(buf, layout)
                 ctx.token_feedback = self._sampled
@@ -359,10 +419,11 @@ class LLMEngine:
                                             ctx.extras["request"][i:i + 1], ctx.extras["out_position"][i:i + 1],
                                             out=self._sampled[i:i + 1], seed=sd)
                     self._pinned_tokens[turn, :k].copy_(self._sampled[:k], non_blocking=True)   # this rare way copies
+                sources.append((self._pinned_tokens[turn], k))
+                for k2, seq in enumerate(sample_seqs):
+                    seq.pending_index = k2
             self._turn = turn
-            pinned = self._pinned_tokens[turn]
-            if k:
-                self.d2h_bytes += 4 * k                        # written by the sampling kernel into pinned host memory
+            self.d2h_bytes += 4 * len(sample_seqs)             # written by the sampling kernel into pinned host memory
             done_event = torch.cuda.Event()
             done_event.record()
 
@@ -373,19 +434,18 @@ class LLMEngine:
             self.cache.advance(seq.cache, n)
         ending = []
         max_len = self.cfg.max_model_len
-        for i, seq in enumerate(sample_seqs):
-            seq.pending_index = i
+        for seq in sample_seqs:
             seq.token_ids.append(PENDING)
             total = len(seq.token_ids)
             if total - seq.prompt_len >= seq.params.max_tokens or total >= max_len:
                 self.scheduler.finish(seq)                 # its pages may go to the next step: that one runs after this one
                 ending.append(seq)
-        return _InFlight(sample_seqs, [s.num_tokens - 1 for s in sample_seqs], ending, pinned, done_event)
+        return _InFlight(sample_seqs, [s.num_tokens - 1 for s in sample_seqs], ending, sources, done_event)
 
     def _complete(self, fl) -> list:
         with _nvtx_range("sample"):
             fl.event.synchronize()
-            new_tokens = fl.pinned[:len(fl.seqs)].tolist()
+            new_tokens = fl.tokens()
         ops.check_range_errors()           # an integer out of range that a kernel refused to follow
         ops.check_tc_errors()
         gemm_tc.check_error()              # a bounded wait that ran out in a tensor-core product is an error, not a result

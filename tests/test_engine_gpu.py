@@ -229,10 +229,43 @@ def test_long_prompts_in_portions_replayed_from_graphs(dtype_name, model_folders
             res += eng.generate([p], SamplingParams(max_tokens=6, ignore_eos=True))
         outs[keep] = [o.output_ids for o in res]
         full = n // budget + (n - 5) // budget             # steps of exactly `budget` tokens that want no logits
-        assert eng.num_portion_graph_steps == (full - 1 if keep else 0), (eng.num_portion_graph_steps, full)
+        # the first of those is launched kernel by kernel, the rest replay its graph; the two prompts' last portions
+        # (24 and 19 tokens) are padded to the same 32 tokens: the second one replays what the first one left
+        assert eng.num_portion_graph_steps == (full - 1 + 1 if keep else 0), (eng.num_portion_graph_steps, full)
         assert eng.cache.num_free() == eng.cache.pools[0].num_usable
     assert outs[4] == outs[0]
     for p, ids in zip(prompts, outs[4]):
+        assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_a_portion_beside_decoding_requests_runs_as_two_graphs(dtype_name, model_folders):
+    """Requests arrive while others decode, under a small token budget: most steps hold one prompt portion
+    beside decoded tokens.  Such a step replays the decode bucket's graph and a graph of the portion's padded
+    length (its padding is a scratch row).  Same tokens as when those steps are launched kernel by kernel, and
+    the plain implementation's."""
+    dtype, rnd = DTYPES[dtype_name]
+    folder = model_folders["tiny_d"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(11)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (41, 7, 75, 33, 58, 19, 66, 90)]
+    from mini_inference_engine_b200 import SamplingParams
+    outs = {}
+    for keep in (16, 0):
+        eng = engine_for(folder, dtype, max_num_batched_tokens=24, max_num_seqs=4, graph_prompt_portions=keep)
+        res = eng.generate(prompts, SamplingParams(max_tokens=20, ignore_eos=True))
+        outs[keep] = [o.output_ids for o in res]
+        if keep:
+            assert eng.num_portion_graph_steps >= 8, eng.num_portion_graph_steps
+            # what is left for kernel-by-kernel launches: the first occurrence of a shape, and steps with two portions
+            assert eng.num_steps - eng.num_graph_steps - eng.num_portion_graph_steps < eng.num_portion_graph_steps
+        else:
+            assert eng.num_portion_graph_steps == 0
+        eng.cache.check()
+        assert eng.cache.num_free() == eng.cache.pools[0].num_usable
+    if dtype_name == "float32":
+        assert outs[16] == outs[0]
+    for p, ids in zip(prompts, outs[16]):
         assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
 
 
