@@ -20,7 +20,12 @@
 // block leaves its partial tile in its own shared memory and, after a barrier, reads its share out
 // of the others' (ld.shared::cluster); a second barrier keeps everyone's memory alive meanwhile.
 // Either way the sum runs in rank order -- the same order every time -- with no global partial
-// sums, no atomics and no second kernel.
+// sums, no atomics and no second kernel.  SWAPPED with 64 tokens or more (BN >= 64): a block owns
+// TOKENS, not rows -- BN / splits tokens of every row of the tile.  Its peers stage their partial
+// tile in their own shared memory, laid out by owner, and send each owner its 4 KB with ONE bulk copy
+// (cp.async.bulk shared::cta -> shared::cluster, counted on the owner's mbarrier) instead of two
+// thousand 16-byte remote stores; the owner's thread r adds up row r for its tokens, and what it then
+// writes -- a token's features, side by side across the warp -- is contiguous in memory.
 //
 // Programmatic dependent launch: the kernel lets its successor start at once
 // (griddepcontrol.launch_dependents) and itself may start while its predecessor still runs.  Weights
@@ -157,6 +162,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     // SWAPPED split-K sends partial rows into the peers' shared memory.  A block may be written to only
     // once it runs: everybody arrives here, and waits (long since satisfied) before its first send.
     const bool push = SWAPPED && p.push;
+    // tokens, not rows, are owned (see the header comment): 4 to 16 tokens per owner
+    const int tpo = BN / (p.splits > 0 ? p.splits : 1);
+    const bool tok = push && BN >= 64 && tpo >= 4 && tpo <= 16;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TC_BM;          // first row of the 128-row operand
@@ -310,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                 if (sub == 0 && i < BN) rstd_s[i] = t < p.M ? rsqrtf(sum / p.sq_width + p.sq_eps) : 1.f;
             }                                                // read after the block-wide barrier below
         }
-        if (p.res) {
+        if (p.res && !tok) {
             // the stream values that this thread will add to (its first item of the owners' sum below) and
             // the norm weight of its feature are fetched now, not at the end of the kernel
             grid_dep_wait();
@@ -334,6 +342,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             float* red = reinterpret_cast<float*>(tiles);     // the ring is free: every MMA has read its slot
             // where row r of the partial tile goes: the owner's slot for this sender (see the sum below)
             uint32_t send_to = 0, send_bar = 0;
+            if (tok) {
+                // the partial tile goes to this block's own shared memory first, laid out [owner][row][tpo tokens];
+                // then one bulk copy per owner
+                const int t_shift = 31 - __clz(tpo);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    if (have_work) tmem_ld16(taddr + c, v);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) {
+                        const int tk = c + i, o = tk >> t_shift, j = tk & (tpo - 1);
+                        *reinterpret_cast<float4*>(red + ((o * TC_BM + r) << t_shift) + j) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy engine reads what these threads wrote
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int et = threadIdx.x - 64;
+                if (et < p.splits) {
+                    const uint32_t bytes = (uint32_t)(TC_BM * tpo) * 4u;
+                    const uint32_t dst = cluster_addr(tiles_base + p.recv_smem_offset, et) + (uint32_t)split * bytes;
+                    const uint32_t bar = cluster_addr(smem_u32(&recv_bar), et);
+                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(dst), "r"(tiles_base + (uint32_t)et * bytes), "r"(bytes), "r"(bar) : "memory");
+                }
+            } else {
             if (push) {
                 const int S = p.splits, rows_per = TC_BM / S;              // powers of two: masks and shifts
                 const int s_shift = 31 - __clz(S), rows_shift = 31 - __clz(rows_per);
@@ -402,6 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                     }
                 }
             }
+            }
         }
     }
 
@@ -418,11 +456,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
         bool have_all = true;
         if (push) { if (warp >= 2) have_all = mbar_wait(&recv_bar, 0, abort_p); }
         else cluster_sync_all();
+        // bulk copies read the SENDER's shared memory: nobody leaves before every owner has what it is owed
+        if (tok) cluster_arrive_release();
         const int S = p.splits;
         const int rows_per = TC_BM / S;                      // S is 2, 4 or 8
         const int rows_shift = 31 - __clz(rows_per);         // rows_per is a power of two: shifts, no divisions, on this last stretch
         const int r_lo = split * rows_per;
-        if (warp >= 2 && !aborted && have_all) {
+        if (tok && warp >= 2 && !aborted && have_all) {
+            // ---- tokens are owned: thread r adds up row r of the tile for this block's tpo tokens
+            const int r = threadIdx.x - 64, t_shift = 31 - __clz(tpo);
+            float* recv = reinterpret_cast<float*>(tiles + p.recv_smem_offset);        // [sender][row][tpo]
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int s2 = 0; s2 < 8; ++s2) {
+                if (s2 < S) {
+                    const float4* src = reinterpret_cast<const float4*>(recv + ((s2 * TC_BM + r) << t_shift));
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        if (j4 * 4 < tpo) {
+                            const float4 f = src[j4];
+                            acc[j4 * 4] += f.x; acc[j4 * 4 + 1] += f.y; acc[j4 * 4 + 2] += f.z; acc[j4 * 4 + 3] += f.w;
+                        }
+                    }
+                }
+            }
+            const int tk0 = split * tpo;                     // this block's first token within the tile
+            if (p.sq_in) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (j < tpo) acc[j] *= rstd_s[tk0 + j];
+            }
+            const int n = a0 + r;
+            const bool live = n < p.N;
+            const float b = (p.bias && live) ? load_tagged(p.bias, n, p.bias_tag) : 0.f;
+            if (p.rope) {
+                // the rotation partner's sums come through shared memory: every row of the tile is here
+                const int D = p.head_dim, half = p.rotary_dim >> 1;
+                const int hd = n >> (31 - __clz(D)), d = n & (D - 1);
+                const bool rotated = live && hd < p.num_heads + p.num_kv_heads && d < p.rotary_dim;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (j < tpo) recv[(r << t_shift) + j] = acc[j] + b;      // slot 0 of this row: read by this thread only, above
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int rp = rotated ? (d < half ? r + half : r - half) : r;
+                if (live) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tk = tk0 + j, t = b0 + tk;
+                        if (j >= tpo || t >= p.M) continue;
+                        float val = acc[j] + b;
+                        if (rotated) {
+                            const int jj = d < half ? d : d - half;
+                            const float cs = rope_cs[tk * half + jj], sn = rope_cs[BN * half + tk * half + jj];
+                            const float other = recv[(rp << t_shift) + j];
+                            val = d < half ? val * cs - other * sn : val * cs + other * sn;
+                        }
+                        if (hd < p.num_heads) {
+                            store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
+                        } else if (p.write_cache) {
+                            const int slot = rope_slot[tk];
+                            if (slot < 0) continue;
+                            const int page = slot >> p.page_shift, off = slot & (p.page_size - 1);
+                            const bool is_k = hd < p.num_heads + p.num_kv_heads;
+                            const int kvh = hd - p.num_heads - (is_k ? 0 : p.num_kv_heads);
+                            const int64_t dst = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + off) * D + d;
+                            (is_k ? p.k_cache : p.v_cache)[dst] = __float2bfloat16_rn(val);
+                        }
+                    }
+                }
+            } else if (p.res) {
+                const float wn = (p.norm_w && live) ? load_tagged(p.norm_w, n, p.norm_w_tag) : 0.f;
+                float old[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    old[j] = (j < tpo && live && b0 + tk0 + j < p.M) ? __ldcg(p.res + (int64_t)(b0 + tk0 + j) * p.N + n) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j >= tpo) continue;
+                    const int t = b0 + tk0 + j;
+                    float sq = 0.f;
+                    if (live && t < p.M) {
+                        const int64_t at = (int64_t)t * p.N + n;
+                        const float rv = old[j] + acc[j] + b;
+                        p.res[at] = rv;
+                        if (p.xw_out) p.xw_out[at] = __float2bfloat16_rn(rv * wn);
+                        sq = rv * rv;
+                    }
+                    if (p.sq_out) {                            // a warp holds 32 rows of the tile: one slot per warp and tile
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        if (lane == 0 && t < p.sq_stride) p.sq_out[(int64_t)(blockIdx.x * 4 + (warp - 2)) * p.sq_stride + t] = sq;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j >= tpo) continue;
+                    const int t = b0 + tk0 + j;
+                    const float val = acc[j] + b;
+                    if (p.swiglu) {                            // gate on the even row, up on the odd one: neighbouring lanes
+                        const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                        if (!(r & 1) && t < p.M && live) store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                    } else if (t < p.M && live) {
+                        store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
+                    }
+                }
+            }
+        } else if (warp >= 2 && !aborted && have_all) {
             const int tid = threadIdx.x - 64;                // 0..127
             uint32_t peer[8];
 #pragma unroll
@@ -578,6 +718,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
             }
         }
         if (!push) cluster_sync_all();                       // nobody leaves while its shared memory is being read
+        if (tok) cluster_wait_acquire();                     // every owner has received: the staged tile may go
     }
 
     __syncthreads();

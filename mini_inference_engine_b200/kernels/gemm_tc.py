@@ -228,6 +228,16 @@ def _chain_submit(x, w, bias, out, M, N, K, swiglu, fuse: "_Fuse", rope_args) ->
         flush_chain()
 
 
+def sq_slots(N: int, pl: dict) -> int:
+    """Shares of sum(res^2) per token that the residual epilogue writes under plan ``pl``: one per 128-row tile and
+    group of 16 or 32 rows where blocks own rows; one per tile and warp where they own tokens (tiles of 64 tokens
+    and more, 4 to 16 tokens an owner)."""
+    tiles = -(-N // 128)
+    if pl["bn"] >= 64 and 4 <= pl["bn"] // pl["splits"] <= 16:
+        return tiles * 4
+    return tiles * max(pl["splits"], 4)
+
+
 def splits_k(M: int, N: int, K: int) -> bool:
     """Whether the plan for these sizes puts the weight on the 128-row side and splits K across a
     cluster: the form whose owners' sum carries the rotation, residual and norm-factor epilogues."""
@@ -276,7 +286,7 @@ def gemm_residual(x, w: torch.Tensor, res: torch.Tensor, bias=None, norm_weight=
     xw = sq = None
     chain = not force and chain_takes(M, N, K)
     if norm_weight is not None:
-        slots = chain_slots(N) if chain else -(-N // 128) * max(pl["splits"], 4)
+        slots = chain_slots(N) if chain else sq_slots(N, pl)
         xw = torch.empty(M, N, dtype=torch.bfloat16, device=res.device)
         sq = torch.empty(slots, max(M, pl["bn"] * -(-M // pl["bn"])), dtype=torch.float32, device=res.device)
         out = DeferredNorm(xw, sq, slots, N, eps)

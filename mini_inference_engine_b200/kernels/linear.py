@@ -15,10 +15,12 @@ import torch
 from . import gemm_tc, ops
 
 _bf16_backend = "auto"
-AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen05 kernel (whole decode step, B200:
-                              # 24 tokens 1.057 ms against 1.098 ms with the library, 32 tokens 1.078 against 1.136 ms,
-                              # 48 tokens 1.61 against 1.18 ms: with the 64-token tile the partial rows' way to their
-                              # owners and the owners' sums take 25 us a layer instead of 8)
+AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen05 kernel.  Whole decode step, TinyLlama-1.1B
+                              # sizes on a B200: 24 tokens 1.057 ms against 1.098 ms with the library, 32 tokens 1.078 against
+                              # 1.136 ms; with the 64-token tile (33 tokens and more) 1.417 / 1.510 / 1.575 ms at 33 / 48 / 64
+                              # tokens against 1.18 / 1.22 ms with the library at 48 / 64 -- although blocks then own tokens
+                              # and receive their partial sums as bulk copies (1.61 -> 1.51 ms at 48 tokens): three ring
+                              # stages of 24 KB instead of five of 18 KB leave each block too little in flight
 
 
 def set_bf16_backend(name: str) -> None:

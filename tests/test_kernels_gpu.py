@@ -625,7 +625,10 @@ def test_prefill_attention_tc_skips_single_token_rows(ops):
 
 
 @pytest.mark.parametrize("H,Hkv,D,rot,M,K", [(32, 4, 64, 64, 8, 2048), (4, 2, 16, 16, 3, 256), (3, 1, 32, 32, 16, 384),
-                                             (8, 8, 128, 64, 5, 512), (2, 1, 64, 0, 7, 256), (32, 8, 128, 128, 32, 4096)])
+                                             (8, 8, 128, 64, 5, 512), (2, 1, 64, 0, 7, 256), (32, 8, 128, 128, 32, 4096),
+                                             # 33 tokens and more: blocks own tokens instead of rows
+                                             (32, 4, 64, 64, 64, 2048), (32, 4, 64, 64, 41, 2048), (6, 2, 32, 32, 50, 512),
+                                             (8, 8, 128, 64, 64, 1024)])
 def test_gemm_tc_fused_rotation_and_cache_write(ops, H, Hkv, D, rot, M, K):
     """The q|k|v product with rotation and cache write in its epilogue against the plain formulas."""
     from mini_inference_engine_b200.kernels import gemm_tc
@@ -671,7 +674,8 @@ def test_gemm_tc_fused_rotation_and_cache_write(ops, H, Hkv, D, rot, M, K):
     assert (vc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 2048, 2048), (1, 2048, 5632), (16, 2048, 5632), (13, 264, 320), (5, 1000, 840), (3, 128, 256)])
+@pytest.mark.parametrize("M,N,K", [(8, 2048, 2048), (1, 2048, 5632), (16, 2048, 5632), (13, 264, 320), (5, 1000, 840), (3, 128, 256),
+                                   (64, 2048, 2048), (33, 2048, 5632), (57, 264, 512), (64, 1000, 840)])
 @pytest.mark.parametrize("with_norm", [True, False])
 def test_gemm_tc_residual_epilogue(M, N, K, with_norm):
     """res += x W^T + b on the float32 stream, and for the norm behind it xw = bf16(res * w_norm) and
@@ -705,7 +709,8 @@ def test_gemm_tc_residual_epilogue(M, N, K, with_norm):
         x.to(DEV), w.to(DEV), res0.clone().to(DEV), b.to(DEV), nw.to(DEV), 1e-5).sq[:, :M])
 
 
-@pytest.mark.parametrize("M,h,N", [(8, 2048, 2560), (16, 2048, 11264), (3, 264, 400), (1, 2048, 2048)])
+@pytest.mark.parametrize("M,h,N", [(8, 2048, 2560), (16, 2048, 11264), (3, 264, 400), (1, 2048, 2048), (64, 2048, 11264),
+                                   (47, 2048, 2560), (64, 520, 400)])
 @pytest.mark.parametrize("swiglu", [False, True])
 def test_gemm_tc_deferred_norm_factor(ops, M, h, N, swiglu):
     """RMSNorm split across two products: the first leaves res * w and sum(res^2), the second scales its
