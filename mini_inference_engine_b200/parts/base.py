@@ -157,8 +157,13 @@ class Runtime:
     def product_sources(self, *weights) -> set:
         """The kernel sources behind ``linear`` for these weights."""
         if self.dtype == torch.float32 or any(w is not None and w.dtype == torch.float32 for w in weights):
-            return {"gemm_simt"} if self.dtype == torch.float32 else {"gemm_simt", "gemm_tcgen05", "gemm_chain"}
-        return {"gemm_tcgen05", "gemm_chain"}
+            return {"gemm_simt"} if self.dtype == torch.float32 else {"gemm_simt"} | self._tc_sources()
+        return self._tc_sources()
+
+    @staticmethod
+    def _tc_sources() -> set:
+        from ..kernels import gemm_tc
+        return {"gemm_tcgen05", "gemm_chain"} if gemm_tc.chain_enabled else {"gemm_tcgen05"}
 
     def step_scope(self):
         """A context for one step of a model: in bfloat16 the fused few-token products queued inside it go
