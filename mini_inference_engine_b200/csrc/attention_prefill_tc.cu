@@ -464,6 +464,385 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     }
 }
 
+// --------------------------------------------------------------------------- two query tiles side by side
+//
+// The kernel above leaves the tensor pipe idle while a block's four softmax warps work and the exponent
+// unit idle while its MMA thread issues; two blocks on an SM interleave only by chance.  This one
+// makes the interleaving a schedule (head_dim 64): a block holds TWO consecutive query tiles of a row
+// (256 queries of one head) and two groups of four softmax warps, one per tile.  They share the key
+// and value tiles (loaded once for both) and the MMA thread, which alternates: while group 0 takes its
+// scores of key tile j through the softmax, the tensor pipe works on S1(j) and on P1 V of the tile
+// before, and the other way round.  TMEM holds S0, S1 (2 x 128 columns), P0, P1 (2 x 64) and O0, O1
+// (2 x 64): all 512.  A softmax thread moves its whole row of S into registers at once and gives S back
+// (s_free), so that the group's scores of the next key tile are computed while its exponentials run.
+// Each group has an MMA-issuing thread of its own (warps 1 and 10): issuing costs a thread 90 - 150
+// cycles per tcgen05.mma here (measured with cycle stamps: one thread serving both groups needed 3,400
+// cycles a key tile, more than both softmaxes), and twelve MMAs go into every (query tile, key tile).
+// Per key tile j the thread of group u issues S_u(j + 1) as soon as s_free says so, then P_u V(j) when
+// the group delivers P (p_full).  Blocks are numbered longest first (the last pair of a row has the
+// most keys), so that short ones fill the tail.
+#define PP_THREADS 352
+#define PP_STAGES 3
+
+// Diagnostic build (-DPP_TRACE): cycle stamps of the first block's roles per key tile; not compiled otherwise.
+#ifdef PP_TRACE
+__device__ long long g_pp_trace[64 * 16];
+#define PP_STAMP(who, j, slot) if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 16) g_pp_trace[((who) * 16 + (j)) * 16 / 4 + (slot)] = clock64()
+extern "C" int mie_pp_trace(long long* out, int count) { return (int)cudaMemcpyFromSymbol(out, g_pp_trace, sizeof(long long) * count); }
+#else
+#define PP_STAMP(who, j, slot)
+#endif
+
+__global__ void __launch_bounds__(PP_THREADS, 1)
+prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+    constexpr int D = 64;
+    constexpr uint32_t SUB_BYTES = 128 * 64 * 2;                // one [128 rows x 64] tile
+    constexpr uint32_t Q_BYTES = SUB_BYTES, KV_BYTES = SUB_BYTES;
+    constexpr uint32_t TMEM_S = 0, TMEM_P = 256, TMEM_O = 384;  // per group u: S + 128 u, P + 64 u, O + 64 u
+    constexpr uint32_t TMEM_COLS = 512;
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t q_full[2], kv_full[PP_STAGES], kv_empty[PP_STAGES], s_full[2], s_free[2], p_full[2], pv_done[2], o_full[2];
+    __shared__ __align__(8) uint64_t exp_done[2];             // a group has run the exponentials of one more key tile
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag, s_row, s_q0, s_nsub;
+
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* tiles = smem_dyn + (base - smem_u32(smem_dyn));
+    // layout: Q0 | Q1 | (K, V) x PP_STAGES
+    auto q_addr = [&](int u) { return base + (uint32_t)u * Q_BYTES; };
+    auto k_addr = [&](int s) { return base + 2 * Q_BYTES + (uint32_t)s * 2 * KV_BYTES; };
+    auto v_addr = [&](int s) { return base + 2 * Q_BYTES + (uint32_t)s * 2 * KV_BYTES + KV_BYTES; };
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int u = 0; u < 2; ++u) {
+            mbar_init(&q_full[u], 1); mbar_init(&s_full[u], 1); mbar_init(&s_free[u], 4); mbar_init(&p_full[u], 4);
+            mbar_init(&pv_done[u], 1); mbar_init(&o_full[u], 1); mbar_init(&exp_done[u], 4);
+        }
+        for (int s = 0; s < PP_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 2); }     // both MMA threads release a stage
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // key/value rows that no copy fills (beyond the context) must hold finite values: 0 * NaN is NaN
+    for (uint32_t i = threadIdx.x * 16; i < PP_STAGES * 2 * KV_BYTES; i += PP_THREADS * 16)
+        *reinterpret_cast<uint4*>(tiles + 2 * Q_BYTES + i) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pdl_wait();
+
+    if (threadIdx.x == 0) {
+        // which row and which pair of query tiles: pairs are numbered from the row's end
+        int pair = blockIdx.y, r = 0, tiles_r = 0;
+        for (; r < p.num_rows; ++r) {
+            const int ql = p.row_q_len[r];
+            tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
+            const int pairs_r = (tiles_r + 1) / 2;
+            if (pair < pairs_r) break;
+            pair -= pairs_r;
+        }
+        s_row = r < p.num_rows ? r : -1;
+        const int first = ((tiles_r + 1) / 2 - 1 - pair) * 2;        // the pair's first tile
+        s_q0 = first * FA_BM;
+        s_nsub = first + 1 < tiles_r ? 2 : 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+    const int row = s_row;
+
+    if (row >= 0) {
+        const int q_len = p.row_q_len[row], ctx = p.row_ctx_len[row], q_start = p.row_q_start[row];
+        const int head = blockIdx.x;                            // heads vary fastest: the longest pairs of ALL heads start first
+        const int kvh = head / (p.num_heads / p.num_kv_heads);
+        const int nsub = s_nsub;
+        struct Sub { int q0, pos0, nq, k_hi, k_lo; };
+        Sub sb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            Sub& g = sb[u];
+            g.q0 = s_q0 + (u < nsub ? u : 0) * FA_BM;
+            g.pos0 = ctx - q_len + g.q0;
+            g.nq = min(FA_BM, q_len - g.q0);
+            g.k_hi = g.pos0 + g.nq;
+            g.k_lo = p.window > 0 ? max(0, g.pos0 - p.window + 1) : 0;
+        }
+        // one grid of key tiles for both query tiles, from the first key the first tile reads
+        const int kbeg = sb[0].k_lo & ~(FA_BN - 1);
+        const int k_hi0 = sb[0].k_hi, k_lo0 = sb[0].k_lo, k_hi1 = nsub > 1 ? sb[1].k_hi : 0, k_lo1 = sb[1].k_lo;
+        const int k_end = nsub > 1 ? k_hi1 : k_hi0;
+        const int J = (k_end - kbeg + FA_BN - 1) / FA_BN;
+        // is key tile j read by query tile u?  (the same answer in every role; the second tile of a lone one reads nothing)
+        auto active = [&](int u, int j) {
+            const int key0 = kbeg + j * FA_BN;
+            return u == 0 ? (key0 < k_hi0 && key0 + FA_BN > k_lo0) : (key0 < k_hi1 && key0 + FA_BN > k_lo1);
+        };
+        const int rows_per_copy = min(p.page_size, FA_BN);
+
+        if (warp == 0) {
+            // ---- producer (as in the kernel above): lane c copies page c of a key tile
+            const int* table = p.block_tables + (int64_t)row * p.table_stride;
+            if (lane == 0) {
+                for (int u = 0; u < nsub; ++u) {
+                    mbar_expect_tx(&q_full[u], Q_BYTES);
+                    tma_load_2d(tiles + u * Q_BYTES, &map_q, &q_full[u], head * D, q_start + sb[u].q0);
+                }
+            }
+            auto copies_of = [&](int j) {
+                const int key0 = kbeg + j * FA_BN;
+                return (min(key0 + FA_BN, k_end) - key0 + rows_per_copy - 1) / rows_per_copy;
+            };
+            auto page_of = [&](int j) {
+                if (j >= J || lane >= copies_of(j)) return 0;
+                const int entry = (kbeg + j * FA_BN + lane * rows_per_copy) >> p.page_shift;
+                return checked_page(table[entry], p.check_pages, p.report, MIE_K_ATTENTION_PREFILL_TC, entry);
+            };
+            int page_next = page_of(0);
+            int s = 0, round = 0;
+            for (int j = 0; j < J; ++j) {
+                const int page = page_next;
+                page_next = page_of(j + 1);
+                int ok = 1;
+                if (lane == 0 && round > 0) ok = mbar_wait(&kv_empty[s], (round & 1) ^ 1, abort_p) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const int copies = copies_of(j);
+                if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)copies * rows_per_copy * 128u * 2u);
+                __syncwarp();
+                if (lane < copies) {
+                    const int key = kbeg + j * FA_BN + lane * rows_per_copy;
+                    const int src_row = (page * p.num_kv_heads + kvh) * p.page_size + (key & (p.page_size - 1));
+                    const uint32_t off = (uint32_t)lane * rows_per_copy * 128u;
+                    tma_load_2d(tiles + (k_addr(s) - base) + off, &map_k, &kv_full[s], 0, src_row);
+                    tma_load_2d(tiles + (v_addr(s) - base) + off, &map_v, &kv_full[s], 0, src_row);
+                }
+                if (++s == PP_STAGES) { s = 0; ++round; }
+            }
+        } else if (warp == 1 || warp == 10) {
+            if (lane == 0) {
+                // ---- the MMA thread of group mu
+                const int mu = warp == 1 ? 0 : 1;
+                const uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN);
+                const uint32_t idesc_o = umma_idesc_bf16(FA_BM, D) | (1u << 16);
+                constexpr int KS = D / 16, KV = FA_BN / 16;
+                uint64_t dq[KS];
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) dq[ks] = umma_desc_sw128(q_addr(mu) + ks * 32);
+                const uint64_t dk0 = umma_desc_sw128(k_addr(0)), dv0 = umma_desc_sw128_mn(v_addr(0), SUB_BYTES);
+                constexpr uint64_t STAGE_STEP = (2 * KV_BYTES) >> 4;       // descriptors of another stage differ in the address field only
+                const uint32_t s_at = tmem_base + TMEM_S + 128u * mu, p_at = tmem_base + TMEM_P + 64u * mu, o_at = tmem_base + TMEM_O + 64u * mu;
+                auto issue_s = [&](int st) {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks)
+                        umma_bf16(s_at, dq[ks], dk0 + STAGE_STEP * st + (uint64_t)(ks * 2), idesc_s, ks > 0 ? 1u : 0u);
+                    umma_commit(&s_full[mu]);
+                };
+                bool ok = mu < nsub ? mbar_wait(&q_full[mu], 0, abort_p) : true;
+                int st = 0, round = 0, taken = 0, uses = 0;
+                if (ok && active(mu, 0)) {
+                    ok = mbar_wait(&kv_full[0], 0, abort_p);
+                    if (ok) { tc_fence_after(); issue_s(0); }
+                }
+                for (int j = 0; j < J && ok; ++j) {
+                    const int st_next = st + 1 == PP_STAGES ? 0 : st + 1, round_next = st + 1 == PP_STAGES ? round + 1 : round;
+                    const bool now = active(mu, j), next = j + 1 < J && active(mu, j + 1);
+                    PP_STAMP(2 + mu, j, 0);
+                    if (next) {
+                        // the group's next scores: as soon as it has moved its scores of tile j into registers (s_free),
+                        // or at once when tile j + 1 is its first
+                        if (now) { ok = mbar_wait(&s_free[mu], taken & 1, abort_p); ++taken; }
+                        if (ok) ok = mbar_wait(&kv_full[st_next], round_next & 1, abort_p);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(st_next);
+                    }
+                    PP_STAMP(2 + mu, j, 1);
+                    if (now) {
+                        ok = mbar_wait(&p_full[mu], uses & 1, abort_p);    // P(j) is written, O rescaled
+                        if (!ok) break;
+                        tc_fence_after();
+                        PP_STAMP(2 + mu, j, 2);
+#pragma unroll
+                        for (int kk = 0; kk < KV; ++kk)
+                            umma_bf16_ts(o_at, p_at + kk * 8, dv0 + STAGE_STEP * st + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                                         (uses > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&pv_done[mu]);                         // P may be overwritten, O rescaled
+                        ++uses;
+                        if (!next) {
+                            umma_commit(&o_full[mu]);                      // this tile's output is complete
+                            ++taken;                                       // (its last s_free is never awaited)
+                        }
+                    }
+                    // A thread whose group does not read this key tile still gives the stage back, but only once the
+                    // stage has been filled: running ahead, its arrivals would count for rounds that are not its own.
+                    if (!now) { ok = mbar_wait(&kv_full[st], round & 1, abort_p); if (!ok) break; }
+                    umma_commit(&kv_empty[st]);                            // what this thread issued on the stage is accounted for
+                    PP_STAMP(2 + mu, j, 3);
+                    st = st_next; round = round_next;
+                }
+            }
+        } else {
+            // ---- softmax group u = 0 (warps 2..5) or 1 (warps 6..9): the row code of the kernel above
+            const int u = warp >= 6 ? 1 : 0;
+            const int q = warp & 3;                                // TMEM lane quarter = warp id % 4
+            const int r = q * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t S_AT = lane_addr + TMEM_S + 128u * u, P_AT = lane_addr + TMEM_P + 64u * u, O_AT = lane_addr + TMEM_O + 64u * u;
+            bool ok = true;
+            if (u < nsub) {
+                const int q0 = u ? sb[1].q0 : sb[0].q0, pos0 = u ? sb[1].pos0 : sb[0].pos0, nq = u ? sb[1].nq : sb[0].nq;
+                const int k_lo = u ? k_lo1 : k_lo0;
+                const int qpos = pos0 + r;
+                float m_run = -INFINITY, l_run = 0.f;
+                int used = 0;                                      // key tiles this group has taken
+                // The two groups take turns at the exponent unit: with both in it at once each takes twice as long
+                // and both then wait for their scores at the same time.  Group 0 goes first; the k-th turn of group 1
+                // follows the k-th of group 0, the (k+1)-th of group 0 the k-th of group 1, as far as the other has turns.
+                int turns_other = 0;
+                for (int j = 0; j < J; ++j) turns_other += active(u ^ 1, j) ? 1 : 0;
+                for (int j = 0; j < J && ok; ++j) {
+                    if (!active(u, j)) continue;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&s_full[u], used & 1, abort_p));
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (q == 2 && lane == 0) { PP_STAMP(u, j, 0); }
+                    const int key0 = kbeg + j * FA_BN;
+                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
+                    // The whole row of S moves into registers at once and S is given back (s_free): the MMA thread
+                    // issues this group's scores of the next key tile while the exponentials below run out of
+                    // registers.  A row that has to be redone against a new maximum is redone from registers too.
+                    uint32_t sv[128];
+                    tmem_ld32_async(S_AT, sv);
+                    tmem_ld32_async(S_AT + 32, sv + 32);
+                    tmem_ld32_async(S_AT + 64, sv + 64);
+                    tmem_ld32_async(S_AT + 96, sv + 96);
+                    tmem_ld_wait(sv); tmem_ld_wait(sv + 32); tmem_ld_wait(sv + 64); tmem_ld_wait(sv + 96);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s_free[u]);
+                    if (q == 2 && lane == 0) { PP_STAMP(u, j, 1); }
+                    auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
+                    if (need_mask) {                               // masked entries become -inf once, here
+#pragma unroll
+                        for (int i = 0; i < 128; ++i) if (masked(key0 + i)) sv[i] = __float_as_uint(-INFINITY);
+                    }
+                    // The row's maximum comes out of the registers first (no second pass over TMEM as in the kernel
+                    // above); the reference point of the exponent moves only when an entry would exceed 2^8 against the
+                    // one in use, so that O is rescaled in the first tiles of a row and hardly ever after.
+                    float alpha = 1.f, sum;
+                    {
+                        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+                        if (mx > -INFINITY && (m_run == -INFINITY || mx - m_run > 8.0f)) {
+                            alpha = m_run == -INFINITY ? 1.f : ex2_approx(m_run - mx);
+                            m_run = mx;
+                        }
+                    }
+                    // P of the tile before must have been read by its product before it is overwritten, and O is
+                    // rescaled only once that product is complete
+                    if (used > 0 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[u], (used - 1) & 1, abort_p))) { ok = false; break; }
+                    if (q == 2 && lane == 0) { PP_STAMP(u, j, 2); }
+                    {
+                        const int wait_for = u == 0 ? used - 1 : used;       // the other group's turn that comes before this one
+                        if (wait_for >= 0 && wait_for < turns_other &&
+                            !__all_sync(0xffffffffu, mbar_wait(&exp_done[u ^ 1], wait_for & 1, abort_p))) { ok = false; break; }
+                    }
+                    {
+                        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+                        float sm[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t packed[16];
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float p0 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i]), p.scale_log2e, neg_m));
+                                const float p1 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2e, neg_m));
+                                sm[(i >> 1) & 3] += p0 + p1;
+                                packed[i >> 1] = pack2_bf16(p0, p1);
+                            }
+                            tmem_st16(P_AT + ch * 16, packed);
+                        }
+                        sum = (sm[0] + sm[1]) + (sm[2] + sm[3]);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&exp_done[u]);      // the other group's turn
+                    l_run = l_run * alpha + sum;
+                    if (used > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                        for (int c = 0; c < D; c += 16) {
+                            float v[16];
+                            tmem_ld16(O_AT + c, v);
+                            uint32_t w[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i] * alpha);
+                            tmem_st8(O_AT + c, w);
+                            tmem_st8(O_AT + c + 8, w + 8);
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_full[u]);
+                    if (q == 2 && lane == 0) { PP_STAMP(u, j, 3); }
+                    ++used;
+                }
+                if (ok) ok = mbar_wait(&o_full[u], 0, abort_p);
+                tc_fence_after();
+                __syncwarp();
+                if (__all_sync(0xffffffffu, ok)) {
+                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                    bf16* op = p.out + ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 16) {
+                        float v[16];
+                        tmem_ld16(O_AT + c, v);
+                        if (r >= nq) continue;
+                        uint4 w0, w1;
+                        w0.x = pack2_bf16(v[0] * inv, v[1] * inv); w0.y = pack2_bf16(v[2] * inv, v[3] * inv);
+                        w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
+                        w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
+                        w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
+                        *reinterpret_cast<uint4*>(op + c) = w0;
+                        *reinterpret_cast<uint4*>(op + c + 8) = w1;
+                    }
+                    tc_fence_before();
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.error, 1);
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+static int launch_fa_pp(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
+                        cudaStream_t stream) {
+    const size_t smem = (size_t)128 * 64 * 2 * (2 + 2 * PP_STAGES) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int tiles = (num_tokens + FA_BM - 1) / FA_BM + p.num_rows;
+    const dim3 grid(p.num_heads, (tiles + p.num_rows + 1) / 2);
+    return launch_kernel(prefill_attention_pp_kernel, grid, dim3(PP_THREADS), smem, stream, mq, mk, mv, p);
+}
+
 // --------------------------------------------------------------------------- host side
 
 static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride_elems, int box_rows) {
@@ -476,6 +855,8 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
+
+static int g_fa_pp_mode = -1;
 
 template <int D>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
@@ -525,9 +906,22 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     if ((rc = make_map_2d(&mq, q, (uint64_t)num_tokens, (uint64_t)q_stride, (uint64_t)q_stride, FA_BM))) return rc;
     if ((rc = make_map_2d(&mk, k_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
     if ((rc = make_map_2d(&mv, v_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
-    if (head_dim == 64) return launch_fa<64>(mq, mk, mv, p, num_tokens, stream);
+    if (head_dim == 64) {
+        // two query tiles side by side once there are two pairs for every SM (measured, 32 heads: 2,048 tokens 48.9 against
+        // 49.5 us, 4,096 tokens 143 against 157 us, 8,192 tokens 462 against 532 us; 1,024 tokens 25.1 against 24.4 us);
+        // below that the one-tile blocks, two on an SM, spread a small launch over more SMs
+        const int64_t tiles = (num_tokens + FA_BM - 1) / FA_BM;
+        if ((tiles + 2 * num_rows) / 2 < 65535 &&
+            (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 4 * (int64_t)device_sm_count())))
+            return launch_fa_pp(mq, mk, mv, p, num_tokens, stream);
+        return launch_fa<64>(mq, mk, mv, p, num_tokens, stream);
+    }
     return launch_fa<128>(mq, mk, mv, p, num_tokens, stream);
 }
+
+// Which kernel serves head_dim 64: -1 chooses by the size of the launch (the default), 0 always one query tile a block,
+// 1 always two side by side.
+extern "C" void mie_prefill_attention_tc_pairs(int mode) { g_fa_pp_mode = mode; }
 
 extern "C" int mie_prefill_attention_tc_error(void) { return g_error_host ? *g_error_host : 0; }
 extern "C" void mie_prefill_attention_tc_clear_error(void) { if (g_error_host) *g_error_host = 0; }

@@ -141,15 +141,6 @@ class LLMEngine:
             self._capture_cuda_graphs()
 
     # ------------------------------------------------------------------ CUDA graphs of decode steps
-    def _sampling_extras(self, n, temps=None, reqs=None, outpos=None, turn=0):
-        t = np.zeros(n, dtype=np.float32)
-        r = np.zeros(n, dtype=np.int64)
-        p = np.zeros(n, dtype=np.int32)
-        if temps is not None:
-            k = len(temps)
-            t[:k], r[:k], p[:k] = temps, reqs, outpos
-        return {"temperature": t, "request": r, "out_position": p, "host_turn": np.array([turn], dtype=np.int32)}
-
     def _forward_and_sample(self, ctx, tokens_out=None, host_out=None, seed=None):
         logits = self.model.step(ctx)
         if logits.shape[0] == 0:
@@ -174,7 +165,7 @@ class LLMEngine:
         pool = None
         for bs in reversed(sizes):
             buf, layout = b.pack([], pad_rows=bs, table_width=self.max_blocks_per_seq,
-                                 extras=self._sampling_extras(bs))
+                                 extras=self.sampler.inputs(bs))
             layout["max_ctx_len"] = self.cfg.max_model_len          # static bound for kernels that plan by it
             static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
             ctx = b.to_device(buf, layout, into=static)
@@ -338,9 +329,7 @@ class LLMEngine:
                     sample_seqs.append(seq)
                 (decoding if n == 1 and last else others).append(i)
             turn = self._turn ^ 1                              # the row of the pinned token buffers that this step fills
-            # the seed of a sampled row: its own if it has one, else the engine's
-            row_seeds = [self.cfg.seed if s.params.seed is None else s.params.seed for s in sample_seqs]
-            seeds = {sd for sd, s in zip(row_seeds, sample_seqs) if s.params.temperature > 0}
+            row_seeds, seeds = self.sampler.seeds_of(sample_seqs)
             graphs_ok = bool(self.graph_sizes) and len(decoding) <= self.graph_sizes[-1] and seeds <= {self.cfg.seed}
             use_graph = graphs_ok and not others
             # One prompt portion, alone or beside requests that decode, runs as a graph of its padded length
@@ -352,10 +341,7 @@ class LLMEngine:
                              and (not decoding or len(rows[others[0]].tokens) <= self.cfg.split_step_max_tokens))
 
         def extras_for(seqs, pad_to):
-            if not seqs:
-                return self._sampling_extras(pad_to, turn=turn) if pad_to else None
-            return self._sampling_extras(pad_to or len(seqs), [s.params.temperature for s in seqs], [s.seq_id for s in seqs],
-                                         [len(s.token_ids) - s.prompt_len for s in seqs], turn)
+            return self.sampler.inputs(pad_to or len(seqs), seqs, turn)
 
         with _nvtx_range("forward"):
             b = self.runner.builder
@@ -381,7 +367,7 @@ class LLMEngine:
                 row = rows[others[0]]
                 pseq = batch[others[0]][0]
                 pseqs = [pseq] if row.want else []
-                extras = extras_for(pseqs, 0) or self._sampling_extras(0, turn=turn)
+                extras = extras_for(pseqs, 0)
                 pg = self._portion_graph(row, extras, len(pseqs))
                 tokens = self._sampled[self._portion_slot:self._portion_slot + len(pseqs)]
                 if pg is not None:
@@ -408,16 +394,8 @@ class LLMEngine:
                 ctx.token_feedback = self._sampled
                 self.h2d_bytes += buf.nbytes
                 logits = self.model.step(ctx)
-                if sample_seqs and len(seeds) <= 1:
-                    self.sampler.sample(logits, ctx.extras["temperature"], ctx.extras["request"],
-                                        ctx.extras["out_position"], out=self._sampled[:k],
-                                        seed=next(iter(seeds)) if seeds else None,
-                                        host_out=self._pinned_tokens, host_turn=ctx.extras["host_turn"])
-                elif sample_seqs:           # requests with different seeds of their own: one launch per row
-                    for i, sd in enumerate(row_seeds):
-                        self.sampler.sample(logits[i:i + 1], ctx.extras["temperature"][i:i + 1],
-                                            ctx.extras["request"][i:i + 1], ctx.extras["out_position"][i:i + 1],
-                                            out=self._sampled[i:i + 1], seed=sd)
+                if sample_seqs and not self.sampler.sample_step(logits, ctx.extras, self._sampled[:k], row_seeds, seeds,
+                                                                host_out=self._pinned_tokens):
                     self._pinned_tokens[turn, :k].copy_(self._sampled[:k], non_blocking=True)   # this rare way copies
                 sources.append((self._pinned_tokens[turn], k))
                 for k2, seq in enumerate(sample_seqs):

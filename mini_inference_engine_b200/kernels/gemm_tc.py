@@ -31,7 +31,6 @@ def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
-plan_overrides: dict = {}      # {(N, K): {"splits": .., "stages": ..}} for few-token products: a tuning hook
 pdl_enabled = True      # launch with programmatic stream serialization (see csrc/gemm_tcgen05.cu)
 
 
@@ -63,9 +62,7 @@ def plan(M: int, N: int, K: int) -> dict:
     stages = max(2, min(8, per_split, (TWO_PER_SM - 1024 - recv) // stage))
     if stages < 3 and per_split > 2:
         stages = max(2, min(8, per_split, (SMEM_BUDGET - 1024 - recv) // stage))
-    pl = dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
-    pl.update(plan_overrides.get((N, K), {}) if swapped else {})
-    return pl
+    return dict(swapped=swapped, bn=bn, splits=splits, stages=stages)
 
 
 @dataclass

@@ -138,15 +138,21 @@ def cmd_prefill_attention(args):
         n = torch.full((1,), T, dtype=torch.int32, device=DEV)
         out = torch.empty(T, H, D, device=DEV, dtype=torch.bfloat16)
         flops = 4 * H * D * T * (T + 1) / 2
-        for name, kernel in (("tcgen05", ops.prefill_attention_tc), ("mma.sync", ops.prefill_attention)):
-            if args.only and args.only != name:
+        for name, kernel in (("tcgen05", ops.prefill_attention_tc), ("tcgen05 x2", ops.prefill_attention_tc),
+                             ("mma.sync", ops.prefill_attention)):
+            if args.only and args.only != name.split()[0]:
                 continue
+            if name.startswith("tcgen05"):                 # one query tile a block, or two side by side (head_dim 64)
+                if name.endswith("x2") and D != 64:
+                    continue
+                ops.set_prefill_pairs(1 if name.endswith("x2") else 0)
             fn = lambda i: kernel(qkv, stride, k, v, bt, z, n, n, T, out, H, Hkv, D, args.page, 1 / math.sqrt(D), min_q_len=1)  # noqa: E731
             if args.once:
                 run_plain(fn, 3)
                 continue
             t = graph_time_us(fn, 5)
-            print(f"prefill attention {name:8s} T={T:5d}: {t:8.1f} us  ({flops / t / 1e6:6.1f} TFLOP/s causal)", flush=True)
+            print(f"prefill attention {name:10s} T={T:5d}: {t:8.1f} us  ({flops / t / 1e6:6.1f} TFLOP/s causal)", flush=True)
+        ops.set_prefill_pairs(-1)
         ops.check_tc_errors()
 
 

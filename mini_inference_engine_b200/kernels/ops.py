@@ -273,6 +273,12 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
     return out
 
 
+def set_prefill_pairs(mode: int = -1) -> None:
+    """Which tcgen05 prefill kernel serves head_dim 64: -1 chooses by the size of the launch (the default), 0 always
+    one query tile a block, 1 always two query tiles side by side (csrc/attention_prefill_tc.cu)."""
+    load("attention_prefill_tc").mie_prefill_attention_tc_pairs(int(mode))
+
+
 def check_tc_errors() -> None:
     """Raises if a block of a tensor-core kernel gave up a bounded wait (call after a synchronise)."""
     for name, fn in (("attention_prefill_tc", "mie_prefill_attention_tc"), ("attention_decode", "mie_decode_attention")):

@@ -617,6 +617,38 @@ def test_prefill_attention_tc_pairs_of_query_tiles(ops, H, Hkv, D, rows, window)
     close(out, want, torch.bfloat16, f"tcgen05 prefill in pairs, rows {rows} window {window}")
 
 
+@pytest.fixture()
+def side_by_side(ops):
+    ops.set_prefill_pairs(1)
+    yield
+    ops.set_prefill_pairs(-1)
+
+
+@pytest.mark.parametrize("rows,window", [
+    ([(2048, 2048)], None),                                              # 8 blocks of two tiles a head
+    ([(5, 5)], None), ([(128, 128)], None), ([(129, 129)], None), ([(300, 300)], None),      # one tile, two, an odd count
+    ([(700, 900), (1300, 1300), (129, 500), (1, 40), (257, 257), (2, 2)], None),         # continued portions, a skipped row
+    ([(1100, 1100), (900, 2000)], 300), ([(70, 300), (400, 400), (150, 150)], 33),      # windows: the second tile starts at a later key tile
+    ([(400, 400)], 128), ([(400, 400)], 129), ([(513, 1200)], 1),
+])
+def test_prefill_attention_tc_two_query_tiles_side_by_side(ops, side_by_side, rows, window):
+    """The kernel that holds two consecutive query tiles and two softmax groups a block (head_dim 64), forced for
+    every launch size, against the plain formula."""
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, rows, window=window, seed=len(rows) + (window or 0), kernel="prefill_tc",
+                            min_q_len=2)
+    live = torch.cat([torch.full((q,), q >= 2) for q, _ in rows])
+    close(out[live], want[live], torch.bfloat16, f"two tiles side by side, rows {rows} window {window}")
+    assert (out[~live] == 77.0).all()
+
+
+@pytest.mark.parametrize("far", [0, 127, 128, 255, 256, 777])
+@pytest.mark.parametrize("page", [16, 64, 128])
+def test_prefill_attention_tc_side_by_side_one_far_key_and_page_sizes(ops, side_by_side, far, page):
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, page, [(300, 800), (3, 800)], boost=far, seed=far, kernel="prefill_tc")
+    assert (want[299] - 5.0).abs().max() < 1e-3
+    close(out, want, torch.bfloat16, f"two tiles side by side, far key {far}, page {page}")
+
+
 def test_prefill_attention_tc_skips_single_token_rows(ops):
     out, want = _paged_case(ops, torch.bfloat16, 8, 2, 64, 16, [(1, 100), (5, 50), (1, 300), (2, 7)], kernel="prefill_tc", min_q_len=2)
     assert (out[0] == 77.0).all() and (out[6] == 77.0).all()
