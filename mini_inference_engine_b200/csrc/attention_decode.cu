@@ -37,16 +37,19 @@
 // before the first launch (the kernel leaves them zero).  `stages`: key/value tiles in flight per
 // block (2, 3 or 4; 0 = 4).  `num_pages`: pages in each cache (rows of the TMA tensor map); 0 keeps the
 // cp.async copies.  `check_pages`: pages in each cache for the range check of block-table entries (0: unchecked).
+// `min_part_tiles` (scratch merge): a row is cut into at most (its 64-key tiles / this) parts, so that one launch
+// laid out for long contexts leaves short rows whole; 0: every row into `splits` parts.
 extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_tables, int table_stride, const int* row_q_start,
                                     const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                     int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                     int window, int splits, float* part_o, float* part_lse, int* counters,
-                                    int stages, int64_t num_pages, int64_t check_pages, cudaStream_t stream) {
+                                    int stages, int64_t num_pages, int64_t check_pages, int min_part_tiles,
+                                    cudaStream_t stream) {
     return decode_attention_launch(q, q_stride, k_cache, v_cache, block_tables, table_stride, row_q_start, row_q_len,
                                    row_ctx_len, num_rows, out, num_heads, num_kv_heads, head_dim, page_size, scale,
                                    window, splits, part_o, part_lse, counters, stream, stages, num_pages, check_pages,
-                                   g_range_report);
+                                   g_range_report, min_part_tiles);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait (TMA copies that did not arrive).

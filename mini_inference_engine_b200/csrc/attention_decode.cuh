@@ -20,6 +20,7 @@ struct DecodeParams {
     float* part_o; float* part_lse; int* counters;      // scratch (splits > 1)
     int num_heads, num_kv_heads, page_size, page_shift, window, splits, chunks;
     int stages;              // tiles in flight per block (2, 3 or 4)
+    int min_part_tiles;      // scratch merge: a row is cut into no more parts than it has this many tiles for (0: always `splits`)
     int cluster;             // 1: the splits of a (row, kv head, chunk) are a thread-block cluster and merge through shared memory
     float scale_log2e;
     int* error;              // host-visible error word (TMA path: a bounded wait that ran out)
@@ -101,7 +102,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int lo = p.window > 0 ? (max(0, ctx - p.window) & ~(DEC_TILE - 1)) : 0;
     const int first_key = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int tiles_total = (ctx - lo + DEC_TILE - 1) / DEC_TILE;
-    const int tiles_per = (tiles_total + p.splits - 1) / p.splits;
+    // The grid is laid out for the longest context the launch may meet; a row is cut into as many parts as
+    // its own length pays for (scratch merge only: the blocks of a cluster all take part in its barriers).
+    // The parts beyond that leave at once, and a row that stays whole writes its output directly.
+    const int eff = (!p.cluster && p.min_part_tiles > 0) ? min(p.splits, max(1, tiles_total / p.min_part_tiles)) : p.splits;
+    if (split >= eff) {
+        pdl_wait();
+        return;
+    }
+    const int tiles_per = (tiles_total + eff - 1) / eff;
     const int kbeg = lo + split * tiles_per * DEC_TILE;
     const int kend = min(ctx, kbeg + tiles_per * DEC_TILE);
     const int ntiles = kend > kbeg ? (kend - kbeg + DEC_TILE - 1) / DEC_TILE : 0;
@@ -369,7 +378,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             val.x += f * v.x; val.y += f * v.y; val.z += f * v.z; val.w += f * v.w;
         }
         const int head = kvh * G + g0 + g;
-        if (p.splits == 1) {
+        if (eff == 1) {
             uint2 packed;
             packed.x = pack_bf16(val.x, val.y);
             packed.y = pack_bf16(val.z, val.w);
@@ -383,7 +392,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (d == 0) p.part_lse[slot] = c_lse[g];
         }
     }
-    if (p.splits == 1) return;
+    if (eff == 1) return;
 
     if (p.cluster) {
         cluster_sync_all();                                        // every partial and log-sum-exp has arrived
@@ -420,7 +429,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __syncthreads();
     if (threadIdx.x == 0) {
         const int done = atomicAdd(p.counters + unit, 1);
-        s_last = done == p.splits - 1;
+        s_last = done == eff - 1;
         if (s_last) p.counters[unit] = 0;                          // ready for the next launch
     }
     __syncthreads();
@@ -431,9 +440,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int head = kvh * G + g0 + g;
         const int64_t base = ((int64_t)row * p.num_heads + head) * p.splits;
         float mm = -INFINITY;
-        for (int s2 = 0; s2 < p.splits; ++s2) mm = fmaxf(mm, __ldcg(p.part_lse + base + s2));
+        for (int s2 = 0; s2 < eff; ++s2) mm = fmaxf(mm, __ldcg(p.part_lse + base + s2));
         float acc = 0.f, wsum = 0.f;
-        for (int s2 = 0; s2 < p.splits; ++s2) {
+        for (int s2 = 0; s2 < eff; ++s2) {
             const float lse = __ldcg(p.part_lse + base + s2);
             if (lse == -INFINITY) continue;
             const float w = fast_exp2(lse - mm);
@@ -503,7 +512,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
                                    cudaStream_t stream, int stages = 0, int64_t num_pages = 0,
-                                   int64_t check_pages = 0, int* report = nullptr) {
+                                   int64_t check_pages = 0, int* report = nullptr, int min_part_tiles = 0) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -523,6 +532,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.splits = splits; p.cluster = cluster ? 1 : 0;
     p.stages = stages > 0 ? stages : 4;
+    p.min_part_tiles = min_part_tiles > 0 ? min_part_tiles : 0;
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;

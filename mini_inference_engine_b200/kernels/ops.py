@@ -289,14 +289,22 @@ def check_tc_errors() -> None:
 
 
 _workspaces: dict = {}
+_outgrown: list = []          # scratch tensors that a larger one replaced; see _workspace
 
 
 def _workspace(device, name: str, numel: int, dtype) -> torch.Tensor:
     """A persistent, zero-initialised scratch tensor per (device, name), grown on demand.  Kernels
-    that use it leave it as they need to find it, so it is cleared only when it is (re)made."""
+    that use it leave it as they need to find it, so it is cleared only when it is (re)made.  A captured
+    graph keeps the ADDRESS of the tensor it was captured with, so a tensor that has been outgrown is kept
+    alive, never handed back to the allocator: graphs captured with it go on using it (each scratch tensor
+    is self-contained, and the launches of one stream use them one after the other).  Sizes at least
+    double, which bounds what is kept."""
     key = (str(device), name)
     t = _workspaces.get(key)
     if t is None or t.numel() < numel:
+        if t is not None:
+            _outgrown.append(t)
+            numel = max(numel, 2 * t.numel())
         t = torch.zeros(max(numel, 1024), dtype=dtype, device=device)
         _workspaces[key] = t
     return t
@@ -313,6 +321,32 @@ def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
     while splits < 8 and blocks * splits * 2 <= 2 * num_sms() and splits * 64 < max_ctx:
         splits *= 2
     return splits
+
+
+LONG_PART_TILES = 8          # a part of a long context is at least this many 64-key tiles (512 keys)
+
+
+def decode_plan(rows: int, kv_units: int, max_ctx: int, tma_ok: bool) -> tuple[int, str, int]:
+    """(splits, merge, min_part_tiles) for a decode launch whose contexts reach up to ``max_ctx``.
+
+    Short contexts and few rows: the cluster merge of ``decode_splits`` (one launch, no global round trip).
+    Long contexts (two parts of LONG_PART_TILES tiles or more) with 64 or more (row, kv head) units: a block
+    walks its keys at about 16 ns a key whatever else runs (three or four 16 KB tiles in flight), so the
+    bytes per second follow the number of blocks that run beside one another -- four per SM with page
+    copies by TMA, three stages and no receive slots of a cluster.  The context is then cut into as many
+    parts as fill those places, merged through scratch memory, and a row shorter than the launch was laid
+    out for is cut into fewer parts by the kernel (``min_part_tiles``).  Measured on B200, 32 q / 4 kv
+    heads of 64, device time in a graph, cluster plan -> this plan: 64 rows x 8,192 keys 149 -> 90 us
+    (5.96 TB/s), 32 x 8,192 72 -> 48 us, 16 x 8,192 38 -> 31 us, 64 x 2,048 36.8 -> 31.0 us, 32 x 2,048
+    20.5 -> 17.8 us; 8 rows stay with the cluster of 8 (20.9 us at 8,192 keys against 24.2 us)."""
+    units = max(1, rows * kv_units)
+    clustered = decode_splits(rows, kv_units, max_ctx)
+    tiles = -(-max(1, max_ctx) // 64)
+    if tma_ok and units >= 64 and tiles >= 2 * LONG_PART_TILES:
+        parts = min(4 * num_sms() // units, tiles // LONG_PART_TILES, 16)
+        if parts >= 2 and parts > clustered:
+            return parts, "scratch", LONG_PART_TILES
+    return clustered, "cluster", 0
 
 
 def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False) -> int:
@@ -344,12 +378,13 @@ def decode_uses_tma(blocks: int) -> bool:
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
-                     splits: int | None = None, merge: str = "cluster", stages: int | None = None,
-                     tma: bool | None = None) -> torch.Tensor:
+                     splits: int | None = None, merge: str | None = None, stages: int | None = None,
+                     tma: bool | None = None, min_part_tiles: int = 0) -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
     blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
     "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
-    splits merged through scratch memory in global memory."""
+    splits merged through scratch memory in global memory, a row cut into at most (its tiles /
+    ``min_part_tiles``) of them.  With neither ``splits`` nor ``merge`` given, ``decode_plan`` chooses."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "decode attention is bfloat16")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the decode kernel takes multiples of 16 from 16 to 128")
@@ -359,11 +394,17 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
         _i32(t, n)
     rows = row_q_len.numel()
     chunks = -(-(num_heads // num_kv_heads) // 16)
-    if splits is None:
+    tma_ok = head_dim in (64, 128) and page_size >= 8
+    if splits is None and merge is None:
+        splits, merge, min_part_tiles = decode_plan(rows, num_kv_heads * chunks, max_ctx or 1, tma_ok and tma is not False)
+        if merge == "scratch" and tma is None:
+            tma = True
+    elif splits is None:
         splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
+    merge = merge or "cluster"
     if tma is None:
         tma = decode_uses_tma(rows * num_kv_heads * chunks * splits)
-    tma = bool(tma) and head_dim in (64, 128) and page_size >= 8
+    tma = bool(tma) and tma_ok
     if stages is None:
         stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma)
     part_o = part_lse = counters = None
@@ -379,7 +420,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     _ptr(row_ctx_len), rows, _ptr(out), num_heads, num_kv_heads, head_dim,
                                     page_size, ctypes.c_float(scale), int(window or 0), int(splits),
                                     _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0),
-                                    ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]), _stream()),
+                                    ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]),
+                                    int(min_part_tiles if merge == "scratch" else 0), _stream()),
            "decode_attention")
     return out
 

@@ -292,7 +292,7 @@ def test_sampling_temperature_matches_plain(ops, vocab):
 # --------------------------------------------------------------------------- tensor-core decode attention
 
 def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=None, q_lens=None, max_ctx=None,
-                 merge="cluster"):
+                 merge="cluster", min_part_tiles=0):
     """Rows with one new token each (or q_lens given: rows with more are to be skipped)."""
     dt = torch.bfloat16
     torch.manual_seed(seed)
@@ -332,13 +332,13 @@ def _decode_case(ops, H, Hkv, D, page, ctxs, splits, window=None, seed=0, boost=
             q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV))
     out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
     ops.decode_attention(*args, out, H, Hkv, D, page, scale, window, max_ctx=max_ctx or max(ctxs), splits=splits, merge=merge,
-                         tma=False)
+                         tma=False, min_part_tiles=min_part_tiles)
     if D in (64, 128) and page >= 8:
         # the same case with keys and values fetched a page per TMA copy (the wrapper picks that way only
         # for many blocks): both ways must give the answer, skipped rows untouched in both
         out_tma = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
         ops.decode_attention(*args, out_tma, H, Hkv, D, page, scale, window, max_ctx=max_ctx or max(ctxs), splits=splits,
-                             merge=merge, tma=True)
+                             merge=merge, tma=True, min_part_tiles=min_part_tiles)
         torch.cuda.synchronize()
         ops.check_tc_errors()
         live = torch.repeat_interleave(q_len == 1, q_len).to(DEV)
@@ -365,6 +365,32 @@ def test_decode_attention_ragged_contexts_and_splits(ops, ctxs, splits):
     if splits is None:
         out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, None, max_ctx=2048)
         close(out, want, torch.bfloat16, "decode with a static context bound")
+
+
+@pytest.mark.parametrize("splits,part_tiles", [(2, 8), (5, 2), (9, 1), (16, 4), (3, 0)])
+def test_decode_attention_cuts_each_row_by_its_own_length(ops, splits, part_tiles):
+    """A launch laid out for long contexts (scratch merge, any number of parts): a row is cut into at most
+    (its 64-key tiles / part_tiles) parts, the blocks of the other parts leave at once, a row that stays whole
+    writes its output itself.  Lengths around the tile and part edges; twice on the same scratch, because the
+    counters of a unit are reset by the part that finds it complete -- whatever number that was."""
+    ctxs = [1, 63, 64, 65, 127, 128, 129, 511, 512, 513, 700, 1023, 1024, 1025, 2048, 3000]
+    for turn in range(2):
+        out, want, _ = _decode_case(ops, 8, 2, 64, 16, ctxs, splits, merge="scratch", min_part_tiles=part_tiles, max_ctx=4096,
+                                    seed=splits + turn)
+        close(out, want, torch.bfloat16, f"decode, {splits} parts of {part_tiles} tiles or more, turn {turn}")
+    out, want, _ = _decode_case(ops, 6, 3, 128, 32, ctxs[5:], splits, merge="scratch", min_part_tiles=part_tiles, max_ctx=4096,
+                                window=600, seed=splits)
+    close(out, want, torch.bfloat16, f"decode with a window, {splits} parts of {part_tiles} tiles or more")
+
+
+def test_decode_attention_plan_for_long_contexts(ops):
+    """The plan the wrapper makes by itself for 64 and more (row, kv head) units under a long context bound
+    (parts through scratch, rows cut by their own lengths) gives the plain answer, ragged lengths included."""
+    from mini_inference_engine_b200.kernels import ops as ops_mod
+    assert ops_mod.decode_plan(32, 4, 8192, True) == (4, "scratch", ops_mod.LONG_PART_TILES)
+    ctxs = [3000, 17, 1, 512, 513, 2048, 100, 1024] * 4
+    out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, None, merge=None, max_ctx=8192, seed=3)
+    close(out, want, torch.bfloat16, "decode, planned for 8,192 keys")
 
 
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 6, 48, 32), (16, 1, 128, 64),

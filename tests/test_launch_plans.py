@@ -1,0 +1,45 @@
+"""The arithmetic of the launch plans that needs no GPU (the planners assume 148 SMs without one)."""
+import pytest
+
+from mini_inference_engine_b200.kernels import device, ops
+
+
+def test_decode_plan_keeps_the_cluster_merge_for_few_rows_and_short_contexts():
+    assert device.num_sms() == device.B200_SMS or device.num_sms() > 0
+    for rows, ctx in [(1, 512), (8, 512), (8, 8192), (8, 32768), (16, 1024), (64, 512), (256, 512), (64, 960)]:
+        splits, merge, part = ops.decode_plan(rows, 4, ctx, True)
+        assert merge == "cluster" and part == 0 and splits == ops.decode_splits(rows, 4, ctx), (rows, ctx)
+    assert ops.decode_plan(64, 4, 8192, False) == (1, "cluster", 0)          # no page copies by TMA: the old plan
+
+
+@pytest.mark.parametrize("rows,ctx,parts", [(64, 8192, 2), (64, 2048, 2), (32, 8192, 4), (32, 2048, 4), (16, 8192, 9),
+                                            (48, 4096, 3), (20, 1 << 20, 7)])
+def test_decode_plan_fills_four_blocks_per_sm_for_long_contexts(rows, ctx, parts):
+    sms = device.num_sms()
+    if sms != device.B200_SMS:
+        pytest.skip("the expected numbers are for 148 SMs")
+    splits, merge, part = ops.decode_plan(rows, 4, ctx, True)
+    assert (splits, merge, part) == (parts, "scratch", ops.LONG_PART_TILES)
+    assert rows * 4 * splits <= 4 * sms                                      # all blocks beside one another
+    assert -(-ctx // 64) // splits >= ops.LONG_PART_TILES                   # no part shorter than it pays for
+
+
+def test_decode_plan_never_cuts_into_more_parts_than_there_are_blocks_for():
+    for rows in (16, 17, 31, 64, 100, 147, 148, 149, 1000):
+        splits, merge, _ = ops.decode_plan(rows, 4, 65536, True)
+        assert 1 <= splits <= 16
+        if merge == "scratch":
+            assert rows * 4 * splits <= 4 * device.num_sms()
+
+
+def test_scratch_that_is_outgrown_stays_alive_for_the_graphs_that_hold_its_address():
+    import torch
+    first = ops._workspace("cpu", "test_scratch", 10, torch.float32)
+    first[3] = 7.0
+    address = first.data_ptr()
+    again = ops._workspace("cpu", "test_scratch", 500, torch.float32)
+    assert again.data_ptr() == address                         # large enough: the same tensor
+    larger = ops._workspace("cpu", "test_scratch", 5000, torch.float32)
+    assert larger.numel() >= 5000 and larger.data_ptr() != address and not larger.any()
+    assert any(t.data_ptr() == address for t in ops._outgrown) and first[3] == 7.0
+    assert ops._workspace("cpu", "test_scratch", 5001, torch.float32).numel() >= 2 * larger.numel()
