@@ -117,13 +117,14 @@ def cmd_decode_attention(args):
         out = torch.empty(B, H, D, device=DEV, dtype=torch.bfloat16)
         fn = lambda i: ops.decode_attention(qkv, stride, k, v, bt, rows, ones, ctx, out, H, Hkv, D, args.page,   # noqa: E731
                                             1 / math.sqrt(D), max_ctx=args.max_context or args.context, splits=args.splits,
-                                            merge=args.merge if args.merge or args.splits is None else "cluster", stages=args.stages, tma={'auto': None, 'on': True, 'off': False}[args.tma])
+                                            merge=args.merge if args.merge or args.splits is None else "cluster",
+                                            stages=args.stages, tma={'auto': None, 'on': True, 'off': False}[args.tma])
         if args.once:
             run_plain(fn, 3)
             continue
         t = graph_time_us(fn, 20)
         byts = B * args.context * Hkv * D * 2 * 2
-        plan = args.splits or "%d by %s" % ops.decode_plan(B, Hkv * -(-(H // Hkv) // 16), args.max_context or args.context, True)[:2]
+        plan = args.splits or "%d by %s" % ops.decode_plan(B, Hkv * -(-(H // Hkv) // 16), args.max_context or args.context, True, D)[:2]
         print(f"decode attention B={B:4d} ctx={args.context} splits={plan}{' ' + args.merge if args.merge else ''}: {t:7.2f} us  "
               f"({byts / t / 1e3:6.0f} GB/s of cache)", flush=True)
 

@@ -326,30 +326,38 @@ def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
 LONG_PART_TILES = 8          # a part of a long context is at least this many 64-key tiles (512 keys)
 
 
-def decode_plan(rows: int, kv_units: int, max_ctx: int, tma_ok: bool) -> tuple[int, str, int]:
+def decode_blocks_per_sm(head_dim: int) -> int:
+    """Blocks of the decode kernel that share an SM with page copies by TMA and three stages: a stage is 16 KB of
+    keys and values per 64 columns of the head, beside 6 KB of static shared memory."""
+    return 4 if head_dim <= 64 else 2
+
+
+def decode_plan(rows: int, kv_units: int, max_ctx: int, tma_ok: bool, head_dim: int = 64) -> tuple[int, str, int]:
     """(splits, merge, min_part_tiles) for a decode launch whose contexts reach up to ``max_ctx``.
 
     Short contexts and few rows: the cluster merge of ``decode_splits`` (one launch, no global round trip).
     Long contexts (two parts of LONG_PART_TILES tiles or more) with 64 or more (row, kv head) units: a block
     walks its keys at about 16 ns a key whatever else runs (three or four 16 KB tiles in flight), so the
-    bytes per second follow the number of blocks that run beside one another -- four per SM with page
-    copies by TMA, three stages and no receive slots of a cluster.  The context is then cut into as many
+    bytes per second follow the number of blocks that run beside one another -- four per SM (two with heads
+    of 128) with page copies by TMA, three stages and no receive slots of a cluster.  The context is then cut into as many
     parts as fill those places, merged through scratch memory, and a row shorter than the launch was laid
     out for is cut into fewer parts by the kernel (``min_part_tiles``).  Measured on B200, 32 q / 4 kv
     heads of 64, device time in a graph, cluster plan -> this plan: 64 rows x 8,192 keys 149 -> 90 us
     (5.96 TB/s), 32 x 8,192 72 -> 48 us, 16 x 8,192 38 -> 31 us, 64 x 2,048 36.8 -> 31.0 us, 32 x 2,048
-    20.5 -> 17.8 us; 8 rows stay with the cluster of 8 (20.9 us at 8,192 keys against 24.2 us)."""
+    20.5 -> 17.8 us; 8 rows stay with the cluster of 8 (20.9 us at 8,192 keys against 24.2 us).  With 8 kv
+    heads of 128 (32 rows x 2,048 keys) the whole context per block is the fastest plan (46.3 us; two parts
+    62.7 us): 256 blocks already fill the two places an SM has."""
     units = max(1, rows * kv_units)
     clustered = decode_splits(rows, kv_units, max_ctx)
     tiles = -(-max(1, max_ctx) // 64)
     if tma_ok and units >= 64 and tiles >= 2 * LONG_PART_TILES:
-        parts = min(4 * num_sms() // units, tiles // LONG_PART_TILES, 16)
+        parts = min(decode_blocks_per_sm(head_dim) * num_sms() // units, tiles // LONG_PART_TILES, 16)
         if parts >= 2 and parts > clustered:
             return parts, "scratch", LONG_PART_TILES
     return clustered, "cluster", 0
 
 
-def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False) -> int:
+def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False, head_dim: int = 64) -> int:
     """Tiles of 64 keys in flight per block.  Shared memory that attention does not take stays free
     for the prologue of the kernel after it (the output projection fills its ring with weights while
     attention still runs): measured on B200 in the whole decode step at batch 8, 512 keys, three
@@ -357,22 +365,28 @@ def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False) -> 
     more than four tiles want the deepest ring (batch 64, 512 keys: 12.7 us with four stages, 15.5 us
     with three; 2048 keys: 40 us with four, 60 us with two); more blocks than fit beside one another
     at four stages want two, which puts twice as many on an SM (batch 256, 512 keys: 34 us against
-    46 us)."""
+    46 us).  Heads of 128 with TMA copies: three stages (two blocks on an SM) up to six blocks per SM in the
+    launch, two stages (three on an SM) beyond (32 kv heads of 128, 512 keys: 64 rows 87.9 against 98.0 us, 32 rows
+    51.4 against 53.9 us; 8 kv heads, 64 rows 32.3 against 27.7 us)."""
     tiles = -(-(-(-max(1, max_ctx) // splits)) // 64)
+    if head_dim > 64 and tma:
+        return 2 if blocks > 6 * num_sms() else 3
     if blocks > 3 * num_sms():
         return 3 if tma else 2            # TMA tiles are unpadded: three stages still put four blocks on an SM (256 x 512: 29.2 us, two stages 30.7)
     return 3 if tiles <= 4 else 4
 
 
-def decode_uses_tma(blocks: int) -> bool:
+def decode_uses_tma(blocks: int, head_dim: int = 64) -> bool:
     """Whether the decode kernel fetches keys and values a page per TMA copy instead of 16 bytes per
     cp.async.  Measured on B200 (32 q / 4 kv heads of 64): it pays where there are more blocks than
     fit beside one another (128 requests x 512 keys: 14.9 us against 20.6 us; 256 x 512: 29.2 against
     34.4 us) and costs a little where each block walks a long part alone (64 x 2048: 42.9 against
     40.0 us; 8 x 512: 7.5 against 7.1 us) -- the copies were never the bound there, the softmax
     bookkeeping per 16 keys is.  Cache slots beyond a request's context are copied along with their
-    page and must hold finite values (the cache storage starts as zeros)."""
-    return blocks > 3 * num_sms()
+    page and must hold finite values (the cache storage starts as zeros).  Heads of 128: always -- a stage of
+    cp.async copies is 34 KB there and the 16-byte copies are four times as many (8 rows x 512 keys, 8 kv heads:
+    7.3 against 14.2 us; 1,024 keys 9.8 against 20.4 us; 32 kv heads, 1 row x 512 keys: 6.2 against 14.4 us)."""
+    return head_dim > 64 or blocks > 3 * num_sms()
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
@@ -396,17 +410,18 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
     chunks = -(-(num_heads // num_kv_heads) // 16)
     tma_ok = head_dim in (64, 128) and page_size >= 8
     if splits is None and merge is None:
-        splits, merge, min_part_tiles = decode_plan(rows, num_kv_heads * chunks, max_ctx or 1, tma_ok and tma is not False)
+        splits, merge, min_part_tiles = decode_plan(rows, num_kv_heads * chunks, max_ctx or 1, tma_ok and tma is not False,
+                                                    head_dim)
         if merge == "scratch" and tma is None:
             tma = True
     elif splits is None:
         splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
     merge = merge or "cluster"
     if tma is None:
-        tma = decode_uses_tma(rows * num_kv_heads * chunks * splits)
+        tma = decode_uses_tma(rows * num_kv_heads * chunks * splits, head_dim)
     tma = bool(tma) and tma_ok
     if stages is None:
-        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma)
+        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma, head_dim)
     part_o = part_lse = counters = None
     if merge == "cluster" and splits not in (1, 2, 4, 8):
         merge = "scratch"

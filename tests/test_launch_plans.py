@@ -43,3 +43,14 @@ def test_scratch_that_is_outgrown_stays_alive_for_the_graphs_that_hold_its_addre
     assert larger.numel() >= 5000 and larger.data_ptr() != address and not larger.any()
     assert any(t.data_ptr() == address for t in ops._outgrown) and first[3] == 7.0
     assert ops._workspace("cpu", "test_scratch", 5001, torch.float32).numel() >= 2 * larger.numel()
+
+
+def test_decode_plan_for_heads_of_128_counts_two_blocks_per_sm():
+    if device.num_sms() != device.B200_SMS:
+        pytest.skip("the expected numbers are for 148 SMs")
+    assert ops.decode_plan(32, 8, 2048, True, 128) == (1, "cluster", 0)       # 256 blocks fill the two places an SM has
+    assert ops.decode_plan(8, 8, 4096, True, 128) == (4, "cluster", 0)
+    assert ops.decode_plan(16, 8, 8192, True, 128) == (2, "cluster", 0)
+    assert ops.decode_uses_tma(10, 128) and not ops.decode_uses_tma(10, 64) and ops.decode_uses_tma(3 * 148 + 1, 64)
+    assert ops.decode_stages(2048, 512, 1, True, 128) == 2 and ops.decode_stages(512, 512, 1, True, 128) == 3
+    assert ops.decode_stages(512, 512, 1, False, 128) == 2                   # cp.async: unchanged
