@@ -34,7 +34,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
 # every source file of the package; `build_all` compiles all of them
 SOURCES = ("embedding", "norm", "rope_cache", "attention_simt", "attention_decode", "attention_decode_static", "attention_prefill",
            "attention_prefill_tc",
-           "activation", "gemm_simt", "gemm_tcgen05", "gemm_chain",
+           "activation", "gemm_simt", "gemm_tcgen05", "gemm_chain", "gemm_pair_tc",
            "sampling")
 
 _libs: dict[str, ctypes.CDLL] = {}

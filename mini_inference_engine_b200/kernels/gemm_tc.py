@@ -369,8 +369,35 @@ def gemm_qkv_rope(x, w: torch.Tensor, out: torch.Tensor, bias, positions, slots,
     return out
 
 
+def pair_supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+    """Whether ``gemm_pair`` takes these operands."""
+    N, K = w.shape
+    return (x.dtype == torch.bfloat16 == w.dtype and out.dtype in (torch.bfloat16, torch.float32) and x.is_cuda
+            and K % 8 == 0 and N % (16 if swiglu else 8) == 0 and x.is_contiguous() and w.is_contiguous()
+            and out.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+              swiglu: bool = False) -> torch.Tensor:
+    """out = x w^T (+ bias), or silu(gate) * value over interleaved rows of ``w`` with ``swiglu``: the product
+    for many tokens on pairs of SMs (``csrc/gemm_pair_tc.cu``: 256 x 256 tiles by cta_group::2 MMAs, two
+    accumulators in tensor memory, one persistent pair of blocks per two SMs)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not pair_supports(x, w, out, swiglu) or w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
+        raise GemmTcError(f"gemm_pair: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} {out.dtype}")
+    lib = ops.load("gemm_pair_tc")
+    ops._check(lib.mie_gemm_pair(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
+                                 ops._ptr(out), ops.tag(out), M, N, K, int(swiglu), ops._stream()), "gemm_pair")
+    return out
+
+
 def check_error() -> None:
     """Raises if a block of an earlier launch gave up a bounded wait (call after a synchronise)."""
+    lib = build._libs.get("gemm_pair_tc")
+    if lib is not None and lib.mie_gemm_pair_error():
+        lib.mie_gemm_pair_clear_error()
+        raise GemmTcError("a block of the paired product gave up waiting on a barrier; its output is not valid")
     lib = build._libs.get("gemm_chain")
     if lib is not None and lib.mie_gemm_chain_error():
         lib.mie_gemm_chain_clear_error()
