@@ -19,7 +19,12 @@
 // Every wait is bounded; a block that gives up raises the error word and leaves.
 //
 // Epilogues: bias; SwiGLU on interleaved rows of w (row 2i the gate, 2i + 1 the value: y has N / 2
-// columns); float32 or bfloat16 output.
+// columns); float32 or bfloat16 output; the two halves of an RMSNorm without a kernel of its own, as in the
+// few-token product (csrc/gemm_tcgen05.cu): with `res` the product is added to the float32 residual stream in
+// place and, for the norm that reads the stream next, xw = bfloat16(res * norm_weight) and the row's share of
+// sum(res^2) over this tile's columns go out (one slot per 256-column tile: sq_out[tile_n][row]); with `sq_in`
+// the float32 sums are scaled by rsqrt(sum over slots / width + eps) before anything else, which is that norm
+// applied to the operand x = xw of a producer (a row factor commutes with the product).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -42,6 +47,8 @@ struct GpParams {
     int M, N, K;
     int tiles_m, num_tiles, k_tiles, stages;
     int* error;
+    float* res; const void* norm_w; int norm_w_tag; bf16* xw_out; float* sq_out; int sq_stride;
+    const float* sq_in; int sq_slots, sq_in_stride; float sq_width, sq_eps;
 };
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
@@ -175,15 +182,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tc_fence_after();
             const int row = tm * 2 * GP_BM + (int)rank * GP_BM + q * 32 + lane;
             const int col0 = tn * 2 * GP_BNH;
+            float rstd = 1.f, ssq = 0.f;
+            if (p.sq_in && row < p.M) {                                  // the norm in front of this product, as a row factor
+                float sum = 0.f;
+                for (int sl = 0; sl < p.sq_slots; ++sl) sum += __ldcg(p.sq_in + (int64_t)sl * p.sq_in_stride + row);
+                rstd = rsqrtf(sum / p.sq_width + p.sq_eps);
+            }
 #pragma unroll 1
             for (int c = 0; c < 2 * GP_BNH; c += 32) {
                 float v[32];
                 tmem_ld32(lane_addr + (uint32_t)buf * 256u + (uint32_t)c, v);
                 const int col = col0 + c;
                 if (row >= p.M || col >= p.N) continue;
+                if (p.sq_in) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= rstd;
+                }
                 if (p.bias) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) if (col + i < p.N) v[i] += load_tagged(p.bias, col + i, p.bias_tag);
+                }
+                if (p.res) {
+                    // the stream takes the sum; the next norm's operand and its sum of squares ride along
+                    float* rp = p.res + (int64_t)row * p.N + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (col + i >= p.N) break;
+                        float4 r = *reinterpret_cast<const float4*>(rp + i);
+                        r.x += v[i]; r.y += v[i + 1]; r.z += v[i + 2]; r.w += v[i + 3];
+                        *reinterpret_cast<float4*>(rp + i) = r;
+                        v[i] = r.x; v[i + 1] = r.y; v[i + 2] = r.z; v[i + 3] = r.w;
+                        ssq += r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
+                    }
+                    if (p.xw_out) {
+                        bf16* op = p.xw_out + (int64_t)row * p.N + col;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col + i >= p.N) break;
+                            float wn[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) wn[j] = load_tagged(p.norm_w, col + i + j, p.norm_w_tag);
+                            uint4 w;
+                            w.x = pack_bf16x2(v[i] * wn[0], v[i + 1] * wn[1]); w.y = pack_bf16x2(v[i + 2] * wn[2], v[i + 3] * wn[3]);
+                            w.z = pack_bf16x2(v[i + 4] * wn[4], v[i + 5] * wn[5]); w.w = pack_bf16x2(v[i + 6] * wn[6], v[i + 7] * wn[7]);
+                            *reinterpret_cast<uint4*>(op + i) = w;
+                        }
+                    }
+                    continue;
                 }
                 if (p.swiglu) {
                     // interleaved rows of w: column 2i the gate, 2i + 1 the value
@@ -227,6 +272,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                 }
             }
+            if (p.sq_out && row < p.M) p.sq_out[(int64_t)tn * p.sq_stride + row] = ssq;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_leader[buf]);
@@ -260,14 +306,33 @@ static int make_map_rows(CUtensorMap* map, const void* ptr, int rows, int K) {
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// The fused epilogues (see the header): the layout the few-token product's entry point takes.
+struct GpFuse {
+    void* res; const void* norm_w; int norm_w_tag; void* xw_out; void* sq_out; int sq_stride;
+    const void* sq_in; int sq_slots; int sq_in_stride; float sq_width; float sq_eps;
+};
+
+// How many slots of sum(res^2) a product with N columns leaves per row (one per 256-column tile).
+extern "C" int mie_gemm_pair_slots(int N) { return (N + 2 * GP_BNH - 1) / (2 * GP_BNH); }
+
 // y = x w^T (+ bias) (then SwiGLU over interleaved columns).  x [M, K], w [N, K] bfloat16 row-major, K % 8 == 0,
-// N % 8 == 0 (N % 16 == 0 with SwiGLU), all pointers 16-byte aligned.  y_tag: MIE_BF16 or MIE_F32.
+// N % 8 == 0 (N % 16 == 0 with SwiGLU), all pointers 16-byte aligned.  y_tag: MIE_BF16 or MIE_F32.  With
+// fuse->res, y is not written (may be null): res [M, N] float32 += the product; with fuse->norm_w also
+// xw_out [M, N] bfloat16 and sq_out [mie_gemm_pair_slots(N)][sq_stride >= M] float32.  With fuse->sq_in
+// [sq_slots][sq_in_stride >= M] the sums are scaled by rsqrt(sum over slots / sq_width + sq_eps) first.
 extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
-                             int K, int swiglu, cudaStream_t stream) {
+                             int K, int swiglu, const GpFuse* fuse, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
-    if (y_tag != MIE_BF16 && y_tag != MIE_F32) return MIE_ERR_BAD_ARG;
+    const bool into_stream = fuse && fuse->res;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | (into_stream ? 0 : reinterpret_cast<uintptr_t>(y))) & 15) return MIE_ERR_BAD_ARG;
+    if (!into_stream && (!y || (y_tag != MIE_BF16 && y_tag != MIE_F32))) return MIE_ERR_BAD_ARG;
+    if (into_stream) {
+        if (swiglu || (reinterpret_cast<uintptr_t>(fuse->res) & 15)) return MIE_ERR_BAD_ARG;
+        if ((fuse->xw_out != nullptr) != (fuse->norm_w != nullptr) || (fuse->sq_out != nullptr) != (fuse->norm_w != nullptr)) return MIE_ERR_BAD_ARG;
+        if (fuse->norm_w && (fuse->sq_stride < M || (reinterpret_cast<uintptr_t>(fuse->xw_out) & 15))) return MIE_ERR_BAD_ARG;
+    }
+    if (fuse && fuse->sq_in && (fuse->sq_slots < 1 || fuse->sq_in_stride < M || !(fuse->sq_width > 0.f))) return MIE_ERR_BAD_ARG;
     int rc = tc_setup();
     if (rc) return rc;
     CUtensorMap mx, mw;
@@ -281,6 +346,14 @@ extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int
     p.k_tiles = (K + GP_BK - 1) / GP_BK;
     p.stages = GP_MAX_STAGES;
     p.error = g_error_dev;
+    p.res = nullptr; p.norm_w = nullptr; p.norm_w_tag = 0; p.xw_out = nullptr; p.sq_out = nullptr; p.sq_stride = 0;
+    p.sq_in = nullptr; p.sq_slots = 0; p.sq_in_stride = 0; p.sq_width = 1.f; p.sq_eps = 0.f;
+    if (fuse) {
+        p.res = (float*)fuse->res; p.norm_w = fuse->norm_w; p.norm_w_tag = fuse->norm_w_tag;
+        p.xw_out = (bf16*)fuse->xw_out; p.sq_out = (float*)fuse->sq_out; p.sq_stride = fuse->sq_stride;
+        p.sq_in = (const float*)fuse->sq_in; p.sq_slots = fuse->sq_slots; p.sq_in_stride = fuse->sq_in_stride;
+        p.sq_width = fuse->sq_width; p.sq_eps = fuse->sq_eps;
+    }
     const size_t smem = (size_t)p.stages * GP_STAGE_BYTES + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

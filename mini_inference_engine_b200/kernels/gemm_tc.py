@@ -377,19 +377,39 @@ def pair_supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
             and out.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
-def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
-              swiglu: bool = False) -> torch.Tensor:
+def gemm_pair(x, w: torch.Tensor, out: torch.Tensor | None, bias: torch.Tensor | None = None, swiglu: bool = False,
+              res: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0):
     """out = x w^T (+ bias), or silu(gate) * value over interleaved rows of ``w`` with ``swiglu``: the product
     for many tokens on pairs of SMs (``csrc/gemm_pair_tc.cu``: 256 x 256 tiles by cta_group::2 MMAs, two
-    accumulators in tensor memory, one persistent pair of blocks per two SMs)."""
-    M, K = x.shape
+    accumulators in tensor memory, one persistent pair of blocks per two SMs).  ``x`` may be a DeferredNorm (the
+    norm in front becomes a row factor on the sums).  With ``res`` (float32 [M, N]) the product is added to it
+    in place instead of being written (``out`` is None); with ``norm_weight`` as well, the DeferredNorm for the
+    product behind that norm is returned."""
+    deferred = x if isinstance(x, DeferredNorm) else None
+    xt = deferred.xw if deferred is not None else x
+    M, K = xt.shape
     N = w.shape[0]
-    if not pair_supports(x, w, out, swiglu) or w.shape[1] != K or out.shape != (M, N // 2 if swiglu else N):
-        raise GemmTcError(f"gemm_pair: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} {out.dtype}")
+    probe = out if out is not None else xt
+    if not pair_supports(xt, w, probe, swiglu) or w.shape[1] != K:
+        raise GemmTcError(f"gemm_pair: x {tuple(xt.shape)} {xt.dtype}, w {tuple(w.shape)} {w.dtype}")
     lib = ops.load("gemm_pair_tc")
-    ops._check(lib.mie_gemm_pair(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
-                                 ops._ptr(out), ops.tag(out), M, N, K, int(swiglu), ops._stream()), "gemm_pair")
-    return out
+    made = None
+    xw = sq = None
+    if res is not None:
+        if out is not None or swiglu or res.dtype != torch.float32 or tuple(res.shape) != (M, N) or not res.is_contiguous():
+            raise GemmTcError(f"gemm_pair into the stream: res {tuple(res.shape)} {res.dtype} for a product of {(M, N)}")
+        if norm_weight is not None:
+            slots = lib.mie_gemm_pair_slots(N)
+            xw = torch.empty(M, N, dtype=torch.bfloat16, device=res.device)
+            sq = torch.empty(slots, M, dtype=torch.float32, device=res.device)
+            made = DeferredNorm(xw, sq, slots, N, eps)
+    elif out is None or tuple(out.shape) != (M, N // 2 if swiglu else N):
+        raise GemmTcError(f"gemm_pair: out {None if out is None else tuple(out.shape)} for a product of {(M, N)}")
+    fuse = _fuse_struct(deferred, res, norm_weight, xw, sq)
+    ops._check(lib.mie_gemm_pair(ops._ptr(xt), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
+                                 ops._ptr(out), ops.tag(out) if out is not None else 0, M, N, K, int(swiglu),
+                                 ctypes.byref(fuse), ops._stream()), "gemm_pair")
+    return made if res is not None else out
 
 
 def check_error() -> None:

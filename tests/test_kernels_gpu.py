@@ -799,6 +799,76 @@ def test_gemm_tc_deferred_norm_factor(ops, M, h, N, swiglu):
     close(out, want, torch.bfloat16, f"deferred norm factor {M}x{h}->{N} swiglu={swiglu}")
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (257, 264, 72), (2048, 2560, 2048), (300, 520, 200), (1000, 11264, 512),
+                                   (33, 2048, 5632), (512, 32000, 256)])
+@pytest.mark.parametrize("out_dt", [torch.bfloat16, torch.float32])
+def test_gemm_pair_against_the_plain_product(M, N, K, out_dt):
+    """The many-token product on pairs of SMs (256 x 256 tiles, cta_group::2): sizes that are no multiple of a
+    tile in any direction, one tile and several waves of them, with a bias, against float64."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + N + K)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    b = (torch.randn(N) * 0.1).bfloat16()
+    out = torch.full((M, N), 9.0, dtype=out_dt, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.to(DEV), out, b.to(DEV))
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    want = (x.double() @ w.double().t() + b.double()).float()
+    close(out, want, out_dt if out_dt == torch.bfloat16 else torch.float32, f"paired product {M}x{N}x{K} -> {out_dt}")
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 11264, 2048), (130, 48, 96), (700, 1040, 328)])
+def test_gemm_pair_swiglu(M, N, K):
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + N)
+    x = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(N, K) * 0.08).bfloat16()
+    out = torch.full((M, N // 2), 9.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.to(DEV), out, swiglu=True)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    y = x.double() @ w.double().t()
+    close(out, pl.swiglu(y[:, 0::2].float(), y[:, 1::2].float()), torch.bfloat16, f"paired product with SwiGLU {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("M,h,K0,N", [(2048, 2048, 2048, 11264), (300, 264, 96, 400), (1025, 520, 200, 48)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_gemm_pair_residual_and_deferred_norm(M, h, K0, N, swiglu):
+    """RMSNorm split across two many-token products: the first adds to the float32 stream and leaves
+    bf16(res * w_norm) and sum(res^2) per 256-column tile, the second scales its sums by rsqrt(mean + eps).
+    The stream, the operand, the sums and the final product against the plain formulas."""
+    from mini_inference_engine_b200.kernels import gemm_tc
+    torch.manual_seed(M + h + N)
+    eps = 1e-5
+    a = (torch.randn(M, K0) * 0.5).bfloat16()
+    w0 = (torch.randn(h, K0) * 0.05).bfloat16()
+    b0 = (torch.randn(h) * 0.1).bfloat16()
+    res0 = torch.randn(M, h) * 3
+    nw = (torch.randn(h) * 0.2 + 1).bfloat16()
+    w1 = (torch.randn(N, h) * 0.05).bfloat16()
+    b1 = None if swiglu else (torch.randn(N) * 0.1).bfloat16().to(DEV)
+    res = res0.clone().to(DEV)
+    d = gemm_tc.gemm_pair(a.to(DEV), w0.to(DEV), None, b0.to(DEV), res=res, norm_weight=nw.to(DEV), eps=eps)
+    out = torch.full((M, N // 2 if swiglu else N), 9.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(d, w1.to(DEV), out, b1, swiglu=swiglu)
+    torch.cuda.synchronize()
+    gemm_tc.check_error()
+    r = res0.double() + a.double() @ w0.double().t() + b0.double()
+    assert (res.cpu().double() - r).abs().max() <= 1e-5 * r.abs().max() + 1e-5
+    close(d.xw, (r * nw.double()).float(), torch.bfloat16, "operand left for the next product")
+    sq = d.sq[:, :M].sum(0).cpu().double()
+    assert ((sq - (r ** 2).sum(1)).abs() <= 1e-5 * (r ** 2).sum(1)).all()
+    y = pl.rmsnorm(r.float(), nw.float(), eps).double() @ w1.double().t()
+    want = pl.swiglu(y[:, 0::2].float(), y[:, 1::2].float()) if swiglu else (y + b1.cpu().double()).float()
+    close(out, want, torch.bfloat16, f"deferred norm through paired products {M}x{h}->{N} swiglu={swiglu}")
+    # without a norm behind it the stream alone is updated, and a second launch adds again
+    res2 = res0.clone().to(DEV)
+    assert gemm_tc.gemm_pair(a.to(DEV), w0.to(DEV), None, b0.to(DEV), res=res2) is None
+    torch.cuda.synchronize()
+    assert torch.equal(res2, res)
+
+
 def test_gemm_tc_deferred_norm_factor_with_rotation(ops):
     """The q|k|v product with both epilogues: the norm factor first, then rotation and cache write."""
     from mini_inference_engine_b200.kernels import gemm_tc
