@@ -6,7 +6,9 @@
   for these (F.linear, inference_engine/model.py:172,178,180,181,185).  ``auto`` (the default) uses
   this package's tcgen05 kernel (``csrc/gemm_tcgen05.cu``) where it is the faster one -- few tokens,
   i.e. decode steps, where it streams the weights, overlaps their fetch with the kernel before it
-  and fuses SwiGLU -- and the library product for many tokens; ``tcgen05`` and ``library`` force one.
+  and fuses SwiGLU -- its product on pairs of SMs (``csrc/gemm_pair_tc.cu``) for the gate/up projection
+  of prompt-sized batches, where its 256 x 256 tiles fill the GPU's pairs evenly and SwiGLU rides in the
+  epilogue, and the library product elsewhere; ``tcgen05`` and ``library`` force one.
 """
 from __future__ import annotations
 
@@ -21,6 +23,35 @@ AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen0
                               # tokens against 1.18 / 1.22 ms with the library at 48 / 64 -- although blocks then own tokens
                               # and receive their partial sums as bulk copies (1.61 -> 1.51 ms at 48 tokens): three ring
                               # stages of 24 KB instead of five of 18 KB leave each block too little in flight
+
+
+PAIR_MIN_TOKENS = 256         # from this many tokens on ``auto`` gives gate/up with SwiGLU to the product on pairs of SMs
+PAIR_MIN_FILL = 0.8           # ... where its tiles fill at least this share of the waves they take.  TinyLlama-1.1B sizes,
+                              # device time in a graph, 2,048 / 4,096 / 8,192 tokens: 68.6 / 132.9 / 260.4 us against the
+                              # library's product and the SwiGLU kernel, 79.4 / 142.6 / 282.2 us (352 tiles on 74 pairs fill
+                              # 0.95 of five waves).  The other products stay with the library: plain, the paired kernel is
+                              # 18.8 / 39.7 / 30.5 us for o / down / q|k|v at 2,048 tokens (64, 64 and 80 tiles: one or two
+                              # waves) against 15.0 / 32.9 / 18.5 us, and its epilogue that adds to the residual stream and
+                              # leaves the next norm's operand (a row of 256 float32 read, summed and written back per
+                              # thread) costs more than the add + norm kernel it saves (o: 42.0 us against 23.6 us)
+
+
+def pair_fill(num_tokens: int, N: int) -> float:
+    """The share of its waves that the paired product's 256 x 256 tiles fill (1.0: every pair of SMs has a
+    tile in every wave)."""
+    from .device import num_sms
+    tiles = -(-num_tokens // 256) * -(-N // 256)
+    pairs = max(1, num_sms() // 2)
+    return tiles / (-(-tiles // pairs) * pairs)
+
+
+def takes_pair(num_tokens: int, w: torch.Tensor) -> bool:
+    """Whether ``auto`` gives the gate/up product with these sizes to the kernel on pairs of SMs."""
+    if _bf16_backend != "auto" or w.dtype != torch.bfloat16 or not w.is_cuda or num_tokens < PAIR_MIN_TOKENS:
+        return False
+    N, K = w.shape
+    return (K % 8 == 0 and N % 8 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0
+            and pair_fill(num_tokens, N) >= PAIR_MIN_FILL)
 
 
 def set_bf16_backend(name: str) -> None:
@@ -104,6 +135,9 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch
             return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
         gu = gemm_tc.gemm(x, w_interleaved, torch.empty(M, 2 * inter, dtype=out_dtype, device=out.device))
         return ops.swiglu(gu, out, interleaved=True)       # the fused epilogue pairs rows within groups of 16
+    if (takes_pair(M, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and x.dtype == torch.bfloat16
+            and out_dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()):
+        return gemm_tc.gemm_pair(x, w_interleaved, out, swiglu=True)
     if uses_tcgen05(x, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and gemm_tc.supports(x, w_interleaved, out):
         return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)
     gu = linear(x, w_interleaved, None, out_dtype)

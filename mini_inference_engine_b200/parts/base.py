@@ -163,7 +163,7 @@ class Runtime:
     @staticmethod
     def _tc_sources() -> set:
         from ..kernels import gemm_tc
-        return {"gemm_tcgen05", "gemm_chain"} if gemm_tc.chain_enabled else {"gemm_tcgen05"}
+        return {"gemm_tcgen05", "gemm_pair_tc"} | ({"gemm_chain"} if gemm_tc.chain_enabled else set())
 
     def step_scope(self):
         """A context for one step of a model: in bfloat16 the fused few-token products queued inside it go
