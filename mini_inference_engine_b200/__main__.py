@@ -200,7 +200,7 @@ def cmd_profile_decode(args):
     wall = time.perf_counter() - t0
     torch.cuda.nvtx.range_pop()
     graph_steps = eng.num_graph_steps - graph0
-    nodes = eng.graphs[next(b for b in eng.graph_sizes if b >= args.batch)].kernels if graph_steps else 0   # of the bucket the batch ran in
+    nodes = eng.decode_graph(args.batch, args.prompt + args.steps).kernels if graph_steps else 0   # of the graph the batch ran in
     print("RESULT " + json.dumps({
         "batch": args.batch, "prompt_len": args.prompt, "steps": args.steps, "graphs": bool(args.graphs),
         "wall_ms_per_step": wall / args.steps * 1e3, "device_ms_per_step": start.elapsed_time(end) / args.steps,

@@ -19,6 +19,10 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     use_cuda_graphs: bool = True
     cuda_graph_batch_sizes: tuple = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256)
+    graph_context_bounds: tuple = (960,)    # decode graphs are captured once per bucket for each of these context bounds
+                                            # below max_model_len, and once for max_model_len: kernels that plan by the
+                                            # longest context a launch may meet (decode attention cuts long contexts into
+                                            # parts) then get a plan that fits the requests a step really holds
     num_blocks: int | None = None           # explicit pool size in pages (page 0 included); None = from memory
     seed: int = 0                           # sampling seed
     overlap_steps: bool = True              # launch step N+1 before reading step N's tokens (they are fed back on the device)
@@ -34,6 +38,7 @@ class EngineConfig:
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1 or self.max_model_len < 1:
             raise ValueError("max_num_seqs, max_num_batched_tokens and max_model_len must be positive")
         self.cuda_graph_batch_sizes = tuple(sorted(set(int(b) for b in self.cuda_graph_batch_sizes)))
+        self.graph_context_bounds = tuple(sorted(set(int(b) for b in self.graph_context_bounds if int(b) > 0)))
 
     @classmethod
     def from_overrides(cls, overrides: dict | None) -> "EngineConfig":

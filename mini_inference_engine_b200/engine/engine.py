@@ -127,8 +127,9 @@ class LLMEngine:
         self._sampled = torch.zeros(most + 8, dtype=torch.int32, device=self.device)   # the last step's tokens, on the device
         self._turn = 0
         self._in_flight = None
-        self.graphs: dict = {}
+        self.graphs: dict = {}                   # (bucket, context bound) -> captured decode step
         self.graph_sizes: list = []
+        self.graph_bounds: list = []             # the context bounds the buckets were captured for, ascending
         self.num_steps = 0
         self.num_graph_steps = 0
         self.num_portion_graph_steps = 0
@@ -153,38 +154,50 @@ class LLMEngine:
     @torch.inference_mode()
     def _capture_cuda_graphs(self):
         """One graph per batch-size bucket, largest first so the smaller ones share its memory
-        pool (inference_engine/engine.py:76-104).  A graph covers the whole step including the
-        sampling kernel; its inputs live in one static device buffer that a step overwrites with one
-        copy.  Rows that pad a batch up to its bucket are scratch rows: one token at position 0 of
-        page 0, context length 1."""
+        pool (inference_engine/engine.py:76-104), and per context bound (``graph_context_bounds`` and
+        ``max_model_len``): a step replays the graph of the smallest bound that covers its longest
+        request.  A graph covers the whole step including the sampling kernel; its inputs live in one
+        static device buffer that a step overwrites with one copy.  Rows that pad a batch up to its
+        bucket are scratch rows: one token at position 0 of page 0, context length 1."""
         t0 = time.perf_counter()
         sizes = sorted(b for b in self.cfg.cuda_graph_batch_sizes if b <= self.cfg.max_num_seqs)
         if not sizes:
             return
         b = self.runner.builder
         pool = None
+        bounds = sorted({c for c in self.cfg.graph_context_bounds if c < self.cfg.max_model_len} | {self.cfg.max_model_len})
         for bs in reversed(sizes):
-            buf, layout = b.pack([], pad_rows=bs, table_width=self.max_blocks_per_seq,
-                                 extras=self.sampler.inputs(bs))
-            layout["max_ctx_len"] = self.cfg.max_model_len          # static bound for kernels that plan by it
-            static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
-            ctx = b.to_device(buf, layout, into=static)
-            ctx.token_feedback = self._sampled
-            tokens = self._sampled[:bs]
-            self._forward_and_sample(ctx, tokens)                   # warm-up: builds kernels, sizes buffers
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            before = ops.launches
-            with torch.cuda.graph(g, pool=pool):
-                self._forward_and_sample(ctx, tokens)
-            pool = g.pool()
-            self.graphs[bs] = _DecodeGraph(g, layout, static, tokens, ops.launches - before)
+            static = None
+            for bound in reversed(bounds):
+                buf, layout = b.pack([], pad_rows=bs, table_width=self.max_blocks_per_seq,
+                                     extras=self.sampler.inputs(bs))
+                layout["max_ctx_len"] = bound                       # static bound for kernels that plan by it
+                if static is None:                                  # the bounds of a bucket share its input buffer
+                    static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
+                ctx = b.to_device(buf, layout, into=static)
+                ctx.token_feedback = self._sampled
+                tokens = self._sampled[:bs]
+                self._forward_and_sample(ctx, tokens)               # warm-up: builds kernels, sizes buffers
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                before = ops.launches
+                with torch.cuda.graph(g, pool=pool):
+                    self._forward_and_sample(ctx, tokens)
+                pool = g.pool()
+                self.graphs[bs, bound] = _DecodeGraph(g, layout, static, tokens, ops.launches - before)
         torch.cuda.synchronize()
         self._graph_pool = pool
         self.graph_sizes = sizes
+        self.graph_bounds = bounds
         if self.verbose:
-            print(f"[mini_inference_engine_b200] captured {len(sizes)} decode graphs (batch <= {sizes[-1]}) "
-                  f"in {time.perf_counter() - t0:.1f} s")
+            print(f"[mini_inference_engine_b200] captured {len(self.graphs)} decode graphs (batch <= {sizes[-1]}, "
+                  f"contexts <= {' / '.join(str(c) for c in bounds)}) in {time.perf_counter() - t0:.1f} s")
+
+    def decode_graph(self, rows: int, context: int):
+        """The captured step that serves ``rows`` decoding requests whose longest context (the new token
+        included) is ``context``."""
+        bs = next(s for s in self.graph_sizes if s >= rows)
+        return self.graphs[bs, next(c for c in self.graph_bounds if c >= context)]
 
     # ------------------------------------------------------------------ CUDA graphs of prompt portions
     PORTION_GRAPH_MIN_TOKENS = 2
@@ -350,7 +363,7 @@ class LLMEngine:
                 drows = [rows[i] for i in decoding]
                 dseqs = [batch[i][0] for i in decoding]
                 bs = next(s for s in self.graph_sizes if s >= len(drows))
-                g = self.graphs[bs]
+                g = self.decode_graph(bs, max(seq.cache.num_computed + 1 for seq in dseqs))
                 buf, layout = b.pack(drows, pad_rows=bs, table_width=self.max_blocks_per_seq, extras=extras_for(dseqs, bs))
                 assert layout["size"] == g.layout["size"]
                 b.to_device(buf, g.layout, into=g.buffer)

@@ -269,6 +269,29 @@ def test_a_portion_beside_decoding_requests_runs_as_two_graphs(dtype_name, model
         assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
 
 
+def test_decode_graphs_by_context_bound(model_folders):
+    """Decode graphs are captured per bucket AND per context bound; a step replays the one of the smallest
+    bound that covers its longest request.  Requests that grow across a bound change graphs on the way,
+    and the tokens are those of an engine with one graph per bucket."""
+    from mini_inference_engine_b200 import SamplingParams
+    folder = model_folders["tiny_a"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(4)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (20, 41, 58)]
+    eng = engine_for(folder, torch.bfloat16, max_model_len=128, graph_context_bounds=(48, 64))
+    assert eng.graph_bounds == [48, 64, 128]
+    assert eng.decode_graph(3, 10) is eng.graphs[4, 48] and eng.decode_graph(3, 49) is eng.graphs[4, 64]
+    assert eng.decode_graph(1, 128) is eng.graphs[1, 128] and eng.graphs[4, 48].buffer is eng.graphs[4, 128].buffer
+    outs = eng.generate(prompts, SamplingParams(max_tokens=40, ignore_eos=True))
+    one = engine_for(folder, torch.bfloat16, max_model_len=128, graph_context_bounds=())
+    assert one.graph_bounds == [128]
+    same = one.generate(prompts, SamplingParams(max_tokens=40, ignore_eos=True))
+    assert [o.output_ids for o in outs] == [o.output_ids for o in same]
+    for p, o in zip(prompts, outs):
+        assert_tokens_follow_plain(cfg, W, pl.round_bf16, p, o.output_ids, torch.bfloat16)
+    assert eng.num_graph_steps > 30
+
+
 def test_command_line_in_process(model_folders, tmp_path, capsys):
     """The command line's sub-commands on a tiny model: a written model folder loads, generation by
     ids follows the plain implementation, and the latency and profile-decode loops report a step."""
