@@ -66,15 +66,20 @@ def cmd_gemm(args):
             y = torch.empty(M, N // 2 if swiglu else N, device=DEV, dtype=torch.bfloat16)
             y_lib = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
             ours = lambda i: gemm_tc.gemm(x, ws[i % copies], y, swiglu=swiglu)        # noqa: E731
+            pair = lambda i: gemm_tc.gemm_pair(x, ws[i % copies], y, swiglu=swiglu)   # noqa: E731
             lib = lambda i: torch.mm(x, ws[i % copies].t(), out=y_lib)              # noqa: E731
             if args.once:
-                run_plain(ours, 3)
+                run_plain(pair if args.pair else ours, 3)
                 continue
             t_ours, t_lib = graph_time_us(ours, copies), graph_time_us(lib, copies)
             gemm_tc.check_error()
             byts, flops = N * K * 2 + M * K * 2 + M * N * 2, 2 * M * N * K
             print(f"{name:15s} M={M:5d} N={N:6d} K={K:5d}  tcgen05 {t_ours:8.1f} us ({byts / t_ours / 1e3:6.0f} GB/s, "
                   f"{flops / t_ours / 1e6:7.1f} TFLOP/s)  library {t_lib:8.1f} us  plan {gemm_tc.plan(M, N, K)}", flush=True)
+            if M >= 256:                 # the product on pairs of SMs (csrc/gemm_pair_tc.cu)
+                t_pair = graph_time_us(pair, copies)
+                gemm_tc.check_error()
+                print(f"{name:15s} M={M:5d} on pairs of SMs {t_pair:8.1f} us ({flops / t_pair / 1e6:7.1f} TFLOP/s)", flush=True)
             H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
             if name == "qkv" and gemm_tc.can_fuse_rope(x, ws[0], H, Hkv, D, D):
                 # the same product with the rotation and the cache write in its epilogue, against product + rotation kernel
@@ -204,6 +209,7 @@ def main(argv=None):
     g = sub.add_parser("gemm")
     g.add_argument("--tokens", type=int, nargs="+", default=[1, 8, 64, 2048])
     g.add_argument("--only", default=None, help="substring of the projection's name")
+    g.add_argument("--pair", action="store_true", help="with --once: run the product on pairs of SMs instead")
     g.set_defaults(fn=cmd_gemm)
     d = sub.add_parser("decode-attention")
     d.add_argument("--batch", type=int, nargs="+", default=[1, 8, 64])
