@@ -110,9 +110,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         pdl_wait();
         return;
     }
-    const int tiles_per = (tiles_total + eff - 1) / eff;
-    const int kbeg = lo + split * tiles_per * DEC_TILE;
-    const int kend = min(ctx, kbeg + tiles_per * DEC_TILE);
+    // tiles go round evenly: every part gets tiles_total / eff of them and the first (tiles_total % eff) parts one
+    // more, so that no part waits at the merge for one that walked twice as many as it needed to
+    const int tiles_base = tiles_total / eff, tiles_more = tiles_total - tiles_base * eff;
+    const int tiles_mine = tiles_base + (split < tiles_more ? 1 : 0);
+    const int kbeg = lo + (split * tiles_base + min(split, tiles_more)) * DEC_TILE;
+    const int kend = min(ctx, kbeg + tiles_mine * DEC_TILE);
     const int ntiles = kend > kbeg ? (kend - kbeg + DEC_TILE - 1) / DEC_TILE : 0;
 
     float o[NBLK][4];
