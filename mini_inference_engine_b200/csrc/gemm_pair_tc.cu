@@ -72,6 +72,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// One lane of a converged warp (the same one every time).  The warp runs its loop as a whole, so that
+// what feeds the tensor-core instructions -- descriptors, barrier addresses, loop counters -- stays uniform
+// across the warp, and only the instructions themselves are predicated on the elected lane.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -143,8 +151,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            // ---- the pair's MMAs: 256 x 256 x 16, four per k-tile
+        if (rank == 0) {
+            // ---- the pair's MMAs: 256 x 256 x 16, four per k-tile; the whole warp walks the loop, one lane issues
             const uint32_t idesc = umma_idesc_bf16(2 * GP_BM, 2 * GP_BNH);
             const uint64_t da0 = umma_desc_sw128(base), db0 = umma_desc_sw128(base + GP_STAGE_BYTES / 2);
             constexpr uint64_t STAGE_STEP = GP_STAGE_BYTES >> 4;       // descriptors of another stage differ in the address field
@@ -154,19 +162,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             bool ok = true;
             for (int tile = pair; tile < p.num_tiles && ok; tile += pairs, ++t_local) {
                 const int buf = t_local & 1, use = t_local >> 1;
-                if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_p)) break;     // both epilogues have read it
+                if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_p))) break;   // both epilogues have read it
                 tc_fence_after();
                 const uint32_t d_at = tmem_base + (uint32_t)buf * 256u;
                 for (int kt = 0; kt < p.k_tiles; ++kt) {
-                    if (!mbar_wait(&full[s], round & 1, abort_p)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], round & 1, abort_p))) { ok = false; break; }
+                    if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < GP_BK / 16; ++ks)
-                        umma_bf16_pair(d_at, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (kt > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit_pair(&empty[s]);                       // the stage is free in both blocks once these are done
+                        for (int ks = 0; ks < GP_BK / 16; ++ks)
+                            umma_bf16_pair(d_at, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, (kt > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit_pair(&empty[s]);                   // the stage is free in both blocks once these are done
+                    }
+                    __syncwarp();
                     if (++s == S) { s = 0; ++round; da = da0; db = db0; }
                     else { da += STAGE_STEP; db += STAGE_STEP; }
                 }
-                if (ok) umma_commit_pair(&acc_full[buf]);
+                if (ok && elect_one()) umma_commit_pair(&acc_full[buf]);
+                __syncwarp();
             }
         }
     } else {
