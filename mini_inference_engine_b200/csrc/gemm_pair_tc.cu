@@ -130,24 +130,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     pdl_wait();
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer: this block's half of every k-tile, counted on the leader's barrier
-            int s = 0;
-            uint32_t round = 0;
-            const uint32_t bar0 = cluster_addr(smem_u32(&full[0]), 0);
-            bool ok = true;
-            for (int tile = pair; tile < p.num_tiles && ok; tile += pairs) {
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                const int row_x = tm * 2 * GP_BM + (int)rank * GP_BM, row_w = tn * 2 * GP_BNH + (int)rank * GP_BNH;
-                for (int kt = 0; kt < p.k_tiles; ++kt) {
-                    if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, abort_p)) { ok = false; break; }
+        // ---- producer: this block's half of every k-tile, counted on the leader's barrier (the warp as a whole
+        // walks the loop, an elected lane issues)
+        int s = 0;
+        uint32_t round = 0;
+        const uint32_t bar0 = cluster_addr(smem_u32(&full[0]), 0);
+        bool ok = true;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += pairs) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int row_x = tm * 2 * GP_BM + (int)rank * GP_BM, row_w = tn * 2 * GP_BNH + (int)rank * GP_BNH;
+            for (int kt = 0; kt < p.k_tiles; ++kt) {
+                if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(&empty[s], (round - 1) & 1, abort_p))) { ok = false; break; }
+                if (elect_one()) {
                     if (rank == 0) mbar_expect_tx(&full[s], 2 * GP_STAGE_BYTES);
                     const uint32_t bar = bar0 + (uint32_t)s * 8u;
                     const uint32_t dst = base + (uint32_t)s * GP_STAGE_BYTES;
                     tma_load_2d_pair(dst, &map_x, bar, kt * GP_BK, row_x);
                     tma_load_2d_pair(dst + GP_STAGE_BYTES / 2, &map_w, bar, kt * GP_BK, row_w);
-                    if (++s == S) { s = 0; ++round; }
                 }
+                __syncwarp();
+                if (++s == S) { s = 0; ++round; }
             }
         }
     } else if (warp == 1) {
