@@ -72,14 +72,6 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
-// One lane of a converged warp (the same one every time).  The warp runs its loop as a whole, so that
-// what feeds the tensor-core instructions -- descriptors, barrier addresses, loop counters -- stays uniform
-// across the warp, and only the instructions themselves are predicated on the elected lane.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);

@@ -199,58 +199,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
     volatile int* abort_p = &abort_flag;
     float pre_res[4] = {0.f, 0.f, 0.f, 0.f}, pre_wn = 0.f, pre_b = 0.f;     // residual epilogue: fetched ahead by the epilogue warps
 
+    // The copy warp and the MMA warp walk their loops as whole warps and an elected lane issues: what feeds the
+    // TMA and tensor-core instructions (descriptors, coordinates, barrier addresses, counters) then stays uniform
+    // across the warp.  Issued from a loop that one lane ran alone, each tcgen05.mma cost that lane 90 - 150 cycles,
+    // which the last k-tiles of a product pay in full (nothing else is left to hide them).
     if (warp == 0) {
-        if (lane == 0) {
+        {
             // weights first: they do not depend on the kernel before this one
+            const bool issuer = elect_one();
             const CUtensorMap* map_w = SWAPPED ? &map_a : &map_b;
             const CUtensorMap* map_x = SWAPPED ? &map_b : &map_a;
             const uint32_t w_off = SWAPPED ? 0 : A_BYTES, x_off = SWAPPED ? A_BYTES : 0;
             const int w0 = SWAPPED ? a0 : b0, x0 = SWAPPED ? b0 : a0;
             const int ahead = min(n_kt, p.stages);
-            for (int it = 0; it < ahead; ++it) {
-                mbar_expect_tx(&full_bar[it], STAGE_BYTES);
-                tma_load_2d(tiles + (size_t)it * STAGE_BYTES + w_off, map_w, &full_bar[it], (kt0 + it) * TC_BK, w0);
+            if (issuer) {
+                for (int it = 0; it < ahead; ++it) {
+                    mbar_expect_tx(&full_bar[it], STAGE_BYTES);
+                    tma_load_2d(tiles + (size_t)it * STAGE_BYTES + w_off, map_w, &full_bar[it], (kt0 + it) * TC_BK, w0);
+                }
             }
+            __syncwarp();
             grid_dep_wait();                                  // the activations are the previous kernel's output
-            for (int it = 0; it < ahead; ++it)
-                tma_load_2d(tiles + (size_t)it * STAGE_BYTES + x_off, map_x, &full_bar[it], (kt0 + it) * TC_BK, x0);
-            // slot and round by counting: a division by the (run-time) ring depth costs this one thread more
-            // than the MMAs of a k-tile cost to issue
+            if (issuer) {
+                for (int it = 0; it < ahead; ++it)
+                    tma_load_2d(tiles + (size_t)it * STAGE_BYTES + x_off, map_x, &full_bar[it], (kt0 + it) * TC_BK, x0);
+            }
+            __syncwarp();
+            // slot and round by counting: a division by the (run-time) ring depth costs more than the MMAs of a
+            // k-tile cost to issue
             int s = ahead == p.stages ? 0 : ahead, round = ahead == p.stages ? 1 : 0;
             for (int it = ahead; it < n_kt; ++it) {
-                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p)) break;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                unsigned char* slot = tiles + (size_t)s * STAGE_BYTES;
-                const int k = (kt0 + it) * TC_BK;
-                tma_load_2d(slot + w_off, map_w, &full_bar[s], k, w0);
-                tma_load_2d(slot + x_off, map_x, &full_bar[s], k, x0);
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p))) break;
+                if (issuer) {
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    unsigned char* slot = tiles + (size_t)s * STAGE_BYTES;
+                    const int k = (kt0 + it) * TC_BK;
+                    tma_load_2d(slot + w_off, map_w, &full_bar[s], k, w0);
+                    tma_load_2d(slot + x_off, map_x, &full_bar[s], k, x0);
+                }
+                __syncwarp();
                 if (++s == p.stages) { s = 0; ++round; }
             }
         }
         __syncwarp();
         if (push) cluster_wait_acquire();
     } else if (warp == 1) {
-        if (lane == 0) {
+        {
+            const bool issuer = elect_one();
             const uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
             bool ok = true;
             int s = 0, round = 0;
             const uint64_t desc_a0 = umma_desc_sw128(tiles_base), desc_b0 = umma_desc_sw128(tiles_base + A_BYTES);
             for (int it = 0; it < n_kt && ok; ++it) {
-                ok = mbar_wait(&full_bar[s], round & 1, abort_p);
+                ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], round & 1, abort_p));
                 if (!ok) break;
                 tc_fence_after();
                 // the descriptors of a slot's slices differ from the first slot's only in the address field
                 // (units of 16 bytes, 14 bits: shared memory ends below 2^18 bytes, so the sum cannot carry)
                 const uint64_t step = (uint64_t)((uint32_t)s * STAGE_BYTES >> 4);
+                if (issuer) {
 #pragma unroll
-                for (int j = 0; j < TC_BK / 16; ++j) {       // 16 elements = 32 bytes of K per MMA, inside the swizzle row
-                    umma_bf16(tmem_base, desc_a0 + step + (uint64_t)(j * 2), desc_b0 + step + (uint64_t)(j * 2), idesc,
-                              (it > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < TC_BK / 16; ++j) {   // 16 elements = 32 bytes of K per MMA, inside the swizzle row
+                        umma_bf16(tmem_base, desc_a0 + step + (uint64_t)(j * 2), desc_b0 + step + (uint64_t)(j * 2), idesc,
+                                  (it > 0 || j > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);              // frees the slot once these MMAs have read it
                 }
-                umma_commit(&empty_bar[s]);                  // frees the slot once these MMAs have read it
+                __syncwarp();
                 if (++s == p.stages) { s = 0; ++round; }
             }
-            if (ok) umma_commit(&tmem_full_bar);             // the accumulator is complete
+            if (ok && issuer) umma_commit(&tmem_full_bar);   // the accumulator is complete
         }
         __syncwarp();
         if (push) cluster_wait_acquire();
