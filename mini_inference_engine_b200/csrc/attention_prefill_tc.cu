@@ -91,6 +91,9 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t* r) {
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t* r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" :: "r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -239,7 +242,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 }
             }
         } else if (warp == 1) {
-            if (lane == 0) {
+            // Head size 64: the whole warp walks this loop and an elected lane issues, so that what feeds the
+            // tensor-core instructions stays uniform across the warp (issued from a loop that one lane ran alone, an
+            // MMA cost that lane 90 - 150 cycles): 49.8 -> 45.1 us at 2,048 tokens, 531 -> 496 us at 8,192.  Head size
+            // 128 (one block on an SM, twice the exponent-free work per score): one lane alone, the 32 polling lanes
+            // cost the softmax warps more than the issue gains (964 -> 1,027 us at 8,192 tokens with the whole warp).
+            constexpr bool WARP_ISSUE = D == 64;
+            if (WARP_ISSUE || lane == 0) {
+                const bool issuer = WARP_ISSUE ? elect_one() : true;
+                auto wait_for = [&](uint64_t* bar, uint32_t parity) {
+                    return WARP_ISSUE ? mbar_wait_warp(bar, parity, abort_p) : mbar_wait(bar, parity, abort_p);
+                };
+                auto converge = [&]() { if (WARP_ISSUE) __syncwarp(); };
                 // S: M 128, N 128, both operands K-major.  PV: M 128, N D, B (values) MN-major.
                 const uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN);
                 const uint32_t idesc_o = umma_idesc_bf16(FA_BM, D) | (1u << 16);
@@ -262,41 +276,47 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 }
                 auto issue_s = [&](int g) {                        // scores of key tile g against its query tile
                     const bool second = g >= nA, st = g & 1;
+                    if (issuer) {
 #pragma unroll
-                    for (int ks = 0; ks < KS; ++ks)
-                        umma_bf16(tmem_base + TMEM_S, second ? dq[1][ks] : dq[0][ks], st ? dk[1][ks] : dk[0][ks], idesc_s, ks > 0 ? 1u : 0u);
-                    umma_commit(&s_full);
+                        for (int ks = 0; ks < KS; ++ks)
+                            umma_bf16(tmem_base + TMEM_S, second ? dq[1][ks] : dq[0][ks], st ? dk[1][ks] : dk[0][ks], idesc_s, ks > 0 ? 1u : 0u);
+                        umma_commit(&s_full);
+                    }
+                    converge();
                 };
                 // Order per key tile: as soon as the softmax warps have taken S(g) (p_full), S(g+1) is issued
                 // ahead of P(g) V(g), so that the next scores are ready while the tensor pipe still works on
                 // this tile's values -- the softmax warps never wait for a product that they do not need yet.
                 // kv_empty (the commit behind P V) also tells them when P may be overwritten and O rescaled:
                 // a commit costs the issuing thread as much as two MMAs, so one serves both.
-                bool ok = mbar_wait(&q_full[0], 0, abort_p);
-                if (ok && nsub > 1) ok = mbar_wait(&q_full[1], 0, abort_p);
-                if (ok) ok = mbar_wait(&kv_full[0], 0, abort_p);
+                bool ok = wait_for(&q_full[0], 0);
+                if (ok && nsub > 1) ok = wait_for(&q_full[1], 0);
+                if (ok) ok = wait_for(&kv_full[0], 0);
                 if (ok) { tc_fence_after(); issue_s(0); }
                 for (int g = 0; g < G && ok; ++g) {
                     const int s = g & 1;
                     const int t = g < nA ? g : g - nA;             // key tile within its query tile
                     const bool last_of_tile = g == nA - 1 || g == G - 1;
-                    ok = mbar_wait(&p_full, g & 1, abort_p);       // P written, O rescaled, S free
+                    ok = wait_for(&p_full, g & 1);       // P written, O rescaled, S free
                     if (!ok) break;
                     tc_fence_after();
                     bool next_issued = g + 1 >= G;
-                    if (!next_issued && mbar_try_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1)) {   // keys of the next tile are here
+                    if (!next_issued && (WARP_ISSUE ? __all_sync(0xffffffffu, mbar_try_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1)) != 0 : mbar_try_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1))) {   // keys of the next tile are here
                         tc_fence_after();
                         issue_s(g + 1);
                         next_issued = true;
                     }
+                    if (issuer) {
 #pragma unroll
-                    for (int kk = 0; kk < KV; ++kk)
-                        umma_bf16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + kk * 8, s ? dv[1][kk] : dv[0][kk], idesc_o,
-                                     (t > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(&kv_empty[s]);                     // the stage may be refilled, P overwritten and O rescaled
-                    if (last_of_tile) umma_commit(&o_full);        // this query tile's output is complete
+                        for (int kk = 0; kk < KV; ++kk)
+                            umma_bf16_ts(tmem_base + TMEM_O, tmem_base + TMEM_P + kk * 8, s ? dv[1][kk] : dv[0][kk], idesc_o,
+                                         (t > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(&kv_empty[s]);                 // the stage may be refilled, P overwritten and O rescaled
+                        if (last_of_tile) umma_commit(&o_full);    // this query tile's output is complete
+                    }
+                    converge();
                     if (!next_issued) {                            // the keys were late: wait for them now
-                        ok = mbar_wait(&kv_full[s ^ 1], ((g + 1) >> 1) & 1, abort_p);
+                        ok = wait_for(&kv_full[s ^ 1], ((g + 1) >> 1) & 1);
                         if (!ok) break;
                         tc_fence_after();
                         issue_s(g + 1);
@@ -907,12 +927,12 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     if ((rc = make_map_2d(&mk, k_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
     if ((rc = make_map_2d(&mv, v_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
     if (head_dim == 64) {
-        // two query tiles side by side once there are two pairs for every SM (measured, 32 heads: 2,048 tokens 48.9 against
-        // 49.5 us, 4,096 tokens 143 against 157 us, 8,192 tokens 462 against 532 us; 1,024 tokens 25.1 against 24.4 us);
-        // below that the one-tile blocks, two on an SM, spread a small launch over more SMs
+        // two query tiles side by side once there are three pairs for every SM (measured, 32 heads, one tile a block
+        // against two side by side: 2,048 tokens 45.1 against 48.5 us, 4,096 tokens 143.7 against 142.4 us, 8,192 tokens
+        // 496 against 462 us); below that the one-tile blocks, two on an SM, spread a launch over more SMs
         const int64_t tiles = (num_tokens + FA_BM - 1) / FA_BM;
         if ((tiles + 2 * num_rows) / 2 < 65535 &&
-            (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 4 * (int64_t)device_sm_count())))
+            (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 6 * (int64_t)device_sm_count())))
             return launch_fa_pp(mq, mk, mv, p, num_tokens, stream);
         return launch_fa<64>(mq, mk, mv, p, num_tokens, stream);
     }
