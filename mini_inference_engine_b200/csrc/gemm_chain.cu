@@ -178,7 +178,8 @@ gemm_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant_
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer: weight tiles, through every product
-        if (lane == 0) {
+        {                                                   // the whole warp walks the loop, an elected lane issues
+            const bool issuer = elect_one();
             int s = 0, round = 0;
             bool ok = true;
             for (int o = 0; o < p.num_ops && ok; ++o) {
@@ -186,9 +187,12 @@ gemm_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant_
                 const int kt0 = rank * op.tiles_per_split, kt1 = min(op.k_tiles, kt0 + op.tiles_per_split);
                 for (int t = cl; t < op.n_tiles && ok; t += p.clusters) {
                     for (int kt = kt0; kt < kt1; ++kt) {
-                        if (round > 0 && !mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p)) { ok = false; break; }
-                        mbar_expect_tx(&full_bar[s], A_BYTES);
-                        tma_load_2d(tiles + (size_t)s * A_BYTES, &maps.w[o], &full_bar[s], kt * CH_BK, t * CH_BM);
+                        if (round > 0 && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (round & 1) ^ 1, abort_p))) { ok = false; break; }
+                        if (issuer) {
+                            mbar_expect_tx(&full_bar[s], A_BYTES);
+                            tma_load_2d(tiles + (size_t)s * A_BYTES, &maps.w[o], &full_bar[s], kt * CH_BK, t * CH_BM);
+                        }
+                        __syncwarp();
                         if (++s == p.stages) { s = 0; ++round; }
                     }
                 }
@@ -198,7 +202,8 @@ gemm_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant_
         cluster_wait_acquire();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {                                                   // the whole warp walks the loop, an elected lane issues
+            const bool issuer = elect_one();
             const uint32_t idesc = umma_idesc_bf16(CH_BM, BN);
             const uint64_t desc_a0 = umma_desc_sw128(tiles_base), desc_b0 = umma_desc_sw128(tiles_base + p.x_off);
             int s = 0, round = 0, item = 0;
@@ -207,28 +212,34 @@ gemm_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant_
                 const ChainOp& op = p.ops[o];
                 const int kt0 = rank * op.tiles_per_split, kt1 = min(op.k_tiles, kt0 + op.tiles_per_split);
                 const int n_kt = max(0, kt1 - kt0);
-                ok = mbar_wait(&x_full, o & 1, abort_p);
+                ok = __all_sync(0xffffffffu, mbar_wait(&x_full, o & 1, abort_p));
                 for (int t = cl; t < op.n_tiles && ok; t += p.clusters, ++item) {
                     const int a = item & 1;
-                    if (item >= 2) ok = mbar_wait(&acc_empty[a], ((item >> 1) - 1) & 1, abort_p);
+                    if (item >= 2) ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[a], ((item >> 1) - 1) & 1, abort_p));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
                     for (int kt = 0; kt < n_kt; ++kt) {
-                        ok = mbar_wait(&full_bar[s], round & 1, abort_p);
+                        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], round & 1, abort_p));
                         if (!ok) break;
                         tc_fence_after();
                         const uint64_t da = desc_a0 + (uint64_t)((uint32_t)s * A_BYTES >> 4);
                         const uint64_t db = desc_b0 + (uint64_t)((uint32_t)kt * B_BYTES >> 4);
+                        if (issuer) {
 #pragma unroll
-                        for (int j = 0; j < CH_BK / 16; ++j)
-                            umma_bf16(tmem_d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kt > 0 || j > 0) ? 1u : 0u);
-                        umma_commit(&empty_bar[s]);
+                            for (int j = 0; j < CH_BK / 16; ++j)
+                                umma_bf16(tmem_d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kt > 0 || j > 0) ? 1u : 0u);
+                            umma_commit(&empty_bar[s]);
+                        }
+                        __syncwarp();
                         if (++s == p.stages) { s = 0; ++round; }
                     }
                     if (!ok) break;
-                    if (n_kt > 0) umma_commit(&acc_full[a]);
-                    else mbar_arrive(&acc_full[a]);           // an empty slice of K adds a zero tile
+                    if (issuer) {
+                        if (n_kt > 0) umma_commit(&acc_full[a]);
+                        else mbar_arrive(&acc_full[a]);       // an empty slice of K adds a zero tile
+                    }
+                    __syncwarp();
                 }
             }
         }
