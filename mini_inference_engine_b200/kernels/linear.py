@@ -27,13 +27,14 @@ AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen0
 
 PAIR_MIN_TOKENS = 256         # from this many tokens on ``auto`` gives gate/up with SwiGLU to the product on pairs of SMs
 PAIR_MIN_FILL = 0.8           # ... where its tiles fill at least this share of the waves they take.  TinyLlama-1.1B sizes,
-                              # device time in a graph, 2,048 / 4,096 / 8,192 tokens: 68.6 / 132.9 / 260.4 us against the
-                              # library's product and the SwiGLU kernel, 79.4 / 142.6 / 282.2 us (352 tiles on 74 pairs fill
-                              # 0.95 of five waves).  The other products stay with the library: plain, the paired kernel is
-                              # 18.8 / 39.7 / 30.5 us for o / down / q|k|v at 2,048 tokens (64, 64 and 80 tiles: one or two
-                              # waves) against 15.0 / 32.9 / 18.5 us, and its epilogue that adds to the residual stream and
-                              # leaves the next norm's operand (a row of 256 float32 read, summed and written back per
-                              # thread) costs more than the add + norm kernel it saves (o: 42.0 us against 23.6 us)
+                              # device time in a graph, 2,048 / 8,192 tokens: 62.2 / 234.4 us against the library's product
+                              # and the SwiGLU kernel, 80.7 / 291.6 us (352 tiles on 74 pairs fill 0.95 of five waves).
+                              # The other products stay with the library: plain, the paired kernel is 16.6 / 37.0 / 25.9 us
+                              # for o / down / q|k|v at 2,048 tokens (64, 64 and 80 tiles: one or two waves) against
+                              # 14.1 / 33.7 / 17.4 us (at 8,192 tokens 48.6 / 141.5 / 60.4 against 47.8 / 124.3 / 59.0 us),
+                              # and its epilogue that adds to the residual stream and leaves the next norm's operand (a row
+                              # of 256 float32 read, summed and written back per thread) costs more than the add + norm
+                              # kernel it saves (o: + 23 us against 8.6 us)
 
 
 def pair_fill(num_tokens: int, N: int) -> float:
