@@ -321,6 +321,29 @@ def test_long_contexts_cut_into_parts_under_graphs(tmp_path):
     ops.check_tc_errors()
 
 
+def test_prompt_portions_through_the_paired_product(model_folders, monkeypatch):
+    """The gate/up product of prompt-sized batches runs on pairs of SMs where its tiles fill the GPU; a tiny
+    model never gets there, so the thresholds are lowered here: prompts of 150 - 250 tokens of `tiny_b` (width 96,
+    feed-forward 256) in portions of 96 must give the plain implementation's tokens with that kernel on the path."""
+    from mini_inference_engine_b200 import SamplingParams
+    from mini_inference_engine_b200.kernels import gemm_tc, linear
+    monkeypatch.setattr(linear, "PAIR_MIN_TOKENS", 64)
+    monkeypatch.setattr(linear, "PAIR_MIN_FILL", 0.0)
+    calls = []
+    real = gemm_tc.gemm_pair
+    monkeypatch.setattr(gemm_tc, "gemm_pair", lambda *a, **k: (calls.append(a[0].shape[0]), real(*a, **k))[1])
+    folder = model_folders["tiny_b"]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(12)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (150, 250, 97)]
+    eng = engine_for(folder, torch.bfloat16, max_num_batched_tokens=96, max_model_len=256)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))
+    assert calls and max(calls) >= 64 and min(calls) >= 64, calls
+    for p, o in zip(prompts, outs):
+        assert_tokens_follow_plain(cfg, W, pl.round_bf16, p, o.output_ids, torch.bfloat16)
+    gemm_tc.check_error()
+
+
 def test_command_line_in_process(model_folders, tmp_path, capsys):
     """The command line's sub-commands on a tiny model: a written model folder loads, generation by
     ids follows the plain implementation, and the latency and profile-decode loops report a step."""
