@@ -25,25 +25,30 @@ AUTO_MAX_TOKENS = 32          # up to this many tokens ``auto`` takes the tcgen0
                               # stages of 24 KB instead of five of 18 KB leave each block too little in flight
 
 
-PAIR_MIN_TOKENS = 256         # from this many tokens on ``auto`` gives gate/up with SwiGLU to the product on pairs of SMs
-PAIR_MIN_FILL = 0.8           # ... where its tiles fill at least this share of the waves they take.  TinyLlama-1.1B sizes,
-                              # device time in a graph, 2,048 / 8,192 tokens: 62.2 / 234.4 us against the library's product
-                              # and the SwiGLU kernel, 80.7 / 291.6 us (352 tiles on 74 pairs fill 0.95 of five waves).
-                              # The other products stay with the library: plain, the paired kernel is 16.6 / 37.0 / 25.9 us
-                              # for o / down / q|k|v at 2,048 tokens (64, 64 and 80 tiles: one or two waves) against
-                              # 14.1 / 33.7 / 17.4 us (at 8,192 tokens 48.6 / 141.5 / 60.4 against 47.8 / 124.3 / 59.0 us),
-                              # and its epilogue that adds to the residual stream and leaves the next norm's operand (a row
-                              # of 256 float32 read, summed and written back per thread) costs more than the add + norm
-                              # kernel it saves (o: + 23 us against 8.6 us)
+PAIR_MIN_TOKENS = 128         # from this many tokens on ``auto`` considers the product on pairs of SMs for gate/up with SwiGLU
+PAIR_MIN_FILL = 0.7           # ... where the product fills at least this share of the 256 x 256 tiles that its rounds over the
+                              # pairs of SMs offer.  Device time in a graph against the library's product and the SwiGLU
+                              # kernel, TinyLlama-1.1B sizes at 512 / 768 / 1,024 / 2,048 / 8,192 tokens (shares 0.59 / 0.89 /
+                              # 0.79 / 0.95 / 0.96): 26.8 / 28.2 / 37.1 / 61.4 / 234.4 us against 24.6 / 30.7 / 43.7 / 78.9 /
+                              # 291.6 us; Llama-3-8B sizes at 256 / 384 / 512 / 2,048 tokens (0.76 / 0.57 / 0.76 / 0.93):
+                              # 55.3 / 89.1 / 93.1 / 298.3 us against 60.2 / 78.1 / 104.4 / 344.8 us.  The other products stay
+                              # with the library: plain, the paired kernel is 16.6 / 37.0 / 25.9 us for o / down / q|k|v at
+                              # 2,048 tokens (64, 64 and 80 tiles: one or two rounds) against 14.1 / 33.7 / 17.4 us (at 8,192
+                              # tokens 48.6 / 141.5 / 60.4 against 47.8 / 124.3 / 59.0 us), and its epilogue that adds to the
+                              # residual stream and leaves the next norm's operand (a row of 256 float32 read, summed and
+                              # written back per thread) costs more than the add + norm kernel it saves (o: + 23 us against
+                              # 8.6 us)
 
 
 def pair_fill(num_tokens: int, N: int) -> float:
-    """The share of its waves that the paired product's 256 x 256 tiles fill (1.0: every pair of SMs has a
-    tile in every wave)."""
+    """The share of the 256 x 256 tiles offered by the paired product's rounds (every pair of SMs one tile a
+    round) that a product of ``num_tokens`` x ``N`` outputs fills: partly empty tiles at the edges and pairs
+    without a tile in the last round both count as offered and unused."""
     from .device import num_sms
     tiles = -(-num_tokens // 256) * -(-N // 256)
     pairs = max(1, num_sms() // 2)
-    return tiles / (-(-tiles // pairs) * pairs)
+    rounds = -(-tiles // pairs)
+    return num_tokens * N / (rounds * pairs * 65536.0)
 
 
 def takes_pair(num_tokens: int, w: torch.Tensor) -> bool:

@@ -54,3 +54,19 @@ def test_decode_plan_for_heads_of_128_counts_two_blocks_per_sm():
     assert ops.decode_uses_tma(10, 128) and not ops.decode_uses_tma(10, 64) and ops.decode_uses_tma(3 * 148 + 1, 64)
     assert ops.decode_stages(2048, 512, 1, True, 128) == 2 and ops.decode_stages(512, 512, 1, True, 128) == 3
     assert ops.decode_stages(512, 512, 1, False, 128) == 2                   # cp.async: unchanged
+
+
+def test_paired_product_is_chosen_by_the_share_of_its_tiles_that_a_product_fills():
+    from mini_inference_engine_b200.kernels import linear
+    if device.num_sms() != device.B200_SMS:
+        pytest.skip("the expected numbers are for 148 SMs")
+    # gate/up of TinyLlama-1.1B (11,264 outputs) and Llama-3-8B (28,672): shares of the offered tiles, and on which side
+    # of the threshold the measured winners fall
+    assert abs(linear.pair_fill(2048, 11264) - 0.951) < 1e-3 and abs(linear.pair_fill(512, 11264) - 0.595) < 1e-3
+    wins = {(768, 11264), (1024, 11264), (2048, 11264), (256, 28672), (512, 28672), (512, 22016)}
+    loses = {(512, 11264), (384, 28672), (384, 22016), (256, 22016), (128, 28672)}
+    for M, N in wins:
+        assert linear.pair_fill(M, N) >= linear.PAIR_MIN_FILL, (M, N)
+    for M, N in loses:
+        assert linear.pair_fill(M, N) < linear.PAIR_MIN_FILL, (M, N)
+    assert linear.pair_fill(1, 256) < 0.001 and 0.99 < linear.pair_fill(74 * 256, 256) <= 1.0
