@@ -38,18 +38,22 @@
 // block (2, 3 or 4; 0 = 4).  `num_pages`: pages in each cache (rows of the TMA tensor map); 0 keeps the
 // cp.async copies.  `check_pages`: pages in each cache for the range check of block-table entries (0: unchecked).
 // `min_part_tiles` (scratch merge): a row is cut into at most (its 64-key tiles / this) parts, so that one launch
-// laid out for long contexts leaves short rows whole; 0: every row into `splits` parts.
+// laid out for long contexts leaves short rows whole; 0: every row into `splits` parts.  `cos_t` / `sin_t` (float32
+// [max_pos, head_dim / 2], or both null): rotate q and the new key inside this kernel and write the new key and
+// value into the cache -- the q|k|v activation then comes unrotated and nothing has written the cache row of
+// position ctx - 1 yet; head_dim % 32 == 0, the whole head rotates.
 extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_tables, int table_stride, const int* row_q_start,
                                     const int* row_q_len, const int* row_ctx_len, int num_rows, void* out,
                                     int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                     int window, int splits, float* part_o, float* part_lse, int* counters,
                                     int stages, int64_t num_pages, int64_t check_pages, int min_part_tiles,
+                                    const float* cos_t, const float* sin_t, int max_pos,
                                     cudaStream_t stream) {
     return decode_attention_launch(q, q_stride, k_cache, v_cache, block_tables, table_stride, row_q_start, row_q_len,
                                    row_ctx_len, num_rows, out, num_heads, num_kv_heads, head_dim, page_size, scale,
                                    window, splits, part_o, part_lse, counters, stream, stages, num_pages, check_pages,
-                                   g_range_report, min_part_tiles);
+                                   g_range_report, min_part_tiles, cos_t, sin_t, max_pos);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait (TMA copies that did not arrive).

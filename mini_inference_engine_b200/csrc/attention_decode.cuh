@@ -5,6 +5,7 @@
 #include "mma_common.cuh"
 #include "tcgen05_common.cuh"      // mbarrier, TMA copies, bounded waits, the tensor-map encoder
 #include "range_check.cuh"
+#include "rope_math.cuh"
 
 #define DEC_WARPS 4
 #define DEC_TILE 64
@@ -27,6 +28,12 @@ struct DecodeParams {
     uint32_t recv_offset;    // where the cluster merge's receive slots start in dynamic shared memory
     int64_t check_pages;     // pages in each cache, for the range check of block-table entries (0: unchecked)
     int* report;             // range report (range_check.cuh); null: nowhere
+    // Rotation inside this kernel (null: q and the newest key arrive rotated, and the newest cache row is written):
+    // q, the new key and the new value are read UNROTATED from the row's q|k|v activation (q_stride wide: the new
+    // key head kvh sits (num_heads + kvh) heads in, the value num_kv_heads heads further), q and the key are
+    // rotated by the token's position ctx - 1 with the whole head as rotary width (D % 32 == 0), and the block
+    // whose part holds that position writes key and value into the cache (the block of the first chunk of heads).
+    const float* cos_t; const float* sin_t; int max_pos;
 };
 
 // Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
@@ -195,6 +202,12 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         cp_async_commit();
     }
     pdl_wait();                                                    // q and the newest key and value are the previous kernel's
+    const int newest = ctx - 1;                                    // the only cached position written during this step
+    if (p.cos_t && range_position(newest, p.max_pos) != MIE_RANGE_OK) {   // no row of the tables for this position
+        // reported; the block goes on without rotating (it takes part in the merge's barriers and counters)
+        if (threadIdx.x == 0 && split == 0 && blockIdx.y == 0) range_report(p.report, MIE_RANGE_POSITION, MIE_K_ATTENTION_DECODE, row, newest);
+    }
+    const bool rotate = p.cos_t && range_position(newest, p.max_pos) == MIE_RANGE_OK;
     // Q fragments (A operand), rows = query heads of the group, zero beyond gn
     unsigned qf[KSTEPS][4];
     {
@@ -207,9 +220,29 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 qf[ks][i] = r < gn ? *reinterpret_cast<const unsigned*>(qb + (int64_t)r * D + c) : 0u;
             }
         }
+        if constexpr (KSTEPS % 2 == 0) {
+            if (rotate) {
+                // a thread holds dimension c of a head in k-step ks and its partner c + D / 2 in k-step ks + KSTEPS / 2
+                const float* cs = p.cos_t + (int64_t)newest * (D / 2);
+                const float* sn = p.sin_t + (int64_t)newest * (D / 2);
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS / 2; ++ks) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int c = ks * 16 + tq * 2 + (i >> 1) * 8;
+                        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qf[ks][i]));
+                        const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qf[ks + KSTEPS / 2][i]));
+                        const float c0 = cs[c], c1 = cs[c + 1], s0 = sn[c], s1 = sn[c + 1];
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x * c0 - y.x * s0, x.y * c1 - y.y * s1);
+                        const __nv_bfloat162 hi = __floats2bfloat162_rn(y.x * c0 + x.x * s0, y.y * c1 + x.y * s1);
+                        qf[ks][i] = *reinterpret_cast<const unsigned*>(&lo);
+                        qf[ks + KSTEPS / 2][i] = *reinterpret_cast<const unsigned*>(&hi);
+                    }
+                }
+            }
+        }
     }
 
-    const int newest = ctx - 1;                                    // the only cached position written during this step
     for (int t = 0; t < ntiles; ++t) {
         const int stage = t % NSTAGE;
         if (t + NSTAGE - 1 < ntiles) load_tile(t + NSTAGE - 1, (t + NSTAGE - 1) % NSTAGE);
@@ -221,15 +254,31 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             cp_async_wait<NSTAGE - 1>();                           // tile t has landed; NSTAGE - 1 younger ones may be in flight
             __syncthreads();
         }
-        if (t < NSTAGE - 1 && newest >= kbeg + t * DEC_TILE && newest < min(kend, kbeg + (t + 1) * DEC_TILE)) {
-            // this tile was copied before the wait: its newest row may be stale, fetch it again (L2, not L1)
+        if ((rotate || t < NSTAGE - 1) && newest >= kbeg + t * DEC_TILE && newest < min(kend, kbeg + (t + 1) * DEC_TILE)) {
+            // The newest row.  Without rotation here: the tile was copied before the wait and the row may be stale, so it
+            // is fetched again (L2, not L1).  With rotation here: the cache does not hold it yet -- this block makes it
+            // from the row's q|k|v activation, uses it and writes it into the cache.
             if (threadIdx.x < 2 * CHUNKS_PER_ROW) {
                 const int which = threadIdx.x / CHUNKS_PER_ROW, c = (threadIdx.x - which * CHUNKS_PER_ROW) * 8;
                 const int r = newest - (kbeg + t * DEC_TILE);
                 const int pi = (newest >> p.page_shift) - first_page;
                 const int page = pi < DEC_PAGE_SLOTS ? s_pages[pi] : checked_page(table[first_page + pi], page_limit, p.report, MIE_K_ATTENTION_DECODE, first_page + pi);
                 const int64_t src = (((int64_t)page * p.num_kv_heads + kvh) * p.page_size + (newest & (p.page_size - 1))) * D + c;
-                const uint4 v = __ldcg(reinterpret_cast<const uint4*>((which ? p.v_cache : p.k_cache) + src));
+                uint4 v;
+                if (rotate) {
+                    const bf16* act = p.q + (int64_t)token * p.q_stride + (int64_t)(p.num_heads + (which ? p.num_kv_heads : 0) + kvh) * D;
+                    if (which) {
+                        v = *reinterpret_cast<const uint4*>(act + c);
+                    } else {
+                        const int j = c < D / 2 ? c : c - D / 2;           // the pair's index: both halves of it are needed
+                        uint4 lo = *reinterpret_cast<const uint4*>(act + j), hi = *reinterpret_cast<const uint4*>(act + j + D / 2), olo, ohi;
+                        rotate8(lo, hi, p.cos_t + (int64_t)newest * (D / 2) + j, p.sin_t + (int64_t)newest * (D / 2) + j, olo, ohi);
+                        v = c < D / 2 ? olo : ohi;
+                    }
+                    if (chunk == 0) *reinterpret_cast<uint4*>(const_cast<bf16*>(which ? p.v_cache : p.k_cache) + src) = v;
+                } else {
+                    v = __ldcg(reinterpret_cast<const uint4*>((which ? p.v_cache : p.k_cache) + src));
+                }
                 if (TMA) *reinterpret_cast<uint4*>(tma_tiles + (size_t)stage * 2 * KV_TILE_BYTES + which * KV_TILE_BYTES + swz_tile_off(r, c / 8)) = v;
                 else *reinterpret_cast<uint4*>((which ? v_s : k_s) + stage * DEC_TILE * DP + r * DP + c) = v;
             }
@@ -515,7 +564,8 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
                                    cudaStream_t stream, int stages = 0, int64_t num_pages = 0,
-                                   int64_t check_pages = 0, int* report = nullptr, int min_part_tiles = 0) {
+                                   int64_t check_pages = 0, int* report = nullptr, int min_part_tiles = 0,
+                                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -540,6 +590,8 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.check_pages = check_pages; p.report = report;
+    if ((cos_t != nullptr) != (sin_t != nullptr) || (cos_t && (head_dim % 32 || max_pos <= 0))) return MIE_ERR_BAD_ARG;
+    p.cos_t = cos_t; p.sin_t = sin_t; p.max_pos = max_pos;
     // TMA copies (see the kernel): head sizes 64 and 128, pages of 8 positions or more, a caller that says
     // how many pages the caches hold (num_pages; the entry point that must not allocate passes 0)
     DecodeMaps maps;

@@ -10,6 +10,7 @@
 // rotated k and plain v go to slot `slots[t]` of the layer's pages
 // (inference_engine/model.py:130-134), page layout [page, kv_head, slot_in_page, head_dim].
 #include "common.cuh"
+#include "rope_math.cuh"
 #include "range_check.cuh"
 
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ cos_t,
@@ -84,21 +85,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
-// bfloat16 with 16-byte accesses: eight rotation pairs per thread (rotary_dim % 16 == 0, head_dim % 8 == 0).
-__device__ __forceinline__ void rotate8(const uint4& lo, const uint4& hi, const float* cs, const float* sn, uint4& out_lo, uint4& out_hi) {
-    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
-    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
-    __nv_bfloat162* oa = reinterpret_cast<__nv_bfloat162*>(&out_lo);
-    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out_hi);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float2 x = __bfloat1622float2(a[j]), y = __bfloat1622float2(b[j]);
-        const float c0 = cs[2 * j], c1 = cs[2 * j + 1], s0 = sn[2 * j], s1 = sn[2 * j + 1];
-        oa[j] = __floats2bfloat162_rn(x.x * c0 - y.x * s0, x.y * c1 - y.y * s1);
-        ob[j] = __floats2bfloat162_rn(y.x * c0 + x.x * s0, y.y * c1 + x.y * s1);
-    }
-}
-
+// bfloat16 with 16-byte accesses: eight rotation pairs per thread (rotary_dim % 16 == 0, head_dim % 8 == 0): rotate8 of rope_math.cuh.
 __global__ void rope_cache_bf16x8_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int num_heads, int num_kv_heads,

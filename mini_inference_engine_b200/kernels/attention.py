@@ -30,11 +30,32 @@ def set_backend(name: str) -> None:
     _backend = name
 
 
-def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window):
+def decode_only(ctx) -> bool:
+    """Whether every row of the step has exactly one new token (known on the host)."""
+    q_lens = ctx.host.get("q_len")
+    return q_lens is not None and all(n == 1 for n in q_lens)
+
+
+def rotates_in_decode(dtype, head_dim: int, ctx) -> bool:
+    """Whether ``attention(..., rope=...)`` can rotate q and the new key itself and write the cache: a step of
+    decoding rows only, on the tensor-core decode kernel, with a head size it rotates."""
+    return (_backend == "auto" and dtype == torch.bfloat16 and head_dim <= 128 and head_dim % 32 == 0
+            and decode_only(ctx))
+
+
+def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window, rope=None):
+    """``rope`` = (cos, sin): ``qkv`` is unrotated and the cache rows of the new tokens are unwritten; only
+    where ``rotates_in_decode`` holds."""
     q_stride = (num_heads + 2 * num_kv_heads) * head_dim
     args = (qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start, ctx.row_q_len,
             ctx.row_ctx_len)
     fast = _backend == "auto" and qkv.dtype == torch.bfloat16 and head_dim <= 128
+    if rope is not None:
+        if not rotates_in_decode(qkv.dtype, head_dim, ctx):
+            raise ValueError("rotation inside attention serves steps of decoding rows only (bfloat16, head sizes "
+                             "in steps of 32 up to 128)")
+        return ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
+                                    max_ctx=ctx.max_ctx_len, rope=rope)
     if not fast:
         return ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size,
                                    scale, window)

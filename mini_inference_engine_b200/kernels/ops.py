@@ -393,12 +393,17 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
                      splits: int | None = None, merge: str | None = None, stages: int | None = None,
-                     tma: bool | None = None, min_part_tiles: int = 0) -> torch.Tensor:
+                     tma: bool | None = None, min_part_tiles: int = 0, rope=None) -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
     blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
     "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
     splits merged through scratch memory in global memory, a row cut into at most (its tiles /
-    ``min_part_tiles``) of them.  With neither ``splits`` nor ``merge`` given, ``decode_plan`` chooses."""
+    ``min_part_tiles``) of them.  With neither ``splits`` nor ``merge`` given, ``decode_plan`` chooses.
+
+    ``rope`` = (cos, sin), float32 [positions, head_dim / 2]: ``q`` holds the UNROTATED q|k|v activation of
+    every row (keys ``num_heads`` heads in, values behind them), and the kernel rotates q and the new key by the
+    row's position (context length - 1, the whole head as rotary width), uses them, and writes the new key and
+    value into the cache -- the separate rotate-and-store launch is not needed then."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "decode attention is bfloat16")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the decode kernel takes multiples of 16 from 16 to 128")
@@ -407,6 +412,15 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                  (row_ctx_len, "row_ctx_len")):
         _i32(t, n)
     rows = row_q_len.numel()
+    cos = sin = None
+    if rope is not None:
+        cos, sin = rope
+        _need(head_dim % 32 == 0, f"head_dim {head_dim}: rotation inside the decode kernel takes multiples of 32")
+        _need(cos.dtype == torch.float32 == sin.dtype and cos.is_contiguous() and sin.is_contiguous()
+              and cos.shape == sin.shape and cos.dim() == 2 and cos.shape[1] == head_dim // 2,
+              "rope tables must be contiguous float32 [positions, head_dim / 2]")
+        _need(q_stride >= (num_heads + 2 * num_kv_heads) * head_dim and q_stride % 8 == 0,
+              "rotation inside the decode kernel reads q|k|v rows (16-byte aligned)")
     chunks = -(-(num_heads // num_kv_heads) // 16)
     tma_ok = head_dim in (64, 128) and page_size >= 8
     if splits is None and merge is None:
@@ -436,7 +450,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     page_size, ctypes.c_float(scale), int(window or 0), int(splits),
                                     _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0),
                                     ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]),
-                                    int(min_part_tiles if merge == "scratch" else 0), _stream()),
+                                    int(min_part_tiles if merge == "scratch" else 0),
+                                    _ptr(cos), _ptr(sin), int(cos.shape[0]) if cos is not None else 0, _stream()),
            "decode_attention")
     return out
 

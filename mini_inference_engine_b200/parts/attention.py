@@ -76,9 +76,13 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache, sink=None):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.position.project_rotate_and_store(x, self.w_qkv, self.b_qkv, ctx, cache, H, Hkv)
         out = self.rt.empty(ctx.num_tokens, H * D)
-        attn_kernels.attention(qkv, ctx, cache, out, H, Hkv, D, self.scale, self.window)
+        if getattr(self.position, "rotates_in_attention", None) and self.position.rotates_in_attention(x, self.w_qkv, ctx, cache):
+            qkv = self.rt.linear(x, self.w_qkv, self.b_qkv)
+            attn_kernels.attention(qkv, ctx, cache, out, H, Hkv, D, self.scale, self.window, rope=self.position.tables())
+        else:
+            qkv = self.position.project_rotate_and_store(x, self.w_qkv, self.b_qkv, ctx, cache, H, Hkv)
+            attn_kernels.attention(qkv, ctx, cache, out, H, Hkv, D, self.scale, self.window)
         if sink is not None:
             done = self.rt.linear_into_stream(out, self.w_o, None, sink)
             if done is not None:

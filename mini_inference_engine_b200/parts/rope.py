@@ -11,12 +11,15 @@ keys and values into their cache slots, which the reference does right after it
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
 from .base import Part, register_part
 
 _table_cache: dict = {}
+ROTATE_IN_ATTENTION = os.environ.get("MIE_B200_ROPE_IN_ATTENTION", "1") != "0"
 
 
 class Rope(Part):
@@ -60,6 +63,18 @@ class Rope(Part):
         qkv = self.rt.linear(x, w_qkv, b_qkv)
         self.rotate_and_store(qkv, ctx, cache, num_heads, num_kv_heads)
         return qkv
+
+    def rotates_in_attention(self, x, w_qkv, ctx, cache) -> bool:
+        """Whether the mixer should leave rotation and the cache write to its attention kernel (``tables``):
+        a step of decoding rows only whose q|k|v product is the library's (above the token count that the
+        tensor-core product with the rotating epilogue serves) -- one launch less a layer."""
+        from ..kernels import attention as attn_kernels, linear as linear_kernels
+        return (ROTATE_IN_ATTENTION and self.rotary_dim == self.head_dim and cache.k is not None and cache.writes
+                and cache.k.dtype == torch.bfloat16 and not linear_kernels.uses_tcgen05(x, w_qkv)
+                and attn_kernels.rotates_in_decode(x.dtype, self.head_dim, ctx))
+
+    def tables(self):
+        return self.cos, self.sin
 
     def rotate_and_store(self, qkv, ctx, cache, num_heads, num_kv_heads):
         ops.rope_cache_write(qkv, ctx.positions, ctx.slots[cache.group], self.cos, self.sin, cache.k, cache.v,

@@ -321,6 +321,41 @@ def test_long_contexts_cut_into_parts_under_graphs(tmp_path):
     ops.check_tc_errors()
 
 
+@pytest.mark.parametrize("name,graphs", [("tiny_b", False), ("tiny_d", True)])
+def test_decode_steps_of_many_requests_rotate_inside_attention(name, graphs, model_folders, monkeypatch):
+    """Steps of decoding rows only whose q|k|v product is the library's (more than 32 rows) leave rotation and the
+    cache write to the decode attention kernel; steps with a prompt portion among the rows do not.  40 requests of
+    ragged lengths: both kinds of step take turns while prompts are still coming in, then decoding alone; every
+    request's tokens against the plain implementation, which they could not follow with one key unrotated,
+    unwritten or written twice.  Once launched one by one (head_dim 32), once under captured graphs (head_dim 64)."""
+    from mini_inference_engine_b200 import SamplingParams
+    from mini_inference_engine_b200.kernels import ops
+    seen = {"inside": 0, "apart": 0}
+    real = ops.decode_attention
+
+    def counted(*a, **k):
+        seen["inside" if k.get("rope") is not None else "apart"] += 1
+        return real(*a, **k)
+    monkeypatch.setattr(ops, "decode_attention", counted)
+    folder = model_folders[name]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(31)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(rng.randrange(3, 50))] for _ in range(40)]
+    eng = engine_for(folder, torch.bfloat16, max_num_seqs=48, max_num_batched_tokens=256, max_model_len=96,
+                     use_cuda_graphs=graphs, cuda_graph_batch_sizes=(8, 48))
+    captured = dict(seen)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=20, ignore_eos=True))
+    if graphs:
+        assert captured["inside"] > 0 and captured["apart"] > 0 and eng.num_graph_steps >= 10, (captured, eng.num_graph_steps)
+    else:
+        assert seen["inside"] >= 10 * cfg["layers"] and seen["apart"] > 0, seen
+    for p, o in zip(prompts, outs):
+        assert len(o.output_ids) == 20
+        assert_tokens_follow_plain(cfg, W, pl.round_bf16, p, o.output_ids, torch.bfloat16)
+    ops.check_range_errors()
+    ops.check_tc_errors()
+
+
 def test_prompt_portions_through_the_paired_product(model_folders, monkeypatch):
     """The gate/up product of prompt-sized batches runs on pairs of SMs where its tiles fill the GPU; a tiny
     model never gets there, so the thresholds are lowered here: prompts of 150 - 250 tokens of `tiny_b` (width 96,

@@ -443,6 +443,83 @@ def test_decode_attention_reads_the_key_written_just_before_it(ops, tma):
         assert err < 0.05, f"step {i}: the newest value was not the one attended to (error {err})"
 
 
+@pytest.mark.parametrize("H,Hkv,D,page", [(32, 4, 64, 16), (8, 8, 128, 16), (6, 2, 32, 32), (34, 1, 96, 16)])
+@pytest.mark.parametrize("splits,merge,part_tiles", [(1, "cluster", 0), (4, "cluster", 0), (5, "scratch", 2), (None, None, 0)])
+def test_decode_attention_rotates_and_writes_the_cache(ops, H, Hkv, D, page, splits, merge, part_tiles):
+    """Rotation inside the decode kernel: q|k|v arrive unrotated, the cache row of the new token holds NaN.  The
+    kernel must rotate q and the new key by the row's position, attend with them and leave the rotated key and the
+    value in the cache -- bit for bit what the rotate-and-store kernel leaves there; skipped rows (more than one
+    new token) keep their NaN.  Lengths around tile, page and part edges; the new key dominates in one row."""
+    dt, theta, max_pos = torch.bfloat16, 10000.0, 2100
+    torch.manual_seed(H + D + (splits or 0))
+    ctxs = [1, 2, 63, 64, 65, 129, 512, 513, 700, 1024, 1025, 2048, 40]
+    q_lens = [1] * (len(ctxs) - 1) + [3]
+    num_pages = sum(math.ceil(c / page) for c in ctxs) + 3
+    tables = scattered_tables(ctxs, page, num_pages, 1)
+    width = max(len(t) for t in tables) + 2
+    j = torch.arange(0, D, 2, dtype=torch.int64).float()
+    cos, sin = ops.rope_tables((1.0 / (theta ** (j / D))).to(DEV), max_pos)
+    k_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)
+    v_cache = (torch.randn(num_pages, Hkv, page, D) * 3).to(dt)
+    scale = 1.0 / math.sqrt(D)
+    acts, want, newest = [], [], []
+    for r, (ql, cl) in enumerate(zip(q_lens, ctxs)):
+        q = torch.randn(cl, H, D).to(dt)
+        k = torch.randn(cl, Hkv, D).to(dt)
+        v = torch.randn(cl, Hkv, D).to(dt)
+        if r == 6:                                               # the new key stands out: a wrong or missing one shows in full
+            k[-1] *= 6
+        ang = pl.rope_angles(torch.arange(cl), D, theta)
+        rq, rk = pl.apply_rope(q.float(), ang), pl.apply_rope(k.float(), ang)
+        rk[:cl - ql] = rk[:cl - ql].to(dt).float()               # older keys are in the cache, rounded
+        for p in range(cl - ql):
+            k_cache[tables[r][p // page], :, p % page] = rk[p].to(dt)
+            v_cache[tables[r][p // page], :, p % page] = v[p]
+        for p in range(cl - ql, cl):                             # nothing has written the rows of the new tokens
+            k_cache[tables[r][p // page], :, p % page] = float("nan")
+            v_cache[tables[r][p // page], :, p % page] = float("nan")
+        acts.append(torch.cat((q[cl - ql:].reshape(ql, -1), k[cl - ql:].reshape(ql, -1), v[cl - ql:].reshape(ql, -1)), 1))
+        want.append(pl.causal_attention(rq, rk, v.float(), scale, None)[cl - ql:])
+        newest.append((tables[r][(cl - 1) // page], (cl - 1) % page, rk[-1], v[-1]))
+    qkv = torch.cat(acts, 0).to(DEV).contiguous()
+    bt = torch.zeros(len(ctxs), width, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t)
+    q_len = torch.tensor(q_lens, dtype=torch.int32)
+    ctx_len = torch.tensor(ctxs, dtype=torch.int32)
+    q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
+    live = torch.repeat_interleave(q_len == 1, q_len)
+    for tma in ((False, True) if D in (64, 128) else (False,)):
+        kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+        out = torch.full((qkv.shape[0], H, D), 77.0, dtype=dt, device=DEV)
+        before = qkv.clone()
+        ops.decode_attention(qkv, qkv.shape[1], kc, vc, bt.to(DEV), q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV), out,
+                             H, Hkv, D, page, scale, None, max_ctx=2048, splits=splits, merge=merge, tma=tma if splits else None,
+                             min_part_tiles=part_tiles, rope=(cos, sin))
+        torch.cuda.synchronize()
+        ops.check_tc_errors()
+        assert torch.equal(qkv, before)                          # the activation is read, never written
+        close(out[live.to(DEV)], torch.cat(want, 0)[live], dt, f"decode with rotation inside, H{H} Hkv{Hkv} D{D} tma {tma}")
+        assert (out[~live.to(DEV)] == 77.0).all()
+        # the cache afterwards: the same bits as the rotate-and-store kernel writes
+        kc2, vc2 = k_cache.to(DEV), v_cache.to(DEV)
+        pos = torch.cat([torch.arange(c - n, c) for n, c in zip(q_lens, ctxs)]).to(torch.int32)
+        slots = torch.tensor([tables[r][int(p) // page] * page + int(p) % page
+                              for r, (n, c) in enumerate(zip(q_lens, ctxs)) for p in range(c - n, c)], dtype=torch.int32)
+        ops.rope_cache_write(qkv.clone(), pos.to(DEV), slots.to(DEV), cos, sin, kc2, vc2, H, Hkv, D, D, page)
+        for r, (pg, off, rk_new, v_new) in enumerate(newest):
+            if q_lens[r] == 1:
+                assert torch.equal(kc[pg, :, off], kc2[pg, :, off]) and torch.equal(vc[pg, :, off], vc2[pg, :, off]), f"row {r}"
+                close(kc[pg, :, off], rk_new, dt, f"cached key of row {r}")
+            else:
+                assert kc[pg, :, off].isnan().all() and vc[pg, :, off].isnan().all()
+        same = ~(kc.isnan() | k_cache.to(DEV).isnan())
+        assert torch.equal(kc[same], k_cache.to(DEV)[same])      # nothing else was touched
+    with pytest.raises(Exception, match="multiples of 32"):
+        ops.decode_attention(qkv, qkv.shape[1], kc, vc, bt.to(DEV), q_start.to(DEV), q_len.to(DEV), ctx_len.to(DEV), out,
+                             H, Hkv, 48, page, scale, None, max_ctx=2048, rope=(cos, sin))
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
 def test_decode_attention_window(ops, window):
     for splits in (1, 3):
