@@ -188,7 +188,8 @@ class BatchBuilder:
             max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"],
             extras={k: dev[o:o + w].view(_TORCH_DTYPES[d]) for k, (o, w, d) in layout.get("extras", {}).items()},
             host=dict(q_len=layout["q_len"], ctx_len=layout["ctx_len"], q_start=layout["q_start"],
-                      state_slots=layout["state_slots"], real_rows=layout["real_rows"]))
+                      state_slots=layout["state_slots"], real_rows=layout["real_rows"],
+                      few_single_rows=layout.get("few_single_rows", False)))
 
     def build(self, rows: list[BatchRow]) -> StepContext:
         buf, layout = self.pack(rows)

@@ -246,8 +246,9 @@ class LLMEngine:
         b = self.runner.builder
         buf, layout = b.pack(self._portion_rows(row, padded), table_width=self.max_blocks_per_seq, extras=extras)
         layout["max_ctx_len"] = self.cfg.max_model_len
-        layout["q_len"] = None              # the split between portion and padding changes from replay to replay:
-        static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)     # kernels for both kinds of row are captured
+        layout["q_len"] = None              # the split between portion and padding changes from replay to replay
+        layout["few_single_rows"] = True    # (a padding of one token is a row like a decoding one: the kernel for portions serves it)
+        static = torch.zeros(layout["size"], dtype=torch.int32, device=self.device)
         ctx = b.to_device(buf, layout, into=static)
         ctx.token_feedback = self._sampled
         tokens = self._sampled[self._portion_slot:self._portion_slot + wanted]

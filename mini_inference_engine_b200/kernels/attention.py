@@ -62,6 +62,11 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
     q_lens = ctx.host.get("q_len")
     has_decode = q_lens is None or any(n == 1 for n in q_lens)
     has_prefill = q_lens is None or any(n > 1 for n in q_lens)
+    min_q_len = 2
+    if q_lens is None and ctx.host.get("few_single_rows"):
+        # row lengths unknown here (a captured step), but rows of one token are the exception among them: the
+        # kernel for portions takes those too, and the launch of the decode kernel is saved
+        has_decode, min_q_len = False, 1
     if has_decode:
         ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
                              max_ctx=ctx.max_ctx_len)
@@ -69,5 +74,5 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
         tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
         fn = ops.prefill_attention_tc if tc else ops.prefill_attention
-        fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window, min_q_len=2)
+        fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window, min_q_len=min_q_len)
     return out

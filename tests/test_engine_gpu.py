@@ -238,6 +238,31 @@ def test_long_prompts_in_portions_replayed_from_graphs(dtype_name, model_folders
         assert_tokens_follow_plain(cfg, W, rnd, p, ids, dtype)
 
 
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_a_portion_graph_whose_padding_is_one_token(name, model_folders):
+    """A captured portion step holds the portion and a scratch row that pads it to the captured length; how the
+    tokens split between the two changes from replay to replay.  With a padding of exactly one token the scratch
+    row looks like a decoding row, and the captured step has no decode kernel in it: the kernel for portions must
+    serve it.  Last portions of 31, 31, 30 and 32 tokens replay one another's graph of 32 (head sizes 32 and 64:
+    the mma.sync and the tcgen05 kernel)."""
+    from mini_inference_engine_b200 import SamplingParams
+    from mini_inference_engine_b200.kernels import ops
+    folder = model_folders[name]
+    cfg, W = pl.read_config(folder), plain_weights(folder)
+    rng = random.Random(17)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (63, 95, 62, 64, 127)]
+    eng = engine_for(folder, torch.bfloat16, max_num_batched_tokens=32, max_model_len=160)
+    eng.PORTION_GRAPH_MIN_TOKENS = 16
+    outs = []
+    for p in prompts:
+        outs += eng.generate([p], SamplingParams(max_tokens=4, ignore_eos=True))
+    assert eng.num_portion_graph_steps >= 8, eng.num_portion_graph_steps
+    for p, o in zip(prompts, outs):
+        assert_tokens_follow_plain(cfg, W, pl.round_bf16, p, o.output_ids, torch.bfloat16)
+    ops.check_range_errors()
+    ops.check_tc_errors()
+
+
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
 def test_a_portion_beside_decoding_requests_runs_as_two_graphs(dtype_name, model_folders):
     """Requests arrive while others decode, under a small token budget: most steps hold one prompt portion
