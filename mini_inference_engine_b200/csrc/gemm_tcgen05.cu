@@ -76,6 +76,7 @@ struct TcParams {
     int* error;              // host-visible error word
     int M, N, K;             // tokens, output features (rows of W), inner size
     int k_tiles, tiles_per_split, splits, stages;
+    int l2_ahead;            // weight k-tiles beyond the ring that the copy warp asks into L2 before the dependency wait
     int swiglu;              // 1: rows 2i / 2i+1 of W are gate_i / up_i; the output is silu(gate) * up, N/2 wide
     // Optional fused rotation + cache write for a q|k|v projection (see the header comment): rows of W
     // are [heads*D of q | kv_heads*D of k | kv_heads*D of v]; q is rotated and written to `out`, k is
@@ -217,6 +218,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                     mbar_expect_tx(&full_bar[it], STAGE_BYTES);
                     tma_load_2d(tiles + (size_t)it * STAGE_BYTES + w_off, map_w, &full_bar[it], (kt0 + it) * TC_BK, w0);
                 }
+            }
+            // the block's weight tiles beyond the ring: asked into L2 while the kernel before this one finishes
+            if (issuer) {
+                for (int it = ahead; it < min(n_kt, ahead + p.l2_ahead); ++it) tma_prefetch_l2_2d(map_w, (kt0 + it) * TC_BK, w0);
             }
             __syncwarp();
             grid_dep_wait();                                  // the activations are the previous kernel's output
@@ -903,6 +908,11 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
     if ((p.rope || p.res || p.sq_in) && p.splits < 2) return MIE_ERR_BAD_ARG;   // these live in the cluster reduction
     if (p.rope && (p.rotary_dim / 2) % p.splits) return MIE_ERR_BAD_ARG;   // a row and its partner must have one owner
     p.stages = stages;
+    {
+        static int l2_ahead = -1;
+        if (l2_ahead < 0) { const char* e = getenv("MIE_B200_L2_AHEAD"); l2_ahead = e ? atoi(e) : 8; }
+        p.l2_ahead = l2_ahead;
+    }
     CUtensorMap ma, mb;
     dim3 grid;
     if (swapped) {

@@ -59,6 +59,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// Asks L2 for the box that a later tma_load_2d with the same coordinates will fetch; completes nothing, counts nothing.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y) : "memory");
+}
+
 // K-major operand tile in shared memory, rows of 64 bfloat16 = 128 bytes, 128-byte swizzle (what a
 // TMA box of {64, rows} with CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are 1024 bytes apart
 // (stride byte offset), the leading byte offset is not used by swizzled K-major layouts (set to 1),
