@@ -20,6 +20,7 @@ import json
 import random
 import statistics
 import sys
+import shutil
 import tempfile
 import time
 
@@ -38,17 +39,22 @@ def _engine(args, **forced):
     from . import EngineConfig, LLMEngine
     from .config import load_preset
     from .weights import write_model_folder
-    folder = args.model
+    folder, made = args.model, None
     if folder is None:
         if not args.preset:
             raise SystemExit("give --model DIR or --preset NAME")
-        folder = tempfile.mkdtemp(prefix="mie_b200_model_")
-        write_model_folder(folder, load_preset(args.preset), args.seed)
+        folder = made = tempfile.mkdtemp(prefix="mie_b200_model_")
     ov = json.loads(args.overrides) if args.overrides else {}
     ov.update(forced)
     ov.setdefault("seed", args.seed)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
-    return LLMEngine(folder, EngineConfig.from_overrides(ov), dtype=dtype, load_tokenizer=False, verbose=True)
+    try:
+        if made:
+            write_model_folder(folder, load_preset(args.preset), args.seed)
+        return LLMEngine(folder, EngineConfig.from_overrides(ov), dtype=dtype, load_tokenizer=False, verbose=True)
+    finally:
+        if made:                # gigabytes of random weights: the engine holds its copy on the device, the folder goes now
+            shutil.rmtree(made, ignore_errors=True)
 
 
 def cmd_generate(args):
