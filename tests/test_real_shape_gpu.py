@@ -10,6 +10,7 @@ figure is quoted at) whole, in portions of the token budget, with its last 32 to
 one, and through the engine with its graphs of prompt portions."""
 import dataclasses
 import random
+import shutil
 
 import pytest
 import torch
@@ -29,7 +30,9 @@ def folder(request, tmp_path_factory):
     from mini_inference_engine_b200.weights import write_model_folder
     preset, changes = request.param
     cfg = dataclasses.replace(load_preset(preset), **changes)
-    return write_model_folder(str(tmp_path_factory.mktemp("real")), cfg, seed=21)
+    made = write_model_folder(str(tmp_path_factory.mktemp("real")), cfg, seed=21)
+    yield made
+    shutil.rmtree(made, ignore_errors=True)        # half a gigabyte: not left for pytest's own clean-up three runs later
 
 
 @pytest.fixture(scope="module")
@@ -107,7 +110,8 @@ def long_case(tmp_path_factory):
         # the oracle's logits at every position would be 262 MB a type: the head runs on the places compared
         hidden = pl.forward(pcfg, dict(W, **{"lm_head.weight": torch.eye(pcfg["hidden"])}), ids, rnd)
         want[name] = pl.linear(hidden[PLACES], head)
-    return folder, pcfg, W, ids, want
+    yield folder, pcfg, W, ids, want
+    shutil.rmtree(folder, ignore_errors=True)
 
 
 def _wanted(lo, hi):
