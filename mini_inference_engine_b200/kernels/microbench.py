@@ -124,6 +124,22 @@ def cmd_decode_attention(args):
                                             1 / math.sqrt(D), max_ctx=args.max_context or args.context, splits=args.splits,
                                             merge=args.merge if args.merge or args.splits is None else "cluster",
                                             stages=args.stages, tma={'auto': None, 'on': True, 'off': False}[args.tma])
+        if args.rope:
+            # the rotation with the cache write as a kernel of its own in front of the attention, against both inside it
+            inv = (1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+            cos, sin = ops.rope_tables(inv, max(args.context, 16))
+            pos = ctx - 1
+            slots = (bt[rows.long(), ((args.context - 1) // args.page)] * args.page + (args.context - 1) % args.page).to(torch.int32)
+            attend = fn
+
+            def apart(i):
+                ops.rope_cache_write(qkv, pos, slots, cos, sin, k, v, H, Hkv, D, D, args.page)
+                attend(i)
+            inside = lambda i: ops.decode_attention(qkv, stride, k, v, bt, rows, ones, ctx, out, H, Hkv, D, args.page,   # noqa: E731
+                                                    1 / math.sqrt(D), max_ctx=args.max_context or args.context, rope=(cos, sin))
+            ta, ti = graph_time_us(apart, 20), graph_time_us(inside, 20)
+            print(f"decode attention B={B:4d} ctx={args.context}: rotation kernel + attention {ta:7.2f} us, rotation inside {ti:7.2f} us", flush=True)
+            continue
         if args.once:
             run_plain(fn, 3)
             continue
@@ -221,6 +237,7 @@ def main(argv=None):
     d.add_argument("--stages", type=int, default=None)
     d.add_argument("--page", type=int, default=16)
     d.add_argument("--tma", choices=["auto", "on", "off"], default="auto", help="key/value copies by TMA (default: the wrapper's choice)")
+    d.add_argument("--rope", action="store_true", help="time the rotation kernel in front of the attention against the rotation inside it")
     d.set_defaults(fn=cmd_decode_attention)
     p = sub.add_parser("prefill-attention")
     p.add_argument("--tokens", type=int, nargs="+", default=[512, 2048, 8192])
