@@ -44,23 +44,19 @@ prefill_attention_kernel(const PrefillParams p) {
     __shared__ int s_row, s_q0;
     __shared__ int s_pages[PRE_PAGE_SLOTS];                        // this block's page ids, fetched once
 
-    pdl_enter();
-    if (threadIdx.x == 0) {
-        // tiles are numbered from the end of each row backwards so that the tiles with the longest
-        // key range start first
-        int tile = blockIdx.x, r = 0;
-        for (; r < p.num_rows; ++r) {
-            const int ql = p.row_q_len[r];
-            const int tiles = ql >= p.min_q_len ? (ql + PRE_BM - 1) / PRE_BM : 0;
-            if (tile < tiles) { tile = tiles - 1 - tile; break; }
-            tile -= tiles;
-        }
-        s_row = r < p.num_rows ? r : -1;
-        s_q0 = tile * PRE_BM;
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        // which row and query tile (a whole warp asks: warp_find_row); tiles are numbered from the end of each row
+        // backwards so that the tiles with the longest key range start first
+        int tile, tiles;
+        const int r = warp_find_row(p.row_q_len, p.num_rows, (int)blockIdx.x,
+                                    [&](int ql) { return ql >= p.min_q_len ? (ql + PRE_BM - 1) / PRE_BM : 0; }, tile, tiles);
+        if (threadIdx.x == 0) { s_row = r; s_q0 = (tiles - 1 - tile) * PRE_BM; }
     }
     __syncthreads();
     const int row = s_row;
     if (row < 0) return;
+    pdl_wait();
     const int q0 = s_q0;
     const int q_len = p.row_q_len[row], ctx = p.row_ctx_len[row], q_start = p.row_q_start[row];
     const int head = blockIdx.y;
@@ -231,21 +227,25 @@ prefill_attention_kernel(const PrefillParams p) {
 }
 
 template <int D>
-static int launch_prefill(const PrefillParams& p, int num_tokens, cudaStream_t stream) {
+static int launch_prefill(const PrefillParams& p, int work_tokens, int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)2 * 2 * PRE_BN * (D + 8) * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const dim3 grid((num_tokens + PRE_BM - 1) / PRE_BM + p.num_rows, p.num_heads);
+    const dim3 grid((work_tokens + PRE_BM - 1) / PRE_BM + work_rows, p.num_heads);     // tiles <= tokens / 64 + rows
     return launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), smem, stream, p);
 }
 
-// Rows with fewer than `min_q_len` new tokens are skipped (the decode kernel serves single tokens).
+// Rows with fewer than `min_q_len` new tokens are skipped (the decode kernel serves single tokens).  work_rows /
+// work_tokens: how many rows have min_q_len tokens or more, and their tokens in sum, where the caller knows (the grid
+// is laid out for the tiles they can have); 0: every row may, num_rows / num_tokens.
 extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                      const int* block_tables, int table_stride, const int* row_q_start,
                                      const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens,
                                      void* out, int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                     float scale, int window, int min_q_len, long long num_pages, cudaStream_t stream) {
+                                     float scale, int window, int min_q_len, long long num_pages, int work_rows,
+                                     int work_tokens, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
+    if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim < 16 || head_dim > PRE_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return MIE_ERR_BAD_ARG;
     if (page_size < 1 || (page_size & (page_size - 1))) return MIE_ERR_BAD_ARG;
@@ -262,14 +262,14 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
     p.scale_log2e = scale * 1.4426950408889634f;
     p.check_pages = num_pages > 0 ? (int64_t)num_pages : ((int64_t)1 << 40); p.report = g_range_report;
     switch (head_dim) {
-        case 16: return launch_prefill<16>(p, num_tokens, stream);
-        case 32: return launch_prefill<32>(p, num_tokens, stream);
-        case 48: return launch_prefill<48>(p, num_tokens, stream);
-        case 64: return launch_prefill<64>(p, num_tokens, stream);
-        case 80: return launch_prefill<80>(p, num_tokens, stream);
-        case 96: return launch_prefill<96>(p, num_tokens, stream);
-        case 112: return launch_prefill<112>(p, num_tokens, stream);
-        case 128: return launch_prefill<128>(p, num_tokens, stream);
+        case 16: return launch_prefill<16>(p, work_tokens, work_rows, stream);
+        case 32: return launch_prefill<32>(p, work_tokens, work_rows, stream);
+        case 48: return launch_prefill<48>(p, work_tokens, work_rows, stream);
+        case 64: return launch_prefill<64>(p, work_tokens, work_rows, stream);
+        case 80: return launch_prefill<80>(p, work_tokens, work_rows, stream);
+        case 96: return launch_prefill<96>(p, work_tokens, work_rows, stream);
+        case 112: return launch_prefill<112>(p, work_tokens, work_rows, stream);
+        case 128: return launch_prefill<128>(p, work_tokens, work_rows, stream);
     }
     return MIE_ERR_BAD_ARG;
 }

@@ -126,6 +126,34 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // Which row and which query tiles are this block's?  Asked first, and by a whole warp (warp_find_row): the grid is
+    // laid out for the most tiles the step's rows could have, and a block without work leaves before it has set
+    // anything up.
+    // A block takes two query tiles of a row, one after the other: the j-th from the end and the j-th
+    // from the start.  Under the causal mask their key ranges add up to the same length for every j,
+    // so all blocks of a row run equally long (the middle tile of an odd count stands alone).
+    // Pairing pays once there are more tiles than the GPU runs at a time (p.pair, the host's call):
+    // below that every tile has a block of its own and the longest one is the critical path.
+    if (warp == 0) {
+        int pair, tiles_r;
+        const int r = warp_find_row(p.row_q_len, p.num_rows, (int)blockIdx.x, [&](int ql) {
+            const int t = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
+            return p.pair ? (t + 1) / 2 : t;
+        }, pair, tiles_r);
+        if (lane == 0) {
+            s_row = r;
+            if (r >= 0) {
+                const int ql = p.row_q_len[r];
+                tiles_r = (ql + FA_BM - 1) / FA_BM;             // (the count above was of blocks)
+                s_q0[0] = (tiles_r - 1 - pair) * FA_BM;         // the longest key ranges start first
+                s_q0[1] = pair * FA_BM;
+                s_nsub = (p.pair && tiles_r - 1 - pair != pair) ? 2 : 1;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_row < 0) return;
+
     if (threadIdx.x == 0) {
         abort_flag = 0;
         mbar_init(&q_full[0], 1); mbar_init(&q_full[1], 1);
@@ -144,26 +172,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     pdl_wait();                                                  // everything below reads what earlier kernels wrote
-
-    if (threadIdx.x == 0) {
-        // A block takes two query tiles of a row, one after the other: the j-th from the end and the j-th
-        // from the start.  Under the causal mask their key ranges add up to the same length for every j,
-        // so all blocks of a row run equally long (the middle tile of an odd count stands alone).
-        // Pairing pays once there are more tiles than the GPU runs at a time (p.pair, the host's call):
-        // below that every tile has a block of its own and the longest one is the critical path.
-        int pair = blockIdx.x, r = 0, tiles_r = 0;
-        for (; r < p.num_rows; ++r) {
-            const int ql = p.row_q_len[r];
-            tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
-            const int blocks_r = p.pair ? (tiles_r + 1) / 2 : tiles_r;
-            if (pair < blocks_r) break;
-            pair -= blocks_r;
-        }
-        s_row = r < p.num_rows ? r : -1;
-        s_q0[0] = (tiles_r - 1 - pair) * FA_BM;                 // the longest key ranges start first
-        s_q0[1] = pair * FA_BM;
-        s_nsub = (p.pair && tiles_r - 1 - pair != pair) ? 2 : 1;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -537,6 +545,26 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // which row and which pair of query tiles (pairs are numbered from the row's end): asked first, by a whole warp;
+    // a block without work leaves before it has set anything up
+    if (warp == 0) {
+        int pair, pairs_r;
+        const int r = warp_find_row(p.row_q_len, p.num_rows, (int)blockIdx.y, [&](int ql) {
+            return ql >= p.min_q_len ? ((ql + FA_BM - 1) / FA_BM + 1) / 2 : 0;
+        }, pair, pairs_r);
+        if (lane == 0) {
+            s_row = r;
+            if (r >= 0) {
+                const int tiles_r = (p.row_q_len[r] + FA_BM - 1) / FA_BM;
+                const int first = (pairs_r - 1 - pair) * 2;              // the pair's first tile
+                s_q0 = first * FA_BM;
+                s_nsub = first + 1 < tiles_r ? 2 : 1;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_row < 0) return;
+
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int u = 0; u < 2; ++u) {
@@ -556,22 +584,6 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     pdl_wait();
-
-    if (threadIdx.x == 0) {
-        // which row and which pair of query tiles: pairs are numbered from the row's end
-        int pair = blockIdx.y, r = 0, tiles_r = 0;
-        for (; r < p.num_rows; ++r) {
-            const int ql = p.row_q_len[r];
-            tiles_r = ql >= p.min_q_len ? (ql + FA_BM - 1) / FA_BM : 0;
-            const int pairs_r = (tiles_r + 1) / 2;
-            if (pair < pairs_r) break;
-            pair -= pairs_r;
-        }
-        s_row = r < p.num_rows ? r : -1;
-        const int first = ((tiles_r + 1) / 2 - 1 - pair) * 2;        // the pair's first tile
-        s_q0 = first * FA_BM;
-        s_nsub = first + 1 < tiles_r ? 2 : 1;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -853,13 +865,13 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-static int launch_fa_pp(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
-                        cudaStream_t stream) {
+static int launch_fa_pp(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int work_tokens,
+                        int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)128 * 64 * 2 * (2 + 2 * PP_STAGES) + 1024;
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const int tiles = (num_tokens + FA_BM - 1) / FA_BM + p.num_rows;
-    const dim3 grid(p.num_heads, (tiles + p.num_rows + 1) / 2);
+    const int tiles = (work_tokens + FA_BM - 1) / FA_BM + work_rows;
+    const dim3 grid(p.num_heads, (tiles + work_rows + 1) / 2);
     return launch_kernel(prefill_attention_pp_kernel, grid, dim3(PP_THREADS), smem, stream, mq, mk, mv, p);
 }
 
@@ -879,30 +891,33 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
 static int g_fa_pp_mode = -1;
 
 template <int D>
-static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int num_tokens,
-                     cudaStream_t stream) {
+static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int work_tokens,
+                     int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 6 + 1024;     // 2 x Q + 2 x (K + V)
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    // tiles <= tokens / 128 + rows; a block takes one tile, or a pair of them (at most (tiles + rows) / 2
-    // pairs) once the tiles of all heads are more than the GPU runs at a time
-    const int tiles = (num_tokens + FA_BM - 1) / FA_BM + p.num_rows;
+    // tiles <= tokens / 128 + rows (of the rows that this kernel serves, where the caller knows them); a block takes
+    // one tile, or a pair of them (at most (tiles + rows) / 2 pairs) once the tiles of all heads are more than the
+    // GPU runs at a time
+    const int tiles = (work_tokens + FA_BM - 1) / FA_BM + work_rows;
     FaParams pp = p;
     pp.pair = (int64_t)tiles * p.num_heads > (int64_t)device_sm_count() * (D == 64 ? 2 : 1);
-    const dim3 grid(pp.pair ? (tiles + p.num_rows + 1) / 2 : tiles, p.num_heads);
+    const dim3 grid(pp.pair ? (tiles + work_rows + 1) / 2 : tiles, p.num_heads);
     return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, pp);
 }
 
 // q: the fused qkv activation [num_tokens, q_stride] bfloat16 (query head h at columns h*D ..), caches
 // [num_pages, kv_heads, page_size, D] bfloat16, out [num_tokens, heads, D] bfloat16.  head_dim 64 or
 // 128, page_size a power of two >= 8, q_stride % 8 == 0.  Rows with fewer than min_q_len new tokens
-// are skipped.
+// are skipped.  work_rows / work_tokens: how many rows have min_q_len tokens or more, and their tokens in sum, where the
+// caller knows (the grid is laid out for the tiles they can have); 0: every row may, num_rows / num_tokens.
 extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                                         int64_t num_pages, const int* block_tables, int table_stride, const int* row_q_start,
                                         const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens, void* out,
                                         int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
-                                        int min_q_len, cudaStream_t stream) {
+                                        int min_q_len, int work_rows, int work_tokens, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
+    if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim != 64 && head_dim != 128) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return MIE_ERR_BAD_ARG;
     if (page_size < 8 || (page_size & (page_size - 1)) || q_stride % 8) return MIE_ERR_BAD_ARG;
@@ -930,13 +945,13 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
         // two query tiles side by side once there are three pairs for every SM (measured, 32 heads, one tile a block
         // against two side by side: 2,048 tokens 45.1 against 48.5 us, 4,096 tokens 143.7 against 142.4 us, 8,192 tokens
         // 496 against 462 us); below that the one-tile blocks, two on an SM, spread a launch over more SMs
-        const int64_t tiles = (num_tokens + FA_BM - 1) / FA_BM;
-        if ((tiles + 2 * num_rows) / 2 < 65535 &&
+        const int64_t tiles = (work_tokens + FA_BM - 1) / FA_BM;
+        if ((tiles + 2 * work_rows) / 2 < 65535 &&
             (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 6 * (int64_t)device_sm_count())))
-            return launch_fa_pp(mq, mk, mv, p, num_tokens, stream);
-        return launch_fa<64>(mq, mk, mv, p, num_tokens, stream);
+            return launch_fa_pp(mq, mk, mv, p, work_tokens, work_rows, stream);
+        return launch_fa<64>(mq, mk, mv, p, work_tokens, work_rows, stream);
     }
-    return launch_fa<128>(mq, mk, mv, p, num_tokens, stream);
+    return launch_fa<128>(mq, mk, mv, p, work_tokens, work_rows, stream);
 }
 
 // Which kernel serves head_dim 64: -1 chooses by the size of the launch (the default), 0 always one query tile a block,

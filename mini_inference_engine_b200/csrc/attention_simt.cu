@@ -60,22 +60,19 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     float* k_s = q_s + ATT_WARPS * D;           // [ATT_KEYS][DP]
     float* v_s = k_s + ATT_KEYS * DP;           // [ATT_KEYS][DP]
 
-    pdl_enter();
-    // which row and query tile is this block's?
-    if (threadIdx.x == 0) {
-        int tile = blockIdx.x, r = 0;
-        for (; r < num_rows; ++r) {
-            const int ql = row_q_len[r];
-            const int tiles = ql >= min_q_len ? (ql + QT - 1) / QT : 0;   // shorter rows belong to another kernel
-            if (tile < tiles) break;
-            tile -= tiles;
-        }
-        s_row = r < num_rows ? r : -1;
-        s_q0 = tile * QT;
+    pdl_launch_dependents();
+    // which row and query tile is this block's?  (a whole warp asks: warp_find_row)
+    if (threadIdx.x < 32) {
+        int tile, tiles;
+        const int found = warp_find_row(row_q_len, num_rows, (int)blockIdx.x,
+                                        [&](int ql) { return ql >= min_q_len ? (ql + QT - 1) / QT : 0; },   // shorter rows belong to another kernel
+                                        tile, tiles);
+        if (threadIdx.x == 0) { s_row = found; s_q0 = tile * QT; }
     }
     __syncthreads();
     const int r = s_row;
     if (r < 0) return;
+    pdl_wait();
     const int q0 = s_q0;
     const int q_len = row_q_len[r], ctx_len = row_ctx_len[r], q_start = row_q_start[r];
     if (ctx_len > table_stride * page_size) {      // more positions than the row's block table covers: reported, row left alone

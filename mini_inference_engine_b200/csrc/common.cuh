@@ -59,6 +59,39 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// The row that work item `index` belongs to when row r has items_of(row_q_len[r]) items (0 for a row that another
+// kernel serves), found by the 32 lanes of a warp together -- 32 rows a round, a prefix sum by shuffles -- instead of
+// one thread walking the rows: a step may hold hundreds of one-token rows in front of the row a block is looking
+// for.  Returns the row (-1: there is no such item), the item's number within the row and the row's item count;
+// every lane gets the same answer.  Row lengths belong to the step's inputs, copied to the device before its first
+// kernel: they may be read before the dependency wait.
+template <typename F>
+__device__ __forceinline__ int warp_find_row(const int* __restrict__ row_q_len, int num_rows, int index, F items_of,
+                                             int& within, int& items_r) {
+    const int lane = threadIdx.x & 31;
+    for (int base = 0; base < num_rows; base += 32) {
+        const int r = base + lane;
+        const int n = r < num_rows ? items_of(row_q_len[r]) : 0;
+        int incl = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        if (index < total) {
+            const int l = __ffs(__ballot_sync(0xffffffffu, incl > index)) - 1;
+            items_r = __shfl_sync(0xffffffffu, n, l);
+            within = index - (__shfl_sync(0xffffffffu, incl, l) - items_r);
+            return base + l;
+        }
+        index -= total;
+    }
+    within = 0;
+    items_r = 0;
+    return -1;
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Streaming multiprocessors of the current device, asked once per device.

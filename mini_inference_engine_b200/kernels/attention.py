@@ -74,5 +74,11 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
         tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
         fn = ops.prefill_attention_tc if tc else ops.prefill_attention
-        fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window, min_q_len=min_q_len)
+        # the rows that are portions, and their tokens: the launch is laid out for those, not for every decoding row
+        work = None
+        if q_lens is not None:
+            long = [n for n in q_lens if n >= min_q_len]
+            work = (len(long), sum(long))
+        fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
+           min_q_len=min_q_len, work=work)
     return out

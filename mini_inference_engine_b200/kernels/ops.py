@@ -229,9 +229,11 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
 def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                       row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: int | None = None,
-                      min_q_len: int = 2) -> torch.Tensor:
+                      min_q_len: int = 2, work=None) -> torch.Tensor:
     """Causal attention of prompt portions over their request's pages (bfloat16, tensor cores).
-    Rows with fewer than ``min_q_len`` new tokens are left alone."""
+    Rows with fewer than ``min_q_len`` new tokens are left alone.  ``work`` = (rows, tokens): how many rows have
+    ``min_q_len`` tokens or more and their tokens in sum, where the caller knows -- the launch then has blocks for the
+    tiles those rows can have, not for every row of the step."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the prefill kernel takes multiples of 16 from 16 to 128")
@@ -245,16 +247,17 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
                                      _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                      _ptr(row_ctx_len), row_q_len.numel(), num_tokens, _ptr(out), num_heads,
                                      num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window or 0),
-                                     int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), _stream()), "prefill_attention")
+                                     int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), *_work_args(work), _stream()),
+           "prefill_attention")
     return out
 
 
 def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                          row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                          head_dim: int, page_size: int, scale: float, window: int | None = None,
-                         min_q_len: int = 2) -> torch.Tensor:
+                         min_q_len: int = 2, work=None) -> torch.Tensor:
     """Causal attention of prompt portions on tcgen05 (S and O in tensor memory, operands by TMA);
-    head_dim 64 or 128."""
+    head_dim 64 or 128.  ``work``: as for ``prefill_attention``."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
     _need(head_dim in (64, 128), f"head_dim {head_dim}: the tcgen05 prefill kernel takes 64 and 128")
     _need(q_stride % 8 == 0 and page_size >= 8, "the tcgen05 prefill kernel needs q rows and pages of whole 16-byte pieces")
@@ -268,9 +271,14 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
                                         ctypes.c_int64(k_cache.shape[0]), _ptr(block_tables), block_tables.shape[1],
                                         _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len), row_q_len.numel(),
                                         num_tokens, _ptr(out), num_heads, num_kv_heads, head_dim, page_size,
-                                        ctypes.c_float(scale), int(window or 0), int(min_q_len), _stream()),
+                                        ctypes.c_float(scale), int(window or 0), int(min_q_len), *_work_args(work), _stream()),
            "prefill_attention_tc")
     return out
+
+
+def _work_args(work):
+    rows, tokens = work if work is not None else (0, 0)
+    return int(rows), int(tokens)
 
 
 def set_prefill_pairs(mode: int = -1) -> None:

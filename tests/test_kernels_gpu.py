@@ -1,5 +1,6 @@
 """Each CUDA kernel alone against the plain float32 formulas, at sizes other than the engine's."""
 import math
+import random
 
 import pytest
 import torch
@@ -116,7 +117,7 @@ def test_rope_and_cache_write(ops, dt, H, Hkv, D, rot, page):
     assert (kc.permute(0, 2, 1, 3).reshape(num_pages * page, -1)[untouched] == 7.0).all()   # nothing else was written
 
 
-def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None, kernel="simt", min_q_len=1):
+def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None, kernel="simt", min_q_len=1, work=None):
     """rows: list of (q_len, ctx_len).  Builds random q/k/v per request, scatters k/v into pages, runs
     the kernel and the plain attention on each request's whole sequence."""
     torch.manual_seed(seed)
@@ -154,8 +155,9 @@ def _paged_case(ops, dt, H, Hkv, D, page, rows, window=None, seed=0, boost=None,
     q_start = torch.cumsum(q_len, 0, dtype=torch.int32) - q_len
     out = torch.full((T, H, D), 77.0, dtype=dt, device=DEV)
     fn = {"simt": ops.paged_attention, "prefill": ops.prefill_attention, "prefill_tc": ops.prefill_attention_tc}[kernel]
+    more = {} if work is None else {"work": work}
     fn(q_all.to(DEV).contiguous(), H * D, k_cache.to(DEV), v_cache.to(DEV), bt.to(DEV), q_start.to(DEV),
-       q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window, min_q_len=min_q_len)
+       q_len.to(DEV), ctx_len.to(DEV), T, out, H, Hkv, D, page, scale, window, min_q_len=min_q_len, **more)
     torch.cuda.synchronize()
     ops.check_tc_errors()
     return out, torch.cat(want, 0)
@@ -166,6 +168,27 @@ RAGGED = [[(1, 1)], [(1, 17)], [(1, 1000)], [(1, 2048)],
           [(5, 5), (17, 17), (33, 33)],                                       # whole prompts
           [(7, 40), (2, 18), (1, 129), (16, 16), (31, 300)],                  # continued portions beside decodes
           [(300, 300)]]
+
+
+@pytest.mark.parametrize("kernel,D", [("prefill_tc", 64), ("prefill_tc", 128), ("prefill", 48), ("simt", 32)])
+@pytest.mark.parametrize("hint", [False, True])
+def test_portions_among_hundreds_of_one_token_rows(ops, kernel, D, hint):
+    """A step of many decoding requests and a few prompt portions: the kernels for portions find a block's row among
+    hundreds of rows that are not theirs (32 rows a round, by a whole warp), in front of, between and behind the
+    portions; with the caller's count of portions and their tokens the launch has no blocks for the others (and must
+    still reach every tile), without it the surplus blocks leave at once.  One-token rows stay untouched by the
+    kernels that skip them."""
+    rng = random.Random(D)
+    rows = ([(1, rng.randrange(1, 80)) for _ in range(70)] + [(200, 260)] + [(1, rng.randrange(1, 80)) for _ in range(100)]
+            + [(2, 2), (129, 129)] + [(1, rng.randrange(1, 80)) for _ in range(90)] + [(300, 300)] + [(1, 5)] * 3)
+    min_q_len = 1 if kernel == "simt" else 2
+    long = [q for q, _ in rows if q >= min_q_len]
+    out, want = _paged_case(ops, torch.bfloat16, 8, 2, D, 16, rows, kernel=kernel, min_q_len=min_q_len, seed=D,
+                            work=(len(long), sum(long)) if hint and kernel != "simt" else None)
+    q_len = torch.tensor([q for q, _ in rows])
+    live = torch.repeat_interleave(q_len >= min_q_len, q_len)
+    close(out[live.to(DEV)], want[live], torch.bfloat16, f"{kernel}: portions among one-token rows")
+    assert (out[~live.to(DEV)] == 77.0).all()
 
 
 @pytest.mark.parametrize("dt", DTYPES)
