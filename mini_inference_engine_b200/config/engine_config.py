@@ -27,6 +27,9 @@ class EngineConfig:
     seed: int = 0                           # sampling seed
     overlap_steps: bool = True              # launch step N+1 before reading step N's tokens (they are fed back on the device)
     graph_prompt_portions: int = 16         # graphs kept for prompt portions, by padded length (0 = none: such steps launch kernel by kernel)
+    warm_up_prompt_step: bool = True        # run one prompt step of the whole token budget on the scratch page at construction:
+                                            # kernels for portions, the library's choices for that many rows and the
+                                            # allocator's blocks are then in place before the first request's first step
     split_step_max_tokens: int = 512        # a portion of up to this many tokens beside decoding requests runs as a graph of
                                             # its own after the decode graph (the weights are read twice, the host launches
                                             # twice instead of 200 times); a longer one keeps the device busy longer than the

@@ -140,6 +140,30 @@ class LLMEngine:
         self.d2h_bytes = 0
         if self.cfg.use_cuda_graphs:
             self._capture_cuda_graphs()
+        if self.cfg.warm_up_prompt_step:
+            self._warm_up_prompt_step()
+
+    @torch.inference_mode()
+    def _warm_up_prompt_step(self):
+        """One prompt step of the whole token budget on scratch rows (tokens 0 at positions 0.. of page 0, as the
+        padding of a portion graph; no logits wanted), and one that wants a token: what a first real step would
+        otherwise pay for -- kernel modules loaded at first use, the library's choice of a product for that many rows,
+        blocks of the allocator -- is paid here.  Nothing but the scratch page is written."""
+        from .batch import BatchRow
+        n = min(self.cfg.max_num_batched_tokens, self.cfg.max_model_len)
+        if n < 2:
+            return
+        b = self.runner.builder
+        pages = -(-n // self.cfg.block_size)
+        zeros = [np.zeros(pages, dtype=np.int32) for _ in range(b.num_groups)]
+        for want in ((), (n - 1,)):
+            row = BatchRow(np.zeros(n, dtype=np.int32), 0, zeros, 0, want)
+            buf, layout = b.pack([row], extras=self.sampler.inputs(len(want)))
+            ctx = b.to_device(buf, layout)
+            ctx.token_feedback = self._sampled
+            self._forward_and_sample(ctx, self._sampled[self._portion_slot:self._portion_slot + len(want)],
+                                     host_out=self._pinned_portion)
+        torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ CUDA graphs of decode steps
     def _forward_and_sample(self, ctx, tokens_out=None, host_out=None, seed=None):

@@ -381,6 +381,23 @@ def test_decode_steps_of_many_requests_rotate_inside_attention(name, graphs, mod
     ops.check_tc_errors()
 
 
+def test_warm_up_step_at_construction_leaves_no_trace(model_folders):
+    """The engine runs one prompt step of the whole token budget on scratch rows when it is built (kernels loaded, the
+    library's choices made before the first request).  It holds no page afterwards, counts no step, and the tokens of
+    the requests that follow are those of an engine built without it."""
+    from mini_inference_engine_b200 import SamplingParams
+    folder = model_folders["tiny_d"]
+    rng = random.Random(23)
+    prompts = [[rng.randrange(1031) for _ in range(n)] for n in (40, 7, 150)]
+    outs = {}
+    for warm in (True, False):
+        eng = engine_for(folder, torch.bfloat16, warm_up_prompt_step=warm, max_num_batched_tokens=64, max_model_len=192)
+        assert eng.num_steps == 0 and eng.cache.num_free() == eng.cache.pools[0].num_usable
+        outs[warm] = [o.output_ids for o in eng.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+        assert eng.cache.num_free() == eng.cache.pools[0].num_usable
+    assert outs[True] == outs[False]
+
+
 def test_prompt_portions_through_the_paired_product(model_folders, monkeypatch):
     """The gate/up product of prompt-sized batches runs on pairs of SMs where its tiles fill the GPU; a tiny
     model never gets there, so the thresholds are lowered here: prompts of 150 - 250 tokens of `tiny_b` (width 96,
