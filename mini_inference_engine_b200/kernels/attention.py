@@ -30,10 +30,24 @@ def set_backend(name: str) -> None:
     _backend = name
 
 
+def _row_kinds(ctx) -> tuple:
+    """(rows of one token, rows of more, tokens of those) of the step, or None where the host does not know the rows'
+    lengths (a captured step).  Counted once a step, not once a layer: a step may hold hundreds of rows."""
+    kinds = ctx.host.get("_row_kinds", False)
+    if kinds is False:
+        q_lens = ctx.host.get("q_len")
+        kinds = None
+        if q_lens is not None:
+            long = [n for n in q_lens if n > 1]
+            kinds = (len(q_lens) - len(long), len(long), sum(long))
+        ctx.host["_row_kinds"] = kinds
+    return kinds
+
+
 def decode_only(ctx) -> bool:
     """Whether every row of the step has exactly one new token (known on the host)."""
-    q_lens = ctx.host.get("q_len")
-    return q_lens is not None and all(n == 1 for n in q_lens)
+    kinds = _row_kinds(ctx)
+    return kinds is not None and kinds[1] == 0 and kinds[0] > 0
 
 
 def rotates_in_decode(dtype, head_dim: int, ctx) -> bool:
@@ -59,11 +73,11 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
     if not fast:
         return ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size,
                                    scale, window)
-    q_lens = ctx.host.get("q_len")
-    has_decode = q_lens is None or any(n == 1 for n in q_lens)
-    has_prefill = q_lens is None or any(n > 1 for n in q_lens)
+    kinds = _row_kinds(ctx)
+    has_decode = kinds is None or kinds[0] > 0
+    has_prefill = kinds is None or kinds[1] > 0
     min_q_len = 2
-    if q_lens is None and ctx.host.get("few_single_rows"):
+    if kinds is None and ctx.host.get("few_single_rows"):
         # row lengths unknown here (a captured step), but rows of one token are the exception among them: the
         # kernel for portions takes those too, and the launch of the decode kernel is saved
         has_decode, min_q_len = False, 1
@@ -75,10 +89,7 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
         fn = ops.prefill_attention_tc if tc else ops.prefill_attention
         # the rows that are portions, and their tokens: the launch is laid out for those, not for every decoding row
-        work = None
-        if q_lens is not None:
-            long = [n for n in q_lens if n >= min_q_len]
-            work = (len(long), sum(long))
+        work = None if kinds is None else (kinds[1], kinds[2])
         fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
            min_q_len=min_q_len, work=work)
     return out
