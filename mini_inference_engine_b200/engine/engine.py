@@ -9,6 +9,7 @@ decode step is one transfer in, one graph launch, one transfer out.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import time
 from dataclasses import dataclass
@@ -136,6 +137,7 @@ class LLMEngine:
         self._portion_graphs: dict = {}          # (tokens, wanted logits) -> captured step of one prompt portion
         self._portion_seen: dict = {}
         self._graph_pool = None
+        self._capture_stream = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         if self.cfg.use_cuda_graphs:
@@ -226,6 +228,24 @@ class LLMEngine:
     # ------------------------------------------------------------------ CUDA graphs of prompt portions
     PORTION_GRAPH_MIN_TOKENS = 2
 
+    @contextlib.contextmanager
+    def _capturing(self, graph):
+        """Captures what the body launches into ``graph`` (memory from the graphs' shared pool) in the middle of
+        serving: on a side stream that waits for the serving stream, without the device-wide synchronisation and the
+        emptying of the device and pinned-memory caches that ``torch.cuda.graph`` begins with -- those cost a capture
+        10 to 60 ms, stall the step in flight, and leave the next eager steps to allocate their buffers anew."""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+        side, main = self._capture_stream, torch.cuda.current_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            graph.capture_begin(self._graph_pool) if self._graph_pool is not None else graph.capture_begin()
+            try:
+                yield
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+
     @staticmethod
     def _padded_length(n: int) -> int:
         """The token count of the graph that serves a portion of ``n`` tokens: the next multiple of 32 up to
@@ -278,10 +298,9 @@ class LLMEngine:
         tokens = self._sampled[self._portion_slot:self._portion_slot + wanted]
         # no warm-up run: a step of this shape has run before (kernels built, buffers sized), and running
         # this one twice would write the request's cache twice -- harmless, but not free
-        torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph, pool=self._graph_pool):
+        with self._capturing(graph):
             self._forward_and_sample(ctx, tokens, host_out=self._pinned_portion)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
