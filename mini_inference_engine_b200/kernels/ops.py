@@ -318,14 +318,25 @@ def _workspace(device, name: str, numel: int, dtype) -> torch.Tensor:
     return t
 
 
-def decode_splits(rows: int, kv_units: int, max_ctx: int) -> int:
-    """How many parts to cut the context into (a cluster of 2, 4 or 8 blocks).  Splitting pays while the
-    batch alone leaves SMs idle; measured on B200, once rows x kv heads reaches the SM count the
-    cluster launches cost more than they bring (batch 64, 4 kv heads, 512 keys: 12.5 us unsplit, 18.6 us
-    with 2 splits, 50 us with 8).  Parts are never shorter than one 64-key tile (the reference keeps
-    256 keys a part, inference_engine/kernels/decode_attention.py:117-125)."""
+def decode_splits(rows: int, kv_units: int, max_ctx: int, head_dim: int = 64) -> int:
+    """How many parts to cut the context into (a cluster of 2, 4 or 8 blocks; the reference keeps 256 keys a
+    part, inference_engine/kernels/decode_attention.py:117-125).
+
+    Heads of up to 64: as many parts as still leave every block a place beside the others -- four blocks on an SM
+    with page copies by TMA and two stages (``decode_uses_tma``, ``decode_stages``) -- and two 64-key tiles a part.
+    Measured on B200 (32 q / 4 kv heads of 64, device time in a graph, context bound 960; the plan before ->
+    this one): 512 keys, 20 / 32 rows 7.1 -> 6.4 / 8.2 -> 7.0 us (4 parts), 40 / 64 / 72 rows 10.5 -> 8.7 / 11.6 -> 9.2 /
+    12.0 -> 9.4 us (2 parts), 80 / 96 rows 20.4 -> 11.3 / 20.6 -> 11.6 us (whole, by TMA, four stages); 960 keys, 16
+    rows 8.4 -> 7.3 us (8 parts), 24 rows 11.8 -> 9.0, 64 rows 19.7 -> 14.2, 96 rows 36.4 -> 19.6 us.  One block
+    more than the places (592) and the launch takes half as long again: 72 rows in two parts 9.4 us, 80 rows 16.3.
+    Wider heads (two blocks on an SM): parts while the batch alone leaves SMs idle."""
     blocks = max(1, rows * kv_units)
     splits = 1
+    if head_dim <= 64:
+        most = -(-(-(-max(1, max_ctx) // 64)) // 2)            # two tiles a part at least
+        while splits < 8 and blocks * splits * 2 <= decode_blocks_per_sm(head_dim) * num_sms() and splits * 2 <= most:
+            splits *= 2
+        return splits
     while splits < 8 and blocks * splits * 2 <= 2 * num_sms() and splits * 64 < max_ctx:
         splits *= 2
     return splits
@@ -356,16 +367,17 @@ def decode_plan(rows: int, kv_units: int, max_ctx: int, tma_ok: bool, head_dim: 
     heads of 128 (32 rows x 2,048 keys) the whole context per block is the fastest plan (46.3 us; two parts
     62.7 us): 256 blocks already fill the two places an SM has."""
     units = max(1, rows * kv_units)
-    clustered = decode_splits(rows, kv_units, max_ctx)
+    clustered = decode_splits(rows, kv_units, max_ctx, head_dim)
     tiles = -(-max(1, max_ctx) // 64)
     if tma_ok and units >= 64 and tiles >= 2 * LONG_PART_TILES:
         parts = min(decode_blocks_per_sm(head_dim) * num_sms() // units, tiles // LONG_PART_TILES, 16)
-        if parts >= 2 and parts > clustered:
+        # (heads of up to 64, as many parts either way: through scratch a short row is cut into fewer)
+        if parts >= 2 and (parts > clustered or (parts == clustered and head_dim <= 64)):
             return parts, "scratch", LONG_PART_TILES
     return clustered, "cluster", 0
 
 
-def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False, head_dim: int = 64) -> int:
+def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False, head_dim: int = 64, clustered: bool = True) -> int:
     """Tiles of 64 keys in flight per block.  Shared memory that attention does not take stays free
     for the prologue of the kernel after it (the output projection fills its ring with weights while
     attention still runs): measured on B200 in the whole decode step at batch 8, 512 keys, three
@@ -379,6 +391,10 @@ def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False, hea
     tiles = -(-(-(-max(1, max_ctx) // splits)) // 64)
     if head_dim > 64 and tma:
         return 2 if blocks > 6 * num_sms() else 3
+    if tma and splits > 1 and clustered:
+        return 2                          # the parts of a cluster by TMA: four blocks on an SM (see decode_splits)
+    if tma and blocks <= 3 * num_sms():
+        return 4                          # whole contexts by TMA, up to three blocks an SM (80 rows x 512 keys: 11.3 us; 128 rows want three stages: 13.0 against 21.0 us)
     if blocks > 3 * num_sms():
         return 3 if tma else 2            # TMA tiles are unpadded: three stages still put four blocks on an SM (256 x 512: 29.2 us, two stages 30.7)
     return 3 if tiles <= 4 else 4
@@ -387,14 +403,15 @@ def decode_stages(blocks: int, max_ctx: int, splits: int, tma: bool = False, hea
 def decode_uses_tma(blocks: int, head_dim: int = 64) -> bool:
     """Whether the decode kernel fetches keys and values a page per TMA copy instead of 16 bytes per
     cp.async.  Measured on B200 (32 q / 4 kv heads of 64): it pays where there are more blocks than
-    fit beside one another (128 requests x 512 keys: 14.9 us against 20.6 us; 256 x 512: 29.2 against
-    34.4 us) and costs a little where each block walks a long part alone (64 x 2048: 42.9 against
+    fit beside one another at three or four padded stages of 16-byte copies, from two blocks per SM on (128 requests
+    x 512 keys: 14.9 us against 20.6 us; 256 x 512: 29.2 against 34.4 us; 80 x 512, whole contexts: 11.3 against
+    20.4 us; 16 x 960 in 8 parts: 7.3 against 12.0 us) and costs a little where each block walks a long part alone (64 x 2048: 42.9 against
     40.0 us; 8 x 512: 7.5 against 7.1 us) -- the copies were never the bound there, the softmax
     bookkeeping per 16 keys is.  Cache slots beyond a request's context are copied along with their
     page and must hold finite values (the cache storage starts as zeros).  Heads of 128: always -- a stage of
     cp.async copies is 34 KB there and the 16-byte copies are four times as many (8 rows x 512 keys, 8 kv heads:
     7.3 against 14.2 us; 1,024 keys 9.8 against 20.4 us; 32 kv heads, 1 row x 512 keys: 6.2 against 14.4 us)."""
-    return head_dim > 64 or blocks > 3 * num_sms()
+    return head_dim > 64 or blocks > 2 * num_sms()
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
@@ -437,13 +454,14 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
         if merge == "scratch" and tma is None:
             tma = True
     elif splits is None:
-        splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1)
+        splits = decode_splits(rows, num_kv_heads * chunks, max_ctx or 1, head_dim)
     merge = merge or "cluster"
     if tma is None:
         tma = decode_uses_tma(rows * num_kv_heads * chunks * splits, head_dim)
     tma = bool(tma) and tma_ok
     if stages is None:
-        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma, head_dim)
+        stages = decode_stages(rows * num_kv_heads * chunks * splits, max_ctx or 4096, splits, tma, head_dim,
+                               clustered=merge == "cluster" and splits in (1, 2, 4, 8))
     part_o = part_lse = counters = None
     if merge == "cluster" and splits not in (1, 2, 4, 8):
         merge = "scratch"

@@ -6,10 +6,28 @@ from mini_inference_engine_b200.kernels import device, ops
 
 def test_decode_plan_keeps_the_cluster_merge_for_few_rows_and_short_contexts():
     assert device.num_sms() == device.B200_SMS or device.num_sms() > 0
-    for rows, ctx in [(1, 512), (8, 512), (8, 8192), (8, 32768), (16, 1024), (64, 512), (256, 512), (64, 960)]:
+    for rows, ctx in [(1, 512), (8, 512), (8, 8192), (8, 32768), (16, 960), (64, 512), (256, 512), (64, 960)]:
         splits, merge, part = ops.decode_plan(rows, 4, ctx, True)
         assert merge == "cluster" and part == 0 and splits == ops.decode_splits(rows, 4, ctx), (rows, ctx)
-    assert ops.decode_plan(64, 4, 8192, False) == (1, "cluster", 0)          # no page copies by TMA: the old plan
+
+
+def test_decode_plan_for_heads_of_64_fills_four_places_per_sm_with_parts_of_two_tiles():
+    if device.num_sms() != device.B200_SMS:
+        pytest.skip("the expected numbers are for 148 SMs")
+    # (rows, context bound) -> parts, page copies by TMA, stages: the measured winners (4 kv heads)
+    want = {(8, 960): (8, False, 3), (8, 512): (4, False, 3), (16, 960): (8, True, 2), (20, 960): (4, True, 2),
+            (32, 512): (4, True, 2), (40, 512): (2, True, 2), (64, 960): (2, True, 2), (72, 512): (2, True, 2),
+            (80, 512): (1, True, 4), (96, 960): (1, True, 4), (128, 512): (1, True, 3), (256, 512): (1, True, 3),
+            (1, 960): (8, False, 3), (4, 256): (2, False, 3)}
+    for (rows, ctx), (parts, tma, stages) in want.items():
+        splits = ops.decode_splits(rows, 4, ctx, 64)
+        blocks = rows * 4 * splits
+        got = (splits, ops.decode_uses_tma(blocks, 64), ops.decode_stages(blocks, ctx, splits, ops.decode_uses_tma(blocks, 64), 64))
+        assert got == (parts, tma, stages), (rows, ctx, got)
+        assert blocks <= 4 * 148 or splits == 1
+    # merged through scratch (long contexts): the stages as before, whatever the parts
+    assert ops.decode_stages(512, 8192, 2, True, 64, clustered=False) == 3
+    assert ops.decode_stages(256, 8192, 4, True, 64, clustered=False) == 4
 
 
 @pytest.mark.parametrize("rows,ctx,parts", [(64, 8192, 2), (64, 2048, 2), (32, 8192, 4), (32, 2048, 4), (16, 8192, 9),
@@ -51,7 +69,7 @@ def test_decode_plan_for_heads_of_128_counts_two_blocks_per_sm():
     assert ops.decode_plan(32, 8, 2048, True, 128) == (1, "cluster", 0)       # 256 blocks fill the two places an SM has
     assert ops.decode_plan(8, 8, 4096, True, 128) == (4, "cluster", 0)
     assert ops.decode_plan(16, 8, 8192, True, 128) == (2, "cluster", 0)
-    assert ops.decode_uses_tma(10, 128) and not ops.decode_uses_tma(10, 64) and ops.decode_uses_tma(3 * 148 + 1, 64)
+    assert ops.decode_uses_tma(10, 128) and not ops.decode_uses_tma(10, 64) and ops.decode_uses_tma(2 * 148 + 1, 64)
     assert ops.decode_stages(2048, 512, 1, True, 128) == 2 and ops.decode_stages(512, 512, 1, True, 128) == 3
     assert ops.decode_stages(512, 512, 1, False, 128) == 2                   # cp.async: unchanged
 
