@@ -52,9 +52,11 @@ def plan(M: int, N: int, K: int) -> dict:
     room = 2 * sms if swapped else sms
     while splits < 8 and tiles * splits * 2 <= room and k_tiles // (splits * 2) >= 2:
         # a cluster of 2, 4 or 8 blocks per tile, two k-tiles each at least; more blocks than SMs only if
-        # each still streams eight k-tiles (a second wave of short blocks costs more than it brings: the
-        # q|k|v product of TinyLlama, 20 tiles, runs the whole decode step 11 us faster with 4 splits than 8)
-        if tiles * splits * 2 > sms and k_tiles // (splits * 2) < 8:
+        # each still streams four k-tiles (a second wave of short blocks costs more than it brings).  The
+        # q|k|v product of TinyLlama (20 tiles, 32 k-tiles) used to run the whole decode step 11 us faster
+        # with 4 splits than with 8; since a block asks L2 for its weight tiles before its dependency wait
+        # the 160 blocks of 8 splits win by 6 us (0.7805 -> 0.7748 ms), and 2 splits lose 26 us
+        if tiles * splits * 2 > sms and k_tiles // (splits * 2) < 4:
             break
         splits *= 2
     per_split = -(-k_tiles // splits)
