@@ -370,9 +370,13 @@ def decode_plan(rows: int, kv_units: int, max_ctx: int, tma_ok: bool, head_dim: 
     clustered = decode_splits(rows, kv_units, max_ctx, head_dim)
     tiles = -(-max(1, max_ctx) // 64)
     if tma_ok and units >= 64 and tiles >= 2 * LONG_PART_TILES:
-        parts = min(decode_blocks_per_sm(head_dim) * num_sms() // units, tiles // LONG_PART_TILES, 16)
-        # (heads of up to 64, as many parts either way: through scratch a short row is cut into fewer)
-        if parts >= 2 and (parts > clustered or (parts == clustered and head_dim <= 64)):
+        parts = min(decode_blocks_per_sm(head_dim) * num_sms() // units, tiles // LONG_PART_TILES, 8 if head_dim <= 64 else 16)
+        # Only where scratch allows MORE parts than a cluster (which takes 2, 4 or 8): with as many parts the cluster
+        # is the faster merge (heads of 64, page copies by TMA, two stages; rows x keys, scratch -> cluster:
+        # 64 x 2,048 31.5 -> 25.6 us, 64 x 3,400 45.5 -> 39.6, 32 x 2,048 18.2 -> 14.6, 16 x 2,048 17.6 -> 10.0 us);
+        # three parts through scratch against two of a cluster win from about 3,400 keys on (48 x 7,000: 63.9
+        # against 71.9 us; 48 x 2,048: 27.0 against 24.0 us)
+        if parts >= 2 and parts > clustered:
             return parts, "scratch", LONG_PART_TILES
     return clustered, "cluster", 0
 

@@ -318,10 +318,11 @@ def test_decode_graphs_by_context_bound(model_folders):
 
 
 def test_long_contexts_cut_into_parts_under_graphs(tmp_path):
-    """64 requests x 4 kv heads with a context bound beyond 1,024 keys: the decode graphs' attention launches are
-    laid out for parts merged through scratch memory, and every row is cut by its own length -- one request
-    grows across 1,024 keys (one part, then two) while the others stay whole.  Tokens against the plain
-    implementation, and the scratch that the graphs hold stays in place while eager steps ask for more."""
+    """48 requests x 4 kv heads with a context bound of 1,600 keys: the decode graphs' attention launches are
+    laid out for three parts merged through scratch memory (a cluster would take two), and every row is cut by its
+    own length -- one request grows across 1,024 keys (one part, then two) while the others stay whole.  Tokens
+    against the plain implementation, and the scratch that the graphs hold stays in place while eager steps ask for
+    more."""
     from mini_inference_engine_b200 import SamplingParams
     from mini_inference_engine_b200.config import load_config
     from mini_inference_engine_b200.kernels import ops
@@ -329,14 +330,14 @@ def test_long_contexts_cut_into_parts_under_graphs(tmp_path):
     folder = str(tmp_path / "long")
     write_model_folder(folder, load_config(dict(
         vocab_size=300, hidden_size=256, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
-        num_key_value_heads=4, head_dim=64, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=1088,
+        num_key_value_heads=4, head_dim=64, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=1600,
         tie_word_embeddings=True, architectures=["LlamaForCausalLM"])), seed=21)
     cfg, W = pl.read_config(folder), plain_weights(folder)
-    assert ops.decode_plan(64, 4, 1088, True, 64) == (2, "scratch", ops.LONG_PART_TILES)
+    assert ops.decode_plan(48, 4, 1600, True, 64) == (3, "scratch", ops.LONG_PART_TILES)
     rng = random.Random(8)
-    lengths = [1015, 955] + [rng.randrange(700, 1000) for _ in range(62)]
+    lengths = [1015, 955] + [rng.randrange(700, 1000) for _ in range(46)]
     prompts = [[rng.randrange(300) for _ in range(n)] for n in lengths]
-    eng = engine_for(folder, torch.bfloat16, max_num_seqs=64, max_model_len=1088, cuda_graph_batch_sizes=(64,),
+    eng = engine_for(folder, torch.bfloat16, max_num_seqs=48, max_model_len=1600, cuda_graph_batch_sizes=(48,),
                      max_num_batched_tokens=4096)
     outs = eng.generate(prompts, SamplingParams(max_tokens=24, ignore_eos=True))
     assert eng.num_graph_steps >= 20 and all(len(o.output_ids) == 24 for o in outs)

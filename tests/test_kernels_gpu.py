@@ -410,10 +410,15 @@ def test_decode_attention_plan_for_long_contexts(ops):
     """The plan the wrapper makes by itself for 64 and more (row, kv head) units under a long context bound
     (parts through scratch, rows cut by their own lengths) gives the plain answer, ragged lengths included."""
     from mini_inference_engine_b200.kernels import ops as ops_mod
-    assert ops_mod.decode_plan(32, 4, 8192, True) == (4, "scratch", ops_mod.LONG_PART_TILES)
-    ctxs = [3000, 17, 1, 512, 513, 2048, 100, 1024] * 4
+    assert ops_mod.decode_plan(24, 4, 8192, True) == (6, "scratch", ops_mod.LONG_PART_TILES)
+    ctxs = [3000, 17, 1, 512, 513, 2048, 100, 1024] * 3
     out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, None, merge=None, max_ctx=8192, seed=3)
     close(out, want, torch.bfloat16, "decode, planned for 8,192 keys")
+    # and where a cluster cuts as often as scratch would, the cluster of the plan (4 parts, page copies by TMA)
+    assert ops_mod.decode_plan(32, 4, 8192, True) == (4, "cluster", 0)
+    ctxs = [3000, 17, 1, 512, 513, 2048, 100, 1024] * 4
+    out, want, _ = _decode_case(ops, 32, 4, 64, 16, ctxs, None, merge=None, max_ctx=8192, seed=4)
+    close(out, want, torch.bfloat16, "decode, planned for 8,192 keys, 32 rows")
 
 
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 6, 48, 32), (16, 1, 128, 64),

@@ -30,8 +30,14 @@ def test_decode_plan_for_heads_of_64_fills_four_places_per_sm_with_parts_of_two_
     assert ops.decode_stages(256, 8192, 4, True, 64, clustered=False) == 4
 
 
-@pytest.mark.parametrize("rows,ctx,parts", [(64, 8192, 2), (64, 2048, 2), (32, 8192, 4), (32, 2048, 4), (16, 8192, 9),
-                                            (48, 4096, 3), (20, 1 << 20, 7)])
+def test_decode_plan_leaves_long_contexts_to_the_cluster_where_it_cuts_as_often():
+    if device.num_sms() != device.B200_SMS:
+        pytest.skip("the expected numbers are for 148 SMs")
+    for rows, ctx, parts in [(64, 8192, 2), (64, 2048, 2), (32, 8192, 4), (32, 2048, 4), (16, 8192, 8)]:
+        assert ops.decode_plan(rows, 4, ctx, True) == (parts, "cluster", 0), (rows, ctx)
+
+
+@pytest.mark.parametrize("rows,ctx,parts", [(48, 4096, 3), (40, 8192, 3), (24, 8192, 6), (20, 1 << 20, 7)])
 def test_decode_plan_fills_four_blocks_per_sm_for_long_contexts(rows, ctx, parts):
     sms = device.num_sms()
     if sms != device.B200_SMS:
